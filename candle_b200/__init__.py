@@ -1,0 +1,28 @@
+"""candle_b200: candle's normalisation + embedding path on B200 (sm_100a).
+
+The package is the Python-side mirror of the candle front ends for this path
+(``candle_nn::ops::{rms_norm, layer_norm}``, ``candle_nn::{LayerNorm, RmsNorm, Embedding}``,
+``Tensor::index_select``, ``QTensor::dequantize``) on top of the C ABI in ``include/candle_b200.h``.
+torch supplies device memory and streams only; every result is computed by the CUDA kernels in
+``csrc/``.  Importing the package needs the built library -- there is no CPU fallback.
+"""
+from . import _cabi  # noqa: F401  (fails loudly when the extension is missing)
+from .errors import CandleError, InvalidIndex
+from .ops import (
+    FLAG_FAST_SUM,
+    FLAG_FORCE_GENERIC,
+    FLAG_FORCE_LANEROW,
+    embedding_rms_norm,
+    index_select,
+    layer_norm,
+    qembedding_rms_norm,
+    rms_norm,
+)
+from .nn import Embedding, LayerNorm, QEmbedding, RmsNorm
+from .quantized import GgmlDType, QTensor
+
+__all__ = [
+    "CandleError", "InvalidIndex", "rms_norm", "layer_norm", "index_select", "embedding_rms_norm",
+    "qembedding_rms_norm", "Embedding", "LayerNorm", "RmsNorm", "QEmbedding", "QTensor", "GgmlDType",
+    "FLAG_FAST_SUM", "FLAG_FORCE_LANEROW", "FLAG_FORCE_GENERIC",
+]

@@ -1,0 +1,286 @@
+// The extern "C" surface declared in include/candle_b200.h: argument validation, error strings
+// and dispatch to the kernel launchers.  No allocation, no synchronisation, no global state
+// beyond a thread-local error message.
+#include <cstdarg>
+#include <cstdio>
+
+#include "launch.h"
+#include "qblocks.cuh"
+#include "rms_rowreg.cuh"
+
+namespace {
+
+thread_local char g_last_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_result(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return CB200_OK;
+  return fail(CB200_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool valid_dtype(int d) { return d == CB200_DTYPE_F32 || d == CB200_DTYPE_F16 || d == CB200_DTYPE_BF16; }
+bool valid_id_dtype(int d) { return d == CB200_ID_U8 || d == CB200_ID_U32 || d == CB200_ID_I64; }
+bool valid_qtype(int q) { return q == CB200_QTYPE_Q4_0 || q == CB200_QTYPE_Q8_0; }
+int elem_bytes(int d) { return d == CB200_DTYPE_F32 ? 4 : 2; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename... P>
+bool all_aligned16(P... ptrs) {
+  return (aligned16(ptrs) && ...);
+}
+
+int norm_impl(int op, const void* x, const void* residual, const void* alpha, const void* beta, void* y,
+              void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags, cudaStream_t stream) {
+  const char* name = op == cb200::kOpLayerNorm ? "cb200_layer_norm" : "cb200_rms_norm";
+  if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
+  if (rows < 0 || cols < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape [%lld, %d]", name, (long long)rows, cols);
+  if (rows == 0) return CB200_OK;
+  if (cols == 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: rows of zero columns cannot be normalised", name);
+  if (x == nullptr || alpha == nullptr || y == nullptr || (op == cb200::kOpLayerNorm && beta == nullptr))
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  if (rows > (int64_t(1) << 40)) return fail(CB200_E_INVALID_ARGUMENT, "%s: too many rows", name);
+
+  const bool vec_ok = all_aligned16(x, residual, alpha, beta, y, sum_out) &&
+                      (static_cast<int64_t>(cols) * elem_bytes(dtype)) % 16 == 0;
+  const bool force_lane = flags & CB200_FLAG_FORCE_LANEROW;
+  const bool force_generic = flags & CB200_FLAG_FORCE_GENERIC;
+
+  if (op == cb200::kOpRmsNorm && vec_ok && !force_lane && !force_generic && cb200::rms_rowreg_supported(dtype, cols)) {
+    cb200::RmsRowRegArgs a{};
+    a.x = static_cast<const uint4*>(x);
+    a.res = static_cast<const uint4*>(residual);
+    a.alpha = static_cast<const uint4*>(alpha);
+    a.y = static_cast<uint4*>(y);
+    a.sum_out = static_cast<uint4*>(sum_out);
+    a.rows = rows;
+    a.V = cols / 8;
+    a.n = cols;
+    a.eps = eps;
+    a.flags = flags;
+    return cuda_result(cb200::launch_rms_rowreg(dtype, a, stream), name);
+  }
+  cb200::LaneRowArgs a{};
+  a.x = x;
+  a.res = residual;
+  a.alpha = alpha;
+  a.beta = beta;
+  a.y = y;
+  a.sum_out = sum_out;
+  a.rows = rows;
+  a.n = cols;
+  a.eps = eps;
+  if (vec_ok && !force_generic && cb200::norm_lanerow_supported(dtype, cols))
+    return cuda_result(cb200::launch_norm_lanerow(dtype, op, a, stream), name);
+  return cuda_result(cb200::launch_norm_generic(dtype, op, a, stream), name);
+}
+
+int check_lookup(const char* name, const void* table, const void* ids, const void* out, int64_t vocab,
+                 int64_t hidden, int64_t n_ids, int id_dtype) {
+  if (!valid_id_dtype(id_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported ids dtype code %d", name, id_dtype);
+  if (vocab < 0 || hidden < 0 || n_ids < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape", name);
+  if (n_ids > 0 && hidden > 0 && (table == nullptr || ids == nullptr || out == nullptr))
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  return CB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_version(void) { return CB200_VERSION; }
+
+const char* cb200_last_error(void) { return g_last_error; }
+
+int cb200_rms_norm(const void* x, const void* residual, const void* alpha, void* y, void* sum_out, int64_t rows,
+                   int32_t cols, float eps, int dtype, int flags, cb200_stream_t stream) {
+  return norm_impl(cb200::kOpRmsNorm, x, residual, alpha, nullptr, y, sum_out, rows, cols, eps, dtype, flags, stream);
+}
+
+int cb200_layer_norm(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
+                     void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags,
+                     cb200_stream_t stream) {
+  return norm_impl(cb200::kOpLayerNorm, x, residual, gamma, beta, y, sum_out, rows, cols, eps, dtype, flags, stream);
+}
+
+int cb200_index_select(const void* src, const void* ids, void* out, int64_t left, int64_t src_dim, int64_t right,
+                       int64_t n_ids, int32_t elem_size, int id_dtype, cb200_status* status,
+                       cb200_stream_t stream) {
+  const char* name = "cb200_index_select";
+  if (!valid_id_dtype(id_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported ids dtype code %d", name, id_dtype);
+  if (left < 0 || src_dim < 0 || right < 0 || n_ids < 0 || elem_size <= 0)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: bad shape", name);
+  if (left == 0 || right == 0 || n_ids == 0) return CB200_OK;
+  if (src == nullptr || ids == nullptr || out == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  cb200::GatherArgs a{};
+  a.src = static_cast<const unsigned char*>(src);
+  a.ids = ids;
+  a.out = static_cast<unsigned char*>(out);
+  a.left = left;
+  a.src_dim = src_dim;
+  a.n_ids = n_ids;
+  a.row_bytes = right * elem_size;
+  a.id_dtype = id_dtype;
+  a.status = status;
+  return cuda_result(cb200::launch_gather_rows(a, stream), name);
+}
+
+int cb200_embedding(const void* table, const void* ids, void* out, int64_t vocab, int32_t hidden, int64_t n_ids,
+                    int dtype, int id_dtype, cb200_status* status, cb200_stream_t stream) {
+  if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "cb200_embedding: unsupported dtype code %d", dtype);
+  int rc = check_lookup("cb200_embedding", table, ids, out, vocab, hidden, n_ids, id_dtype);
+  if (rc != CB200_OK) return rc;
+  return cb200_index_select(table, ids, out, 1, vocab, hidden, n_ids, elem_bytes(dtype), id_dtype, status, stream);
+}
+
+int cb200_dequantize(const void* blocks, int qtype, void* out, int64_t k, int out_dtype, cb200_stream_t stream) {
+  const char* name = "cb200_dequantize";
+  if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
+  if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
+  if (k < 0 || k % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: %lld is not divisible by 32", name, (long long)k);
+  if (k == 0) return CB200_OK;
+  if (blocks == nullptr || out == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  if (!aligned16(out) || (reinterpret_cast<uintptr_t>(blocks) & 1u))
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: output must be 16-byte aligned and blocks 2-byte aligned", name);
+  return cuda_result(cb200::launch_dequantize_flat(qtype, out_dtype, blocks, out, k / 32, stream), name);
+}
+
+int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, int64_t vocab, int32_t hidden,
+                     int64_t n_ids, int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
+                     cb200_status* status, cb200_stream_t stream) {
+  const char* name = "cb200_qembedding";
+  if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
+  if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
+  int rc = check_lookup(name, qtable, ids, out, vocab, hidden, n_ids, id_dtype);
+  if (rc != CB200_OK) return rc;
+  if (hidden % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by 32", name, hidden);
+  if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
+                (long long)vocab_end, (long long)vocab);
+  if (n_ids == 0 || hidden == 0) return CB200_OK;
+  if (!aligned16(out) || (reinterpret_cast<uintptr_t>(qtable) & 1u))
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: output must be 16-byte aligned and the table 2-byte aligned", name);
+  cb200::QGatherArgs a{};
+  a.qtable = static_cast<const unsigned char*>(qtable);
+  a.ids = ids;
+  a.out = out;
+  a.id_dtype = id_dtype;
+  a.vocab = vocab;
+  a.vocab_begin = vocab_begin;
+  a.vocab_end = vocab_end;
+  a.status = status;
+  a.rows = n_ids;
+  a.n = hidden;
+  a.row_bytes = hidden / 32 * cb200::qblock_bytes(qtype);
+  a.bulk = aligned16(qtable) && a.row_bytes % 16 == 0;
+  if (2 * ((a.row_bytes + 15) & ~15) + 64 > 227 * 1024)
+    return fail(CB200_E_UNSUPPORTED_SHAPE, "%s: hidden size %d exceeds the staged-row limit", name, hidden);
+  return cuda_result(cb200::launch_qgather(qtype, out_dtype, a, stream), name);
+}
+
+int cb200_embedding_rms_norm(const void* table, const void* ids, const void* alpha, void* y, void* gathered,
+                             int64_t vocab, int32_t hidden, int64_t n_ids, float eps, int dtype, int id_dtype,
+                             int flags, cb200_status* status, cb200_stream_t stream) {
+  const char* name = "cb200_embedding_rms_norm";
+  if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
+  int rc = check_lookup(name, table, ids, y, vocab, hidden, n_ids, id_dtype);
+  if (rc != CB200_OK) return rc;
+  if (n_ids == 0) return CB200_OK;
+  if (hidden == 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: rows of zero columns cannot be normalised", name);
+  if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  const bool vec_ok = all_aligned16(table, alpha, y, gathered) && (static_cast<int64_t>(hidden) * elem_bytes(dtype)) % 16 == 0;
+  const bool force_lane = flags & CB200_FLAG_FORCE_LANEROW;
+  const bool force_generic = flags & CB200_FLAG_FORCE_GENERIC;
+  if (vec_ok && !force_lane && !force_generic && cb200::rms_rowreg_supported(dtype, hidden)) {
+    cb200::RmsRowRegArgs a{};
+    a.x = static_cast<const uint4*>(table);
+    a.alpha = static_cast<const uint4*>(alpha);
+    a.y = static_cast<uint4*>(y);
+    a.sum_out = static_cast<uint4*>(gathered);
+    a.ids = ids;
+    a.id_dtype = id_dtype;
+    a.vocab = vocab;
+    a.status = status;
+    a.rows = n_ids;
+    a.V = hidden / 8;
+    a.n = hidden;
+    a.eps = eps;
+    a.flags = flags;
+    return cuda_result(cb200::launch_rms_rowreg(dtype, a, stream), name);
+  }
+  cb200::LaneRowArgs a{};
+  a.x = table;
+  a.alpha = alpha;
+  a.y = y;
+  a.sum_out = gathered;
+  a.ids = ids;
+  a.id_dtype = id_dtype;
+  a.vocab = vocab;
+  a.status = status;
+  a.rows = n_ids;
+  a.n = hidden;
+  a.eps = eps;
+  a.bulk = 1;
+  if (vec_ok && !force_generic && cb200::norm_lanerow_supported(dtype, hidden))
+    return cuda_result(cb200::launch_norm_lanerow(dtype, cb200::kOpRmsNorm, a, stream), name);
+  return cuda_result(cb200::launch_norm_generic(dtype, cb200::kOpRmsNorm, a, stream), name);
+}
+
+int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, const void* alpha, void* y,
+                              void* gathered, int64_t vocab, int32_t hidden, int64_t n_ids, float eps, int out_dtype,
+                              int id_dtype, int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
+                              cb200_stream_t stream) {
+  const char* name = "cb200_qembedding_rms_norm";
+  if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
+  if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
+  int rc = check_lookup(name, qtable, ids, y, vocab, hidden, n_ids, id_dtype);
+  if (rc != CB200_OK) return rc;
+  if (hidden % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by 32", name, hidden);
+  if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
+                (long long)vocab_end, (long long)vocab);
+  if (n_ids == 0) return CB200_OK;
+  if (hidden == 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: rows of zero columns cannot be normalised", name);
+  if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  if (!all_aligned16(alpha, y, gathered) || (reinterpret_cast<uintptr_t>(qtable) & 1u))
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha, y and gathered must be 16-byte aligned, the table 2-byte aligned", name);
+  const bool fused = out_dtype != CB200_DTYPE_F32 && cb200::rms_rowreg_supported(out_dtype, hidden) &&
+                     !(flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC));
+  if (!fused) {
+    // Two launches through the caller's `gathered` buffer (f32 output, or a forced implementation).
+    if (gathered == nullptr)
+      return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: this dtype/flag combination needs a `gathered` buffer", name);
+    rc = cb200_qembedding(qtable, qtype, ids, gathered, vocab, hidden, n_ids, out_dtype, id_dtype, vocab_begin,
+                          vocab_end, status, stream);
+    if (rc != CB200_OK) return rc;
+    return cb200_rms_norm(gathered, nullptr, alpha, y, nullptr, n_ids, hidden, eps, out_dtype, flags, stream);
+  }
+  cb200::QRmsArgs a{};
+  a.qtable = static_cast<const unsigned char*>(qtable);
+  a.ids = ids;
+  a.alpha = static_cast<const uint4*>(alpha);
+  a.y = static_cast<uint4*>(y);
+  a.gathered = static_cast<uint4*>(gathered);
+  a.id_dtype = id_dtype;
+  a.vocab = vocab;
+  a.vocab_begin = vocab_begin;
+  a.vocab_end = vocab_end;
+  a.status = status;
+  a.rows = n_ids;
+  a.V = hidden / 8;
+  a.n = hidden;
+  a.row_bytes = hidden / 32 * cb200::qblock_bytes(qtype);
+  a.bulk = aligned16(qtable) && a.row_bytes % 16 == 0;
+  a.eps = eps;
+  a.flags = flags;
+  return cuda_result(cb200::launch_qrms_rowreg(qtype, out_dtype, a, stream), name);
+}
+
+}  // extern "C"

@@ -1,0 +1,71 @@
+// Host-side launcher declarations shared by the .cu files and the C ABI layer.
+#pragma once
+
+#include "common.cuh"
+
+namespace cb200 {
+
+constexpr int kOpRmsNorm = 0;
+constexpr int kOpLayerNorm = 1;
+
+// Arguments of the lane-per-row and any-shape norm kernels.
+struct LaneRowArgs {
+  const void* x;      // [rows, n], or the dense table [vocab, n] when ids != nullptr
+  const void* res;    // optional residual (dense source only)
+  const void* alpha;  // weight [n]
+  const void* beta;   // bias [n] (layer norm)
+  void* y;
+  void* sum_out;      // optional: h = x + res, or the gathered rows
+  const void* ids;
+  int id_dtype;
+  int64_t vocab;
+  cb200_status* status;
+  int64_t rows;
+  int n;
+  float eps;
+  int bulk;   // gather source: stage rows with the bulk-copy engine
+  int V;      // filled by the launcher: 16-byte vectors per row
+  int pitch;  // filled by the launcher: shared-memory row pitch in bytes
+  int R;      // filled by the launcher: rows per CTA
+};
+
+struct RmsRowRegArgs;
+struct QRmsArgs;
+
+bool rms_rowreg_supported(int dtype, int cols);
+cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t stream);
+cudaError_t launch_qrms_rowreg(int qtype, int dtype, const QRmsArgs& a, cudaStream_t stream);
+
+bool norm_lanerow_supported(int dtype, int cols);
+cudaError_t launch_norm_lanerow(int dtype, int op, const LaneRowArgs& a, cudaStream_t stream);
+cudaError_t launch_norm_generic(int dtype, int op, const LaneRowArgs& a, cudaStream_t stream);
+
+// Row gathers (embedding.cu)
+struct GatherArgs {
+  const unsigned char* src;  // [left, src_dim, row_bytes]
+  const void* ids;
+  unsigned char* out;        // [left, n_ids, row_bytes]
+  int64_t left, src_dim, n_ids;
+  int64_t row_bytes;
+  int id_dtype;
+  cb200_status* status;
+};
+cudaError_t launch_gather_rows(const GatherArgs& a, cudaStream_t stream);
+
+struct QGatherArgs {
+  const unsigned char* qtable;
+  const void* ids;
+  void* out;
+  int id_dtype;
+  int64_t vocab, vocab_begin, vocab_end;
+  cb200_status* status;
+  int64_t rows;
+  int n;          // elements per row (multiple of 32)
+  int row_bytes;  // bytes per quantised row
+  int bulk;
+};
+cudaError_t launch_qgather(int qtype, int out_dtype, const QGatherArgs& a, cudaStream_t stream);
+cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks, void* out, int64_t n_blocks,
+                                   cudaStream_t stream);
+
+}  // namespace cb200

@@ -1,0 +1,331 @@
+// Lane-per-row norms: the exact-order kernels for layer norm (all dtypes) and f32 RMS norm.
+//
+// candle's CPU path accumulates each row's sum (and sum of squares) strictly left to right in
+// f32 (candle-nn/src/ops.rs:484-490, 709-715).  For these ops nothing coarser than f32 absorbs
+// the rounding of that sum, so bit-equal results need the same order.  A CTA stages R whole rows
+// in shared memory (h = T(x + residual) when a residual is given, or rows gathered from a dense
+// table by the bulk-copy engine), then one LANE per row walks its row sequentially -- R
+// independent dependency chains advance per instruction, and several CTAs per SM overlap their
+// load / chain / store phases -- and finally all threads normalise and store the rows with
+// 16-byte coalesced accesses.  Each row is read from HBM once.
+// The row pitch in shared memory is an odd number of 16-byte units so the 16-byte loads of the
+// lane-per-row walk are bank-conflict free.
+#include "launch.h"
+
+namespace cb200 {
+
+constexpr int kLaneRowThreads = 256;
+constexpr int kLaneRowWarps = kLaneRowThreads / 32;
+
+template <int DT>
+__device__ __forceinline__ void vec_to_floats(const uint4& q, float (&f)[Elem<DT>::kPerVec]) {
+  if constexpr (DT == kDtF32) {
+    f[0] = __uint_as_float(q.x);
+    f[1] = __uint_as_float(q.y);
+    f[2] = __uint_as_float(q.z);
+    f[3] = __uint_as_float(q.w);
+  } else {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = unpack2<DT>(w[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+template <int DT>
+__device__ __forceinline__ uint4 floats_to_vec(const float (&f)[Elem<DT>::kPerVec]) {
+  if constexpr (DT == kDtF32) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  } else {
+    return make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
+  }
+}
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const LaneRowArgs a) {
+  constexpr int PV = Elem<DT>::kPerVec;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* rowbuf = smem_raw;                                                  // [R][pitch]
+  float2* stats = reinterpret_cast<float2*>(smem_raw + static_cast<size_t>(a.R) * a.pitch);  // [R]
+  int* valid = reinterpret_cast<int*>(stats + a.R);                                  // [R]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(valid + a.R + (a.R & 1));              // 8-byte aligned
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * a.R;
+  const int live = static_cast<int>(min(static_cast<int64_t>(a.R), a.rows - row0));
+  const uint4* gx = static_cast<const uint4*>(a.x);
+
+  // ---- fill ----
+  if (a.ids != nullptr) {
+    if (a.bulk) {
+      if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_init_fence();
+        uint32_t bytes = 0;
+        for (int r = 0; r < live; ++r) {
+          uint64_t id = read_id(a.ids, a.id_dtype, row0 + r);
+          int ok = id < static_cast<uint64_t>(a.vocab);
+          valid[r] = ok;
+          if (ok)
+            bytes += static_cast<uint32_t>(a.V) * 16u;
+          else
+            report_status(a.status, CB200_STATUS_INVALID_INDEX, row0 + r, static_cast<int64_t>(id), a.vocab);
+        }
+        mbar_expect_tx(bar, bytes);
+        for (int r = 0; r < live; ++r) {
+          if (!valid[r]) continue;
+          uint64_t id = read_id(a.ids, a.id_dtype, row0 + r);
+          bulk_g2s(rowbuf + static_cast<size_t>(r) * a.pitch, gx + id * a.V, static_cast<uint32_t>(a.V) * 16u, bar);
+        }
+      }
+      __syncthreads();
+      const bool ok = mbar_wait(bar, 0);
+      if (!__syncthreads_and(ok ? 1 : 0)) {
+        // give the copies in flight one more bounded chance to land before the CTA retires
+        if (tid == 0) {
+          mbar_wait(bar, 0);
+          report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row0, 0, a.vocab);
+        }
+        return;
+      }
+    } else {
+      for (int r = warp; r < live; r += kLaneRowWarps) {
+        uint64_t id = read_id(a.ids, a.id_dtype, row0 + r);
+        int ok = id < static_cast<uint64_t>(a.vocab);
+        if (lane == 0) {
+          valid[r] = ok;
+          if (!ok) report_status(a.status, CB200_STATUS_INVALID_INDEX, row0 + r, static_cast<int64_t>(id), a.vocab);
+        }
+        if (!ok) continue;
+        uint4* dst = reinterpret_cast<uint4*>(rowbuf + static_cast<size_t>(r) * a.pitch);
+        for (int v = lane; v < a.V; v += 32) dst[v] = ldg_stream(gx + id * a.V + v);
+      }
+      __syncthreads();
+    }
+  } else {
+    const uint4* gr = static_cast<const uint4*>(a.res);
+    uint4* gs = static_cast<uint4*>(a.sum_out);
+    for (int r = warp; r < live; r += kLaneRowWarps) {
+      const int64_t base = (row0 + r) * a.V;
+      uint4* dst = reinterpret_cast<uint4*>(rowbuf + static_cast<size_t>(r) * a.pitch);
+      for (int v0 = lane; v0 < a.V; v0 += 128) {
+        uint4 xv[4], rv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int v = v0 + 32 * j;
+          if (v < a.V) xv[j] = ldg_stream(gx + base + v);
+        }
+        if (gr != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int v = v0 + 32 * j;
+            if (v < a.V) rv[j] = ldg_stream(gr + base + v);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float fa[PV], fb[PV];
+            vec_to_floats<DT>(xv[j], fa);
+            vec_to_floats<DT>(rv[j], fb);
+#pragma unroll
+            for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
+            xv[j] = floats_to_vec<DT>(fa);  // rounds the sum to T, as Tensor::add does
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int v = v0 + 32 * j;
+          if (v < a.V) {
+            dst[v] = xv[j];
+            if (gs != nullptr) stg_stream(gs + base + v, xv[j]);
+          }
+        }
+      }
+    }
+    if (tid < live) valid[tid] = 1;
+    __syncthreads();
+  }
+
+  // ---- pass 1: one lane per row, strictly sequential f32 accumulation ----
+  if (tid < live && valid[tid]) {
+    const uint4* row = reinterpret_cast<const uint4*>(rowbuf + static_cast<size_t>(tid) * a.pitch);
+    float s = 0.0f, s2 = 0.0f;
+#pragma unroll 4
+    for (int v = 0; v < a.V; ++v) {
+      float f[PV];
+      vec_to_floats<DT>(row[v], f);
+#pragma unroll
+      for (int e = 0; e < PV; ++e) {
+        if (OP == kOpLayerNorm) s = __fadd_rn(s, f[e]);
+        s2 = __fadd_rn(s2, __fmul_rn(f[e], f[e]));
+      }
+    }
+    const float nf = static_cast<float>(a.n);
+    if (OP == kOpLayerNorm) {
+      // candle-nn/src/ops.rs:716-718
+      float mean = __fdiv_rn(s, nf);
+      float var = __fsub_rn(__fdiv_rn(s2, nf), __fmul_rn(mean, mean));
+      float inv_std = __frcp_rn(__fsqrt_rn(__fadd_rn(var, a.eps)));
+      stats[tid] = make_float2(mean, inv_std);
+    } else {
+      // candle-nn/src/ops.rs:491-492
+      stats[tid] = make_float2(round_to<DT>(rms_from_sum(s2, nf, a.eps)), 0.0f);
+    }
+  }
+  __syncthreads();
+
+  // ---- pass 2: normalise and store, 16 bytes per thread, coalesced ----
+  const uint4* ga = static_cast<const uint4*>(a.alpha);
+  const uint4* gb = static_cast<const uint4*>(a.beta);
+  uint4* gy = static_cast<uint4*>(a.y);
+  uint4* gg = (a.ids != nullptr) ? static_cast<uint4*>(a.sum_out) : nullptr;  // gathered rows
+  for (int r = warp; r < live; r += kLaneRowWarps) {
+    if (!valid[r]) continue;
+    const float2 st = stats[r];
+    const int64_t base = (row0 + r) * a.V;
+    const uint4* row = reinterpret_cast<const uint4*>(rowbuf + static_cast<size_t>(r) * a.pitch);
+    for (int v = lane; v < a.V; v += 32) {
+      const uint4 hv = row[v];
+      float h[PV], g[PV], o[PV];
+      vec_to_floats<DT>(hv, h);
+      vec_to_floats<DT>(__ldg(ga + v), g);
+      if (OP == kOpLayerNorm) {
+        float b[PV];
+        vec_to_floats<DT>(__ldg(gb + v), b);
+#pragma unroll
+        for (int e = 0; e < PV; ++e)
+          o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), g[e]), b[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), g[e]);
+      }
+      stg_stream(gy + base + v, floats_to_vec<DT>(o));
+      if (gg != nullptr) stg_stream(gg + base + v, hv);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Any-shape fallback: one thread per row, scalar accesses, same arithmetic and order.  Used for
+// rows that are not 16-byte multiples, misaligned bases, and rows too long for shared memory.
+// ---------------------------------------------------------------------------------------------
+template <int DT, int OP>
+__global__ void norm_generic_kernel(const LaneRowArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= a.rows) return;
+  int64_t src_row = row;
+  if (a.ids != nullptr) {
+    uint64_t id = read_id(a.ids, a.id_dtype, row);
+    if (id >= static_cast<uint64_t>(a.vocab)) {
+      report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
+      return;
+    }
+    src_row = static_cast<int64_t>(id);
+  }
+  const int64_t xo = src_row * a.n, ro = row * a.n;
+  const bool has_res = a.ids == nullptr && a.res != nullptr;
+  float s = 0.0f, s2 = 0.0f;
+  for (int c = 0; c < a.n; ++c) {
+    float h = load_elem<DT>(a.x, xo + c);
+    if (has_res) h = round_to<DT>(__fadd_rn(h, load_elem<DT>(a.res, ro + c)));
+    if (OP == kOpLayerNorm) s = __fadd_rn(s, h);
+    s2 = __fadd_rn(s2, __fmul_rn(h, h));
+  }
+  const float nf = static_cast<float>(a.n);
+  float mean = 0.0f, scale;
+  if (OP == kOpLayerNorm) {
+    mean = __fdiv_rn(s, nf);
+    float var = __fsub_rn(__fdiv_rn(s2, nf), __fmul_rn(mean, mean));
+    scale = __frcp_rn(__fsqrt_rn(__fadd_rn(var, a.eps)));
+  } else {
+    scale = round_to<DT>(rms_from_sum(s2, nf, a.eps));
+  }
+  for (int c = 0; c < a.n; ++c) {
+    float h = load_elem<DT>(a.x, xo + c);
+    if (has_res) h = round_to<DT>(__fadd_rn(h, load_elem<DT>(a.res, ro + c)));
+    float g = load_elem<DT>(a.alpha, c);
+    float o;
+    if (OP == kOpLayerNorm)
+      o = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h, mean), scale), g), load_elem<DT>(a.beta, c));
+    else
+      o = __fmul_rn(round_to<DT>(__fdiv_rn(h, scale)), g);
+    store_elem<DT>(a.y, ro + c, o);
+    if (a.sum_out != nullptr) store_elem<DT>(a.sum_out, ro + c, h);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Launchers
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kMaxDynSmem = 227 * 1024;
+
+static size_t lanerow_smem(int R, int pitch) {
+  return static_cast<size_t>(R) * pitch + static_cast<size_t>(R) * 8 + static_cast<size_t>(R + (R & 1)) * 4 + 16;
+}
+
+bool norm_lanerow_supported(int dtype, int cols) {
+  int esz = dtype == kDtF32 ? 4 : 2;
+  int64_t row_bytes = static_cast<int64_t>(cols) * esz;
+  if (cols <= 0 || row_bytes % 16 != 0) return false;
+  return lanerow_smem(1, static_cast<int>(row_bytes) + 16) <= kMaxDynSmem;
+}
+
+template <int DT, int OP>
+static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
+  const int row_bytes = a.n * Elem<DT>::kBytes;
+  a.V = row_bytes / 16;
+  a.pitch = row_bytes + ((a.V & 1) ? 0 : 16);
+  // rows per CTA: up to a warp's worth, sized so that about three CTAs fit in an SM's shared
+  // memory, and small enough that small problems still spread over all SMs
+  int R = static_cast<int>((72 * 1024) / a.pitch);
+  if (R > 32) R = 32;
+  if (R < 1) R = 1;
+  int64_t spread = (a.rows + 2 * kSmCount - 1) / (2 * kSmCount);
+  if (R > spread) R = static_cast<int>(spread);
+  a.R = R;
+  size_t smem = lanerow_smem(R, a.pitch);
+  auto kern = norm_lanerow_kernel<DT, OP>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
+  int64_t grid = (a.rows + R - 1) / R;
+  kern<<<static_cast<unsigned>(grid), kLaneRowThreads, smem, stream>>>(a);
+  return cudaGetLastError();
+}
+
+template <int DT, int OP>
+static cudaError_t launch_generic_t(const LaneRowArgs& a, cudaStream_t stream) {
+  const int threads = 64;
+  int64_t grid = (a.rows + threads - 1) / threads;
+  norm_generic_kernel<DT, OP><<<static_cast<unsigned>(grid), threads, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+template <int OP>
+static cudaError_t dispatch_dt(int dtype, bool generic, const LaneRowArgs& a, cudaStream_t stream) {
+  switch (dtype) {
+    case kDtF32:
+      return generic ? launch_generic_t<kDtF32, OP>(a, stream) : launch_lanerow_t<kDtF32, OP>(a, stream);
+    case kDtF16:
+      return generic ? launch_generic_t<kDtF16, OP>(a, stream) : launch_lanerow_t<kDtF16, OP>(a, stream);
+    default:
+      return generic ? launch_generic_t<kDtBF16, OP>(a, stream) : launch_lanerow_t<kDtBF16, OP>(a, stream);
+  }
+}
+
+cudaError_t launch_norm_lanerow(int dtype, int op, const LaneRowArgs& a, cudaStream_t stream) {
+  if (a.rows == 0) return cudaSuccess;
+  return op == kOpLayerNorm ? dispatch_dt<kOpLayerNorm>(dtype, false, a, stream)
+                            : dispatch_dt<kOpRmsNorm>(dtype, false, a, stream);
+}
+
+cudaError_t launch_norm_generic(int dtype, int op, const LaneRowArgs& a, cudaStream_t stream) {
+  if (a.rows == 0) return cudaSuccess;
+  return op == kOpLayerNorm ? dispatch_dt<kOpLayerNorm>(dtype, true, a, stream)
+                            : dispatch_dt<kOpRmsNorm>(dtype, true, a, stream);
+}
+
+}  // namespace cb200

@@ -1,0 +1,69 @@
+// Decoders for GGML Q4_0 / Q8_0 blocks (32 elements per block).
+//   BlockQ4_0 { d: f16, qs: [u8; 16] }  18 bytes   candle-core/src/quantized/k_quants.rs:42-48
+//   BlockQ8_0 { d: f16, qs: [i8; 32] }  34 bytes   candle-core/src/quantized/k_quants.rs:78-84
+// Values follow GgmlType::to_float (k_quants.rs:163-183 and 568-584):
+//   Q4_0: y[j] = ((qs[j] & 15) - 8) * d,  y[j + 16] = ((qs[j] >> 4) - 8) * d   (j < 16)
+//   Q8_0: y[j] = qs[j] * d
+// The products are exact in f32 (an 8-bit integer times an 11-bit significand), so the decoded
+// f32 values, and their roundings to f16 / bf16, are bit-identical to the CPU's, including the
+// sign of zero: the integer is converted to float first and multiplied by d, exactly as the CPU
+// does, instead of the d*q + (-8d) form of the reference's CUDA kernel.
+// Blocks are only 2-byte aligned inside a row, hence the 16-bit loads.
+#pragma once
+
+#include "common.cuh"
+
+namespace cb200 {
+
+template <int QT>
+struct QBlock;
+template <>
+struct QBlock<CB200_QTYPE_Q4_0> {
+  static constexpr int kBytes = 18;
+};
+template <>
+struct QBlock<CB200_QTYPE_Q8_0> {
+  static constexpr int kBytes = 34;
+};
+
+__host__ __device__ inline int qblock_bytes(int qtype) {
+  return qtype == CB200_QTYPE_Q4_0 ? 18 : (qtype == CB200_QTYPE_Q8_0 ? 34 : 0);
+}
+
+// Decodes elements [8v, 8v+8) of a row of blocks starting at `row` (shared or global memory).
+template <int QT>
+__device__ __forceinline__ void decode8(const unsigned char* row, int v, float (&out)[8]) {
+  const int blk = v >> 2, sub = v & 3;
+  const unsigned char* b = row + blk * QBlock<QT>::kBytes;
+  const float d = __half2float(*reinterpret_cast<const __half*>(b));
+  if (QT == CB200_QTYPE_Q8_0) {
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + sub * 8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint16_t w = q[i];
+      out[2 * i] = __fmul_rn(static_cast<float>(static_cast<int8_t>(w & 0xFF)), d);
+      out[2 * i + 1] = __fmul_rn(static_cast<float>(static_cast<int8_t>(w >> 8)), d);
+    }
+  } else {
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + (sub & 1) * 8);
+    const int shift = (sub >> 1) * 4;  // elements 0..15 are low nibbles, 16..31 high nibbles
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint16_t w = q[i];
+      int n0 = ((w & 0xFF) >> shift) & 0xF;
+      int n1 = ((w >> 8) >> shift) & 0xF;
+      out[2 * i] = __fmul_rn(static_cast<float>(n0 - 8), d);
+      out[2 * i + 1] = __fmul_rn(static_cast<float>(n1 - 8), d);
+    }
+  }
+}
+
+// Same, rounded to a 16-bit type and packed into one 16-byte vector.
+template <int QT, int DT>
+__device__ __forceinline__ uint4 decode_vec8(const unsigned char* row, int v) {
+  float f[8];
+  decode8<QT>(row, v, f);
+  return make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
+}
+
+}  // namespace cb200

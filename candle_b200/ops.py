@@ -1,0 +1,213 @@
+"""Front ends with the names, argument meaning and error behaviour of candle's own.
+
+``rms_norm`` / ``layer_norm`` mirror ``candle_nn::ops::{rms_norm, layer_norm}``
+(candle-nn/src/ops.rs:641-652, 896-909) plus the checks their ``cuda_fwd`` performs
+(:536-543, 770-781); ``index_select`` mirrors ``Tensor::index_select``
+(candle-core/src/tensor.rs:1568-1589).  The optional ``residual`` argument fuses the
+``(x + residual)?`` the models compute just before the norm
+(candle-transformers/src/models/llama.rs:446-450, bert.rs:301).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+from ._cabi import FLAG_FAST_SUM, FLAG_FORCE_GENERIC, FLAG_FORCE_LANEROW  # noqa: F401
+from .errors import CandleError, InvalidIndex
+
+_DTYPES = {torch.float32: _cabi.DTYPE_F32, torch.float16: _cabi.DTYPE_F16, torch.bfloat16: _cabi.DTYPE_BF16}
+_DTYPE_NAMES = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16"}
+_ID_DTYPES = {
+    torch.uint8: _cabi.ID_U8,
+    torch.uint32: _cabi.ID_U32,
+    torch.int32: _cabi.ID_U32,  # the bit pattern is read as u32: negative values fail the bounds check
+    torch.int64: _cabi.ID_I64,
+}
+
+
+def _dims(t: torch.Tensor) -> str:
+    return str(list(t.shape))
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _same_device(*ts: torch.Tensor) -> None:
+    first = ts[0]
+    if not first.is_cuda:
+        raise CandleError("candle_b200 runs on Device::Cuda only: there is no CPU fallback")
+    for t in ts[1:]:
+        if t is not None and t.device != first.device:
+            raise CandleError(f"device mismatch in op, lhs: {first.device}, rhs: {t.device}")
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed ``cb200_status`` record (4 x int64 = 32 bytes) in device memory."""
+    return torch.zeros(4, dtype=torch.int64, device=device)
+
+
+def raise_for_status(status: torch.Tensor, op: str = "index-select") -> None:
+    """Synchronises on the status record and raises what candle's CPU backend would have raised."""
+    code_word, position, index, size = status.cpu().tolist()
+    code = code_word & 0xFFFFFFFF
+    if code == _cabi.STATUS_INVALID_INDEX:
+        raise InvalidIndex(index & (2**64 - 1), size, op, position)
+    if code == _cabi.STATUS_WAIT_TIMEOUT:
+        raise CandleError(f"device-side wait timed out at row {position} in {op}")
+
+
+def _norm_checks(name: str, xs: torch.Tensor, params: list[tuple[str, torch.Tensor]], residual):
+    if xs.dtype not in _DTYPES or any(p.dtype != xs.dtype for _, p in params):
+        raise CandleError(f"unsupported dtype for rmsnorm {_DTYPE_NAMES.get(xs.dtype, xs.dtype)}")
+    if not xs.is_contiguous():
+        raise CandleError("input has to be contiguous")
+    for pname, p in params:
+        if not p.is_contiguous():
+            raise CandleError(f"{pname} has to be contiguous")
+    if residual is not None:
+        if residual.shape != xs.shape or residual.dtype != xs.dtype:
+            raise CandleError(f"shape mismatch in binary op add, lhs: {_dims(xs)}, rhs: {_dims(residual)}")
+        if not residual.is_contiguous():
+            raise CandleError("input has to be contiguous")
+    _same_device(xs, *[p for _, p in params], residual)
+
+
+def rms_norm(xs: torch.Tensor, alpha: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
+             return_sum: bool = False, flags: int = 0):
+    """``candle_nn::ops::rms_norm(xs, alpha, eps)``; with ``residual`` the norm of ``xs + residual``.
+
+    Returns ``y``, or ``(y, xs + residual)`` when ``return_sum`` is set.
+    """
+    if xs.dim() == 0:
+        raise CandleError("unexpected rank, expected: at least 1, got: 0")
+    if alpha.dim() != 1:
+        raise CandleError(f"unexpected rank, expected: 1, got: {alpha.dim()} ({_dims(alpha)})")
+    if xs.shape[-1] != alpha.shape[0]:
+        raise CandleError(f"shape mismatch in rms-norm {_dims(xs)} {_dims(alpha)}")
+    _norm_checks("rms-norm", xs, [("alpha", alpha)], residual)
+    cols = xs.shape[-1]
+    rows = xs.numel() // cols if cols else 0
+    y = torch.empty_like(xs)
+    h = torch.empty_like(xs) if return_sum else None
+    _cabi.call("cb200_rms_norm", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(y), _ptr(h), rows, cols, float(eps),
+               _DTYPES[xs.dtype], flags, _stream(xs))
+    return (y, h) if return_sum else y
+
+
+def layer_norm(xs: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, eps: float, *,
+               residual: torch.Tensor | None = None, return_sum: bool = False, flags: int = 0):
+    """``candle_nn::ops::layer_norm(xs, alpha, beta, eps)``; with ``residual`` the norm of ``xs + residual``."""
+    if xs.dim() == 0:
+        raise CandleError("unexpected rank, expected: at least 1, got: 0")
+    if alpha.dim() != 1 or beta.dim() != 1:
+        bad = alpha if alpha.dim() != 1 else beta
+        raise CandleError(f"unexpected rank, expected: 1, got: {bad.dim()} ({_dims(bad)})")
+    if xs.shape[-1] != alpha.shape[0] or xs.shape[-1] != beta.shape[0]:
+        raise CandleError(f"shape mismatch in layer-norm src: {_dims(xs)} alpha: {_dims(alpha)} beta: {_dims(beta)}")
+    _norm_checks("layer-norm", xs, [("alpha", alpha), ("beta", beta)], residual)
+    cols = xs.shape[-1]
+    rows = xs.numel() // cols if cols else 0
+    y = torch.empty_like(xs)
+    h = torch.empty_like(xs) if return_sum else None
+    _cabi.call("cb200_layer_norm", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(beta), _ptr(y), _ptr(h), rows, cols,
+               float(eps), _DTYPES[xs.dtype], flags, _stream(xs))
+    return (y, h) if return_sum else y
+
+
+def _ids_checks(ids: torch.Tensor) -> torch.Tensor:
+    if ids.dim() != 1:
+        raise CandleError(f"unexpected number of dims: expected 1, got {ids.dim()}, shape {_dims(ids)}")
+    if ids.dtype not in _ID_DTYPES:
+        raise CandleError(f"unsupported dtype {ids.dtype} for index-select ids (expected U8, U32 or I64)")
+    return ids if ids.is_contiguous() else ids.contiguous()  # the CPU op honours an ids stride
+
+
+def index_select(t: torch.Tensor, ids: torch.Tensor, dim: int, *, check: bool = True,
+                 status: torch.Tensor | None = None) -> torch.Tensor:
+    """``Tensor::index_select(ids, dim)``.  With ``check`` the call synchronises and raises
+    ``InvalidIndex`` like the CPU backend; pass ``check=False`` and a ``status`` record to defer."""
+    if not t.is_contiguous():
+        raise CandleError("index-select requires contiguous tensors")
+    ids = _ids_checks(ids)
+    _same_device(t, ids)
+    dim = dim if dim >= 0 else dim + t.dim()
+    if not 0 <= dim < t.dim():
+        raise CandleError(f"dim out of range in index-select: {dim} for shape {_dims(t)}")
+    shape = list(t.shape)
+    left = 1
+    for d in shape[:dim]:
+        left *= d
+    right = 1
+    for d in shape[dim + 1:]:
+        right *= d
+    src_dim = shape[dim]
+    shape[dim] = ids.shape[0]
+    out = torch.empty(shape, dtype=t.dtype, device=t.device)
+    st = status if status is not None else (new_status(t.device) if check else None)
+    _cabi.call("cb200_index_select", _ptr(t), _ptr(ids), _ptr(out), left, src_dim, right, ids.shape[0],
+               t.element_size(), _ID_DTYPES[ids.dtype], _ptr(st), _stream(t))
+    if check:
+        raise_for_status(st)
+    return out
+
+
+def embedding_rms_norm(table: torch.Tensor, ids: torch.Tensor, alpha: torch.Tensor, eps: float, *,
+                       return_gathered: bool = False, flags: int = 0, check: bool = True,
+                       status: torch.Tensor | None = None):
+    """``rms_norm(Embedding::forward(ids), alpha, eps)`` in one launch (ids of any shape)."""
+    if table.dim() != 2 or not table.is_contiguous():
+        raise CandleError("index-select requires contiguous tensors")
+    if alpha.dim() != 1 or alpha.shape[0] != table.shape[1]:
+        raise CandleError(f"shape mismatch in rms-norm {list(ids.shape) + [table.shape[1]]} {_dims(alpha)}")
+    _norm_checks("rms-norm", table, [("alpha", alpha)], None)
+    flat = _ids_checks(ids.reshape(-1))
+    _same_device(table, flat, alpha)
+    vocab, hidden = table.shape
+    final = list(ids.shape) + [hidden]
+    y = torch.empty(final, dtype=table.dtype, device=table.device)
+    g = torch.empty(final, dtype=table.dtype, device=table.device) if return_gathered else None
+    st = status if status is not None else (new_status(table.device) if check else None)
+    _cabi.call("cb200_embedding_rms_norm", _ptr(table), _ptr(flat), _ptr(alpha), _ptr(y), _ptr(g), vocab, hidden,
+               flat.shape[0], float(eps), _DTYPES[table.dtype], _ID_DTYPES[flat.dtype], flags, _ptr(st),
+               _stream(table))
+    if check:
+        raise_for_status(st)
+    return (y, g) if return_gathered else y
+
+
+def qembedding_rms_norm(qtensor, ids: torch.Tensor, alpha: torch.Tensor, eps: float, *,
+                        return_gathered: bool = False, flags: int = 0, check: bool = True,
+                        status: torch.Tensor | None = None, vocab_range: tuple[int, int] | None = None,
+                        vocab: int | None = None):
+    """Rows ``ids`` of a Q4_0 / Q8_0 table decoded to ``alpha.dtype`` and RMS-normalised, one launch."""
+    from .quantized import QTensor  # local import: quantized imports this module
+
+    if not isinstance(qtensor, QTensor) or len(qtensor.shape) != 2:
+        raise CandleError("qembedding expects a rank-2 QTensor")
+    if alpha.dtype not in _DTYPES:
+        raise CandleError(f"unsupported dtype for rmsnorm {alpha.dtype}")
+    local_vocab, hidden = qtensor.shape
+    if alpha.dim() != 1 or alpha.shape[0] != hidden or not alpha.is_contiguous():
+        raise CandleError(f"shape mismatch in rms-norm {list(ids.shape) + [hidden]} {_dims(alpha)}")
+    flat = _ids_checks(ids.reshape(-1))
+    _same_device(qtensor.data, flat, alpha)
+    begin, end = vocab_range if vocab_range is not None else (0, local_vocab)
+    total = vocab if vocab is not None else end
+    if end - begin != local_vocab:
+        raise CandleError(f"vocab shard [{begin}, {end}) does not match the table's {local_vocab} rows")
+    final = list(ids.shape) + [hidden]
+    y = torch.empty(final, dtype=alpha.dtype, device=alpha.device)
+    need_g = return_gathered or alpha.dtype == torch.float32 or (flags & (FLAG_FORCE_LANEROW | FLAG_FORCE_GENERIC))
+    g = torch.empty(final, dtype=alpha.dtype, device=alpha.device) if need_g else None
+    st = status if status is not None else (new_status(alpha.device) if check else None)
+    _cabi.call("cb200_qembedding_rms_norm", _ptr(qtensor.data), qtensor.dtype.value, _ptr(flat), _ptr(alpha), _ptr(y),
+               _ptr(g), total, hidden, flat.shape[0], float(eps), _DTYPES[alpha.dtype], _ID_DTYPES[flat.dtype],
+               begin, end, flags, _ptr(st), _stream(alpha))
+    if check:
+        raise_for_status(st)
+    return (y, g) if return_gathered else y

@@ -1,0 +1,184 @@
+/*
+ * candle_b200 -- C ABI of the B200 (sm_100a) normalisation + embedding kernels.
+ *
+ * Each entry point replaces one device-side step of candle's CUDA backend for this path and is
+ * what a Rust `extern "C"` block (in the style of candle-flash-attn/src/ffi.rs:3-51) binds.
+ * Conventions, identical for every function:
+ *   - all tensor pointers are DEVICE pointers to contiguous row-major data whose start offset
+ *     has already been applied by the caller (candle-nn/src/ops.rs:536-543 does the same
+ *     `slice(o1..o2)` before launching); strides are never passed;
+ *   - the CALLER allocates every output (candle: `unsafe { dev.alloc::<T>(el) }`,
+ *     candle-nn/src/ops.rs:557); the library allocates and frees nothing and writes every
+ *     output element of a call that succeeds;
+ *   - work is enqueued on `stream` and the call returns without synchronising;
+ *   - the return value is 0 or a negative CB200_E_* code; cb200_last_error() returns a
+ *     thread-local message for the last failing call of the calling thread;
+ *   - problems only the device can see (an id outside the table, a bounded wait that ran out)
+ *     are recorded in a caller-provided `cb200_status` record in device memory, which the caller
+ *     zeroes before the call and reads after synchronising the stream; kernels never trap.
+ *
+ * Numerics: results equal those of candle's CPU backend on the same inputs -- bit-exact for the
+ * gathers and the Q4_0/Q8_0 decoders, and for the norms bit-exact as well (NaN payloads aside)
+ * unless CB200_FLAG_FAST_SUM is set, because the row sums are accumulated in candle's strictly
+ * sequential f32 order (candle-nn/src/ops.rs:484-490, 709-715) and every rounding step of its
+ * f32 / f16 / bf16 arithmetic is reproduced.
+ */
+#ifndef CANDLE_B200_H_
+#define CANDLE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CB200_VERSION 100
+
+#if defined(__GNUC__)
+#define CB200_API __attribute__((visibility("default")))
+#else
+#define CB200_API
+#endif
+
+/* Element types of tensors (candle DType::F32 / F16 / BF16). */
+#define CB200_DTYPE_F32 0
+#define CB200_DTYPE_F16 1
+#define CB200_DTYPE_BF16 2
+
+/* Index types (candle DType::U8 / U32 / I64, the three IntDType ids index_select accepts,
+ * candle-core/src/cuda_backend/mod.rs:366-372). */
+#define CB200_ID_U8 0
+#define CB200_ID_U32 1
+#define CB200_ID_I64 2
+
+/* Block formats: ggml type ids as in candle-core/src/quantized/mod.rs:152-171. */
+#define CB200_QTYPE_Q4_0 2
+#define CB200_QTYPE_Q8_0 8
+
+/* flags */
+#define CB200_FLAG_FAST_SUM 1 /* tree-order row sums: faster for some shapes, NOT bit-faithful */
+/* Implementation selectors.  Results are identical whichever kernel runs; the tests use these
+ * to cross-check the independent kernels against each other at sizes the CPU oracle is slow at. */
+#define CB200_FLAG_FORCE_LANEROW 0x100 /* lane-per-row sequential kernel even where the register kernel applies */
+#define CB200_FLAG_FORCE_GENERIC 0x200 /* any-shape scalar kernel */
+
+/* return codes */
+#define CB200_OK 0
+#define CB200_E_INVALID_ARGUMENT -1
+#define CB200_E_UNSUPPORTED_DTYPE -2
+#define CB200_E_CUDA -3
+#define CB200_E_NCCL -4
+#define CB200_E_UNSUPPORTED_SHAPE -5
+
+/* cb200_status.code */
+#define CB200_STATUS_OK 0
+#define CB200_STATUS_INVALID_INDEX 1 /* candle: Error::InvalidIndex{index,size,op:"index-select"} */
+#define CB200_STATUS_WAIT_TIMEOUT 2  /* a bounded device-side wait gave up */
+
+typedef struct cb200_status {
+  int32_t code;     /* CB200_STATUS_*; only the first problem of a call is kept */
+  int32_t reserved;
+  int64_t position; /* which id (flattened position) was bad / which row timed out */
+  int64_t index;    /* the offending id value */
+  int64_t size;     /* the dimension size it was checked against */
+} cb200_status;
+
+typedef struct CUstream_st* cb200_stream_t; /* == cudaStream_t */
+
+CB200_API int cb200_version(void);
+CB200_API const char* cb200_last_error(void);
+
+/*
+ * RMS norm over the last dimension, optionally fused with the residual add that precedes it.
+ *   h = residual ? T(x + residual) : x          (the rounded sum candle's `Tensor::add` yields,
+ *                                                candle-core/src/op.rs:330)
+ *   y = h / T(sqrt(mean(h^2) + eps)) * alpha     (candle-nn/src/ops.rs:484-495)
+ * Replaces the CUDA launch in RmsNorm::cuda_fwd (candle-nn/src/ops.rs:510-580, kernel
+ * `rmsnorm_{f32,f16,bf16}` of candle-kernels/src/reduce.cu:135-175) and, when `residual` is
+ * given, also the `badd_*` launch before it (candle-kernels/src/binary.cu:5).
+ * x, residual, y, sum_out: [rows, cols]; alpha: [cols]; residual and sum_out may be NULL;
+ * sum_out, when given, receives h (what the model keeps as the next residual stream).
+ * y may alias x or residual; sum_out may alias x or residual.
+ */
+CB200_API int cb200_rms_norm(const void* x, const void* residual, const void* alpha, void* y, void* sum_out,
+                   int64_t rows, int32_t cols, float eps, int dtype, int flags, cb200_stream_t stream);
+
+/*
+ * Layer norm with affine weight and bias, optionally fused with the preceding residual add.
+ *   y = T((h - mean) * (1/sqrt(var + eps)) * gamma + beta), all in f32 with one final rounding
+ * (candle-nn/src/ops.rs:709-726).  Replaces LayerNorm::cuda_fwd (candle-nn/src/ops.rs:743-822,
+ * kernel `layernorm_*` of candle-kernels/src/reduce.cu:72-131).
+ */
+CB200_API int cb200_layer_norm(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
+                     void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags,
+                     cb200_stream_t stream);
+
+/*
+ * index_select along one dimension of a contiguous tensor viewed as [left, src_dim, right]:
+ *   out[l, i, :] = src[l, ids[i], :]   for i < n_ids
+ * Replaces IndexSelect::f + BackendStorage::index_select of the CUDA backend
+ * (candle-core/src/cuda_backend/mod.rs:352-410, 1622-1626; kernel `is_{u8,u32,i64}_{T}` of
+ * candle-kernels/src/indexing.cu:6-44).  `elem_size` is the element size in bytes (any dtype).
+ * Unlike the reference kernel every id is bounds-checked; a bad id is reported through `status`
+ * (as the CPU backend does, candle-core/src/cpu_backend/mod.rs:539-546) and its output slice is
+ * left unwritten.
+ */
+CB200_API int cb200_index_select(const void* src, const void* ids, void* out, int64_t left, int64_t src_dim,
+                       int64_t right, int64_t n_ids, int32_t elem_size, int id_dtype, cb200_status* status,
+                       cb200_stream_t stream);
+
+/*
+ * Embedding::forward (candle-nn/src/embedding.rs:29-36): out[i, :] = table[ids[i], :], table
+ * [vocab, hidden].  Equivalent to cb200_index_select with left = 1.
+ */
+CB200_API int cb200_embedding(const void* table, const void* ids, void* out, int64_t vocab, int32_t hidden,
+                    int64_t n_ids, int dtype, int id_dtype, cb200_status* status, cb200_stream_t stream);
+
+/*
+ * Whole-buffer block decode: k elements (k % 32 == 0) of Q4_0 / Q8_0 blocks -> out_dtype.
+ * Replaces QCudaStorage::dequantize / dequantize_f16 (candle-core/src/quantized/cuda.rs:69-124,
+ * 391-414; kernels `dequantize_block_q{4,8}_0_{f32,f16}` of candle-kernels/src/quantized.cu:
+ * 779-805, 1068-1091) and, for bf16 / f16 output, the cast kernel that follows it
+ * (candle-kernels/src/cast.cu:4-25).  Values equal GgmlType::to_float on the CPU
+ * (candle-core/src/quantized/k_quants.rs:163-183, 568-584) including the sign of zero.
+ */
+CB200_API int cb200_dequantize(const void* blocks, int qtype, void* out, int64_t k, int out_dtype,
+                     cb200_stream_t stream);
+
+/*
+ * Row lookup straight out of a block-quantised [vocab, hidden] table (hidden % 32 == 0):
+ *   out[i, :] = T(to_float(qtable[ids[i], :]))
+ * i.e. what QTensor::dequantize + to_dtype + Embedding::forward compute
+ * (candle-transformers/src/models/quantized_llama.rs:378-379, candle-nn/src/embedding.rs:29-36)
+ * without materialising the decoded table.  The reference has no such device entry point.
+ * Vocab sharding: `qtable` holds rows [vocab_begin, vocab_end) of the full table; ids inside that
+ * range are decoded, ids outside it (but < vocab) produce rows of -0.0, the value that keeps a
+ * sum over shards bit-exact; pass 0 and `vocab` for an unsharded table.  ids >= vocab are reported
+ * through `status`.
+ */
+CB200_API int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, int64_t vocab,
+                     int32_t hidden, int64_t n_ids, int out_dtype, int id_dtype, int64_t vocab_begin,
+                     int64_t vocab_end, cb200_status* status, cb200_stream_t stream);
+
+/*
+ * Fused Embedding::forward -> rms_norm: y[i, :] = rms_norm(table[ids[i], :], alpha, eps); when
+ * `gathered` is not NULL it also receives the gathered rows (the residual stream).  Replaces an
+ * `is_*` launch followed by a `rmsnorm_*` launch (candle-transformers/src/models/llama.rs:507
+ * followed by :446).
+ */
+CB200_API int cb200_embedding_rms_norm(const void* table, const void* ids, const void* alpha, void* y, void* gathered,
+                             int64_t vocab, int32_t hidden, int64_t n_ids, float eps, int dtype,
+                             int id_dtype, int flags, cb200_status* status, cb200_stream_t stream);
+
+/* Fused cb200_qembedding -> rms_norm in `out_dtype` (same sharding arguments). */
+CB200_API int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, const void* alpha, void* y,
+                              void* gathered, int64_t vocab, int32_t hidden, int64_t n_ids, float eps,
+                              int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
+                              int flags, cb200_status* status, cb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CANDLE_B200_H_ */

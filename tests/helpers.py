@@ -1,0 +1,61 @@
+"""Shared helpers of the parity tests: torch <-> oracle array conversion and seeded inputs."""
+import numpy as np
+import torch
+
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+ID_NP = {"u8": np.uint8, "u32": np.uint32, "i64": np.int64}
+ID_TORCH = {"u8": torch.uint8, "u32": torch.uint32, "i64": torch.int64}
+
+
+def to_oracle(t: torch.Tensor) -> np.ndarray:
+    """torch tensor (any device) -> the array layout the oracle takes (uint16 bits for f16/bf16)."""
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.float32:
+        return t.numpy()
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.view(torch.int16).numpy().view(np.uint16)
+    if t.dtype == torch.uint32:
+        return t.view(torch.int32).numpy().view(np.uint32)
+    return t.numpy()
+
+
+def from_oracle(a: np.ndarray, dtype: str, device="cuda") -> torch.Tensor:
+    a = np.ascontiguousarray(a)
+    if dtype == "f32":
+        return torch.from_numpy(a).to(device)
+    return torch.from_numpy(a.view(np.int16)).view(TORCH_DT[dtype]).to(device)
+
+
+def ids_tensor(ids: np.ndarray, device="cuda") -> torch.Tensor:
+    ids = np.ascontiguousarray(ids)
+    if ids.dtype == np.uint32:
+        return torch.from_numpy(ids.view(np.int32)).view(torch.uint32).to(device)
+    return torch.from_numpy(ids).to(device)
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    """Bit patterns for exact comparison."""
+    a = to_oracle(t)
+    return a.view(np.uint32) if a.dtype == np.float32 else a
+
+
+def randn(rng, shape, dtype: str, mean=0.0, std=1.0) -> np.ndarray:
+    """Seeded N(mean, std) rounded to `dtype`, in oracle layout."""
+    import oracle
+
+    x = (mean + std * rng.standard_normal(shape)).astype(np.float32)
+    return x if dtype == "f32" else oracle.cast_from_f32(x, dtype)
+
+
+def make_qtable(rng, qtype: str, vocab: int, hidden: int) -> np.ndarray:
+    """Raw block bytes [vocab, hidden/32*block_bytes] with the value distributions of the
+    benchmark configs: f16 scale |N(0,0.01)|, int8 quants uniform[-127,127] (Q8_0) or 4-bit
+    quants uniform[0,15] (Q4_0)."""
+    nb = hidden // 32
+    d = np.abs(rng.standard_normal((vocab, nb)) * 0.01).astype(np.float16)
+    if qtype == "q8_0":
+        qs = rng.integers(-127, 128, size=(vocab, nb, 32), dtype=np.int16).astype(np.int8).view(np.uint8)
+    else:
+        qs = rng.integers(0, 256, size=(vocab, nb, 16), dtype=np.int16).astype(np.uint8)
+    blocks = np.concatenate([d.view(np.uint8).reshape(vocab, nb, 2), qs], axis=2)
+    return np.ascontiguousarray(blocks.reshape(vocab, -1))

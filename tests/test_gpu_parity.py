@@ -1,0 +1,361 @@
+"""GPU parity: every entry point of the C ABI (through the candle-style Python front ends) against
+the CPU oracle on the same seeded inputs.  Norms are compared BIT-EXACTLY -- stricter than the
+stated tolerances (max-abs 1e-5 for f32, 1e-2 for f16/bf16), which are asserted as well."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import round4
+from helpers import ID_NP, TORCH_DT, bits, from_oracle, ids_tensor, make_qtable, randn, to_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"f32": 1e-5, "f16": 1e-2, "bf16": 1e-2}
+
+
+@pytest.fixture(scope="module")
+def cb():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import candle_b200
+
+    return candle_b200
+
+
+def assert_norm_equal(got: torch.Tensor, want: np.ndarray, dtype: str):
+    g = to_oracle(got)
+    gf, wf = oracle.cast_to_f32(g, dtype), oracle.cast_to_f32(want, dtype)
+    assert np.abs(gf - wf).max() <= TOL[dtype], "outside the stated tolerance"
+    same = bits(got) == (want.view(np.uint32) if dtype == "f32" else want)
+    assert same.all(), f"{(~same).sum()} of {same.size} elements differ in bits"
+
+
+# ------------------------------------------------------------------------------------------------
+# candle's own known-answer tests, run on the device
+# ------------------------------------------------------------------------------------------------
+def test_kat_rms_norm(cb, kats):
+    k = kats["rms_norm"]
+    x = torch.tensor(k["x"], dtype=torch.float32, device="cuda")
+    a = torch.tensor(k["alpha"], dtype=torch.float32, device="cuda")
+    y = cb.rms_norm(x, a, k["eps"])
+    assert np.array_equal(round4(y.cpu().numpy()), np.asarray(k["expected_round4"], np.float32))
+
+
+def test_kat_layer_norm(cb, kats):
+    k = kats["layer_norm"]
+    x = torch.tensor(k["x"], dtype=torch.float32, device="cuda")
+    a = torch.tensor(k["alpha"], dtype=torch.float32, device="cuda")
+    b = torch.tensor(k["beta"], dtype=torch.float32, device="cuda")
+    y = cb.layer_norm(x, a, b, k["eps"])
+    assert np.array_equal(round4(y.cpu().numpy()), np.asarray(k["expected_round4"], np.float32))
+
+
+def test_kat_layer_norm_module_and_doctest(cb, kats):
+    k = kats["layer_norm_module"]
+    for case in k["cases"]:
+        x = torch.tensor(case["x"], dtype=torch.float32, device="cuda")
+        h = x.shape[-1]
+        ln = cb.LayerNorm.new(torch.full((h,), k["w"][0], device="cuda"), torch.full((h,), k["b"][0], device="cuda"), k["eps"])
+        y = ln.forward(x).cpu().numpy()
+        if case.get("exact"):
+            assert np.array_equal(y.reshape(-1), np.asarray(case["expected"], np.float32).reshape(-1))
+        else:
+            assert np.array_equal(round4(y), np.asarray(case["expected_round4"], np.float32))
+    d = kats["layer_norm_doctest"]
+    ln = cb.LayerNorm.new(torch.tensor(d["w"], dtype=torch.float32, device="cuda"),
+                          torch.tensor(d["b"], dtype=torch.float32, device="cuda"), d["eps"])
+    y = ln.forward(torch.tensor(d["x"], dtype=torch.float32, device="cuda")).cpu().numpy()
+    assert np.array_equal(round4(y), np.asarray(d["expected_round4"], np.float32))
+
+
+@pytest.mark.parametrize("name", ["rms_norml", "layer_norml"])
+def test_kat_norml_fused_vs_slow(cb, kats, name):
+    k = kats[name]
+    x = torch.from_numpy(np.random.default_rng(299792458).random(k["shape"], dtype=np.float32)).cuda()
+    n = x.shape[-1]
+    ones, zeros = torch.ones(n, device="cuda"), torch.zeros(n, device="cuda")
+    if name == "rms_norml":
+        y = cb.rms_norm(x, ones, k["eps"])
+        slow = x / torch.sqrt((x * x).sum(-1, keepdim=True) / n + k["eps"])
+    else:
+        y = cb.layer_norm(x, ones, zeros, k["eps"])
+        xc = x - x.sum(-1, keepdim=True) / n
+        slow = xc / torch.sqrt((xc * xc).sum(-1, keepdim=True) / n + k["eps"])
+    assert (y - slow).abs().max().item() < k["max_abs_fused_vs_slow"]
+
+
+def test_kat_embeddings_and_index_select(cb, kats):
+    k = kats["embeddings"]
+    t = torch.tensor(k["table"], dtype=torch.float32, device="cuda")
+    for idt in ("u32", "i64"):
+        ids = ids_tensor(np.asarray(k["ids"], ID_NP[idt]))
+        want = np.asarray(k["expected"], np.float32)
+        assert np.array_equal(cb.Embedding(t, 2).forward(ids).cpu().numpy(), want)
+        assert np.array_equal(cb.index_select(t, ids, 0).cpu().numpy(), want)
+    k = kats["index_select"]
+    t = torch.arange(12, dtype=torch.float32, device="cuda").reshape(4, 3)
+    for idt in k["id_dtypes"]:
+        ids = ids_tensor(np.asarray(k["ids"], ID_NP[idt]))
+        assert np.array_equal(cb.index_select(t, ids, 1).cpu().numpy(), np.asarray(k["expected_dim1"], np.float32))
+        assert np.array_equal(cb.index_select(t, ids, 0).cpu().numpy(), np.asarray(k["expected_dim0"], np.float32))
+        rep = ids_tensor(np.asarray(k["ids_repeated"], ID_NP[idt]))
+        assert np.array_equal(cb.index_select(t, rep, 0).cpu().numpy(), np.asarray(k["expected_repeated_dim0"], np.float32))
+        ids2 = ids_tensor(np.asarray(k["ids2"], ID_NP[idt]))
+        t2 = torch.tensor(k["table2"], dtype=torch.float32, device="cuda")
+        assert np.array_equal(cb.index_select(t2, ids2, 1).cpu().numpy(), np.asarray(k["expected2_dim1"], np.float32))
+
+
+def test_kat_quantize_q4_0_dequantize(cb, kats):
+    k = kats["quantize_q4_0"]
+    blocks = oracle.quantize(np.arange(128, dtype=np.float32), "q4_0")  # the CPU writer of the format
+    q = cb.QTensor.from_raw(torch.from_numpy(blocks), cb.GgmlDType.Q4_0, (128,), device="cuda")
+    want = np.asarray([float(v) for v in k["dequantized"]], np.float32)
+    got = q.dequantize()
+    assert np.array_equal(bits(got), want.view(np.uint32))  # includes the two -0.0
+    f16 = q.dequantize_f16()
+    assert np.array_equal(bits(f16), bits(got.to(torch.float16)))  # diff == 0 in candle's test
+
+
+# ------------------------------------------------------------------------------------------------
+# norms against the oracle
+# ------------------------------------------------------------------------------------------------
+NORM_SHAPES = [(1, 8), (7, 3), (3, 200), (33, 64), (5, 768), (40, 1024), (64, 4096), (17, 8192), (2, 2, 16384), (3, 32768)]
+IMPLS = {"default": 0, "lanerow": 0x100, "generic": 0x200}
+
+
+@pytest.mark.parametrize("impl", list(IMPLS))
+@pytest.mark.parametrize("residual", [False, True])
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_rms_norm_matches_oracle(cb, dtype, residual, impl):
+    rng = np.random.default_rng(1000 + sum(map(ord, dtype)) + int(residual))
+    for shape in NORM_SHAPES:
+        if impl == "generic" and shape[-1] > 8192:
+            continue
+        x = randn(rng, shape, dtype)
+        a = randn(rng, shape[-1:], dtype, 1.0, 0.1)
+        r = randn(rng, shape, dtype) if residual else None
+        h = oracle.add(x, r, dtype) if residual else x
+        want = oracle.rms_norm(h, a, 1e-5, dtype)
+        out = cb.rms_norm(from_oracle(x, dtype), from_oracle(a, dtype), 1e-5,
+                          residual=from_oracle(r, dtype) if residual else None, return_sum=residual,
+                          flags=IMPLS[impl])
+        if residual:
+            y, hs = out
+            assert np.array_equal(to_oracle(hs), h), f"sum_out differs for {shape}"
+        else:
+            y = out
+        assert_norm_equal(y, want, dtype)
+
+
+@pytest.mark.parametrize("impl", ["default", "generic"])
+@pytest.mark.parametrize("residual", [False, True])
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_layer_norm_matches_oracle(cb, dtype, residual, impl):
+    rng = np.random.default_rng(2000 + sum(map(ord, dtype)) + int(residual))
+    for shape in NORM_SHAPES:
+        if impl == "generic" and shape[-1] > 8192:
+            continue
+        x = randn(rng, shape, dtype)
+        g = randn(rng, shape[-1:], dtype, 1.0, 0.1)
+        b = randn(rng, shape[-1:], dtype, 0.0, 0.1)
+        r = randn(rng, shape, dtype) if residual else None
+        h = oracle.add(x, r, dtype) if residual else x
+        want = oracle.layer_norm(h, g, b, 1e-12, dtype)
+        out = cb.layer_norm(from_oracle(x, dtype), from_oracle(g, dtype), from_oracle(b, dtype), 1e-12,
+                            residual=from_oracle(r, dtype) if residual else None, return_sum=residual,
+                            flags=IMPLS[impl])
+        if residual:
+            y, hs = out
+            assert np.array_equal(to_oracle(hs), h)
+        else:
+            y = out
+        assert_norm_equal(y, want, dtype)
+
+
+def test_rms_norm_many_rows_exercises_the_replay_path(cb):
+    # 8192 rows of 8192 bf16 columns: a few percent of the rows cannot be decided by the interval
+    # test and are replayed sequentially; the result must still be bit-equal everywhere.
+    rng = np.random.default_rng(5)
+    x, r = randn(rng, (8192, 8192), "bf16"), randn(rng, (8192, 8192), "bf16")
+    a = randn(rng, (8192,), "bf16", 1.0, 0.1)
+    want = oracle.rms_norm(oracle.add(x, r, "bf16", threads=0), a, 1e-5, "bf16")
+    xt, rt, at = from_oracle(x, "bf16"), from_oracle(r, "bf16"), from_oracle(a, "bf16")
+    y = cb.rms_norm(xt, at, 1e-5, residual=rt)
+    assert_norm_equal(y, want, "bf16")
+    # the independent lane-per-row kernel agrees bit for bit
+    y2 = cb.rms_norm(xt, at, 1e-5, residual=rt, flags=cb.FLAG_FORCE_LANEROW)
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+    # the tree-order variant stays within the stated tolerance on all but a handful of rows and
+    # differs from the exact result only where bf16(m) flipped
+    y3 = cb.rms_norm(xt, at, 1e-5, residual=rt, flags=cb.FLAG_FAST_SUM)
+    rows_diff = (y3.view(torch.int16) != y.view(torch.int16)).any(dim=1).sum().item()
+    assert rows_diff <= 64
+
+
+def test_norm_special_values_and_aliasing(cb):
+    for dtype in ("f32", "bf16", "f16"):
+        x = np.zeros((4, 256), np.float32)
+        x[1, :] = 1.0
+        x[2, 5] = -0.0
+        x[3, ::2] = 65504.0 if dtype == "f16" else 3e18
+        xo = x if dtype == "f32" else oracle.cast_from_f32(x, dtype)
+        a = randn(np.random.default_rng(0), (256,), dtype, 1.0, 0.1)
+        want = oracle.rms_norm(xo, a, 1e-5, dtype)
+        xt = from_oracle(xo, dtype)
+        y = cb.rms_norm(xt, from_oracle(a, dtype), 1e-5)
+        assert_norm_equal(y, want, dtype)
+        # in place: y aliases x
+        from candle_b200 import _cabi
+        from candle_b200.ops import _DTYPES, _stream
+        at = from_oracle(a, dtype)
+        _cabi.call("cb200_rms_norm", xt.data_ptr(), None, at.data_ptr(), xt.data_ptr(), None, 4, 256, 1e-5,
+                   _DTYPES[xt.dtype], 0, _stream(xt))
+        assert_norm_equal(xt, want, dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+# gathers
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("idt", ["u8", "u32", "i64"])
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_embedding_matches_oracle(cb, dtype, idt):
+    rng = np.random.default_rng(11)
+    for vocab, hidden, shape in [(200, 4096, (3, 50)), (255, 6, (40,)), (97, 520, (2, 3, 4)), (130, 16384, (9,)), (50, 24576, (5,))]:
+        table = randn(rng, (vocab, hidden), dtype, 0.0, 0.02)
+        ids = rng.integers(0, min(vocab, 256 if idt == "u8" else vocab), size=shape).astype(ID_NP[idt])
+        want = oracle.embedding(table, ids)
+        emb = cb.Embedding(from_oracle(table, dtype), hidden)
+        got = emb.forward(ids_tensor(ids))
+        assert got.shape == tuple(shape) + (hidden,)
+        assert np.array_equal(to_oracle(got), want)
+
+
+def test_embedding_edge_cases(cb):
+    t = torch.arange(40, dtype=torch.float32, device="cuda").reshape(10, 4)
+    empty = cb.index_select(t, torch.zeros(0, dtype=torch.int64, device="cuda"), 0)
+    assert empty.shape == (0, 4)
+    with pytest.raises(cb.InvalidIndex) as e:
+        cb.index_select(t, torch.tensor([1, 10, 3], dtype=torch.int64, device="cuda"), 0)
+    assert (e.value.index, e.value.size, e.value.op) == (10, 10, "index-select")
+    with pytest.raises(cb.InvalidIndex):
+        cb.index_select(t, torch.tensor([-1], dtype=torch.int64, device="cuda"), 0)
+    big = torch.randn(64, 4096, device="cuda")  # bulk-copy path
+    with pytest.raises(cb.InvalidIndex) as e:
+        cb.index_select(big, torch.tensor([5, 64], dtype=torch.int64, device="cuda"), 0)
+    assert e.value.position == 1
+    strided = torch.tensor([3, 9, 1, 9, 0, 9], dtype=torch.int64, device="cuda")[::2]
+    assert torch.equal(cb.index_select(t, strided, 0), t[[3, 1, 0]])
+    with pytest.raises(cb.CandleError):
+        cb.index_select(t.t(), strided, 0)  # RequiresContiguous
+    with pytest.raises(cb.CandleError):
+        cb.index_select(t, torch.zeros(2, 2, dtype=torch.int64, device="cuda"), 0)  # ids rank
+    # index_select on dim 1 of a 3-d tensor with long rows (left > 1 through the bulk path)
+    t3 = torch.randn(3, 7, 1024, device="cuda")
+    ids = torch.tensor([6, 0, 6, 2], dtype=torch.int64, device="cuda")
+    assert torch.equal(cb.index_select(t3, ids, 1), t3[:, [6, 0, 6, 2], :])
+
+
+@pytest.mark.parametrize("out_dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("qtype", ["q8_0", "q4_0"])
+def test_qembedding_matches_oracle(cb, qtype, out_dtype):
+    rng = np.random.default_rng(13)
+    gq = cb.GgmlDType.Q8_0 if qtype == "q8_0" else cb.GgmlDType.Q4_0
+    for vocab, hidden, shape in [(300, 4096, (4, 64)), (64, 256, (33,)), (50, 96, (20,)), (40, 8192, (2, 8))]:
+        qt = make_qtable(rng, qtype, vocab, hidden)
+        qt[3, :2] = np.asarray([0, 0x80], np.uint8)  # d = -0.0 in one block: exercises the sign of zero
+        ids = rng.integers(0, vocab, size=shape).astype(np.int64)
+        ids.reshape(-1)[0] = 3
+        want = oracle.qembedding(qt, qtype, ids, out_dtype)
+        q = cb.QTensor.from_raw(torch.from_numpy(qt), gq, (vocab, hidden), device="cuda")
+        got = q.embedding(ids_tensor(ids), TORCH_DT[out_dtype])
+        assert np.array_equal(bits(got), want.view(np.uint32) if out_dtype == "f32" else want)
+        # whole-table decode agrees with the CPU decoder too
+        full = q.dequantize(TORCH_DT[out_dtype])
+        want_full = oracle.cast_from_f32(oracle.dequantize(qt, qtype), out_dtype)
+        assert np.array_equal(bits(full), want_full.view(np.uint32) if out_dtype == "f32" else want_full)
+    with pytest.raises(cb.InvalidIndex):
+        q.embedding(torch.tensor([vocab], dtype=torch.int64, device="cuda"))
+
+
+@pytest.mark.parametrize("qtype", ["q8_0", "q4_0"])
+def test_vocab_sharded_partials_sum_to_the_unsharded_lookup(cb, qtype):
+    # Each shard decodes the ids it owns and writes -0.0 elsewhere; summing the partials in bf16
+    # (what the all-reduce does) must reproduce the unsharded lookup bit for bit, -0.0 included.
+    rng = np.random.default_rng(17)
+    gq = cb.GgmlDType.Q8_0 if qtype == "q8_0" else cb.GgmlDType.Q4_0
+    vocab, hidden, n = 512, 1024, 300
+    qt = make_qtable(rng, qtype, vocab, hidden)
+    qt[:, :2] = 0  # first block of every row has d = +0: a source of +-0.0 values
+    ids = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+    want = oracle.qembedding(qt, qtype, ids, "bf16")
+    for shards in (2, 4, 8):
+        per = vocab // shards
+        total = None
+        for s in range(shards):
+            q = cb.QTensor.from_raw(torch.from_numpy(qt[s * per:(s + 1) * per]), gq, (per, hidden), device="cuda")
+            part = q.embedding(ids_tensor(ids), torch.bfloat16, vocab_range=(s * per, (s + 1) * per), vocab=vocab)
+            total = part if total is None else total + part
+        assert np.array_equal(to_oracle(total), want)
+
+
+# ------------------------------------------------------------------------------------------------
+# fused lookups + norm
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_embedding_rms_norm_matches_oracle(cb, dtype):
+    rng = np.random.default_rng(19)
+    for vocab, hidden, shape in [(500, 4096, (8, 64)), (100, 768, (77,)), (64, 100, (10,)), (32, 8192, (40,))]:
+        table = randn(rng, (vocab, hidden), dtype, 0.0, 0.02)
+        a = randn(rng, (hidden,), dtype, 1.0, 0.1)
+        ids = rng.integers(0, vocab, size=shape).astype(np.uint32)
+        e = oracle.embedding(table, ids)
+        want = oracle.rms_norm(e, a, 1e-5, dtype)
+        y, g = cb.embedding_rms_norm(from_oracle(table, dtype), ids_tensor(ids), from_oracle(a, dtype), 1e-5,
+                                     return_gathered=True)
+        assert np.array_equal(to_oracle(g), e)
+        assert_norm_equal(y, want, dtype)
+    with pytest.raises(cb.InvalidIndex):
+        cb.embedding_rms_norm(from_oracle(table, dtype), torch.tensor([vocab], dtype=torch.int64, device="cuda"),
+                              from_oracle(a, dtype), 1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("qtype", ["q8_0", "q4_0"])
+def test_qembedding_rms_norm_matches_oracle(cb, qtype, dtype):
+    rng = np.random.default_rng(23)
+    gq = cb.GgmlDType.Q8_0 if qtype == "q8_0" else cb.GgmlDType.Q4_0
+    for vocab, hidden, shape in [(400, 4096, (6, 100)), (64, 256, (50,)), (30, 96, (12,)), (60, 8192, (3, 40))]:
+        qt = make_qtable(rng, qtype, vocab, hidden)
+        a = randn(rng, (hidden,), dtype, 1.0, 0.1)
+        ids = rng.integers(0, vocab, size=shape).astype(np.uint32)
+        e = oracle.qembedding(qt, qtype, ids, dtype)
+        want = oracle.rms_norm(e, a, 1e-5, dtype)
+        q = cb.QTensor.from_raw(torch.from_numpy(qt), gq, (vocab, hidden), device="cuda")
+        y, g = cb.qembedding_rms_norm(q, ids_tensor(ids), from_oracle(a, dtype), 1e-5, return_gathered=True)
+        assert np.array_equal(to_oracle(g), e)
+        assert_norm_equal(y, want, dtype)
+        y2 = cb.qembedding_rms_norm(q, ids_tensor(ids), from_oracle(a, dtype), 1e-5)
+        assert torch.equal(y2.view(torch.int16 if dtype != "f32" else torch.int32),
+                           y.view(torch.int16 if dtype != "f32" else torch.int32))
+
+
+# ------------------------------------------------------------------------------------------------
+# front-end error behaviour (candle's messages)
+# ------------------------------------------------------------------------------------------------
+def test_front_end_errors(cb):
+    x = torch.randn(4, 8, device="cuda")
+    with pytest.raises(cb.CandleError, match="shape mismatch in rms-norm"):
+        cb.rms_norm(x, torch.ones(7, device="cuda"), 1e-5)
+    with pytest.raises(cb.CandleError, match="shape mismatch in layer-norm"):
+        cb.layer_norm(x, torch.ones(8, device="cuda"), torch.ones(7, device="cuda"), 1e-5)
+    with pytest.raises(cb.CandleError, match="input has to be contiguous"):
+        cb.rms_norm(x.t(), torch.ones(4, device="cuda"), 1e-5)
+    with pytest.raises(cb.CandleError, match="alpha has to be contiguous"):
+        cb.rms_norm(x, torch.ones(16, device="cuda")[::2], 1e-5)
+    with pytest.raises(cb.CandleError, match="unsupported dtype for rmsnorm"):
+        cb.rms_norm(x.double(), torch.ones(8, device="cuda", dtype=torch.float64), 1e-5)
+    with pytest.raises(cb.CandleError, match="unsupported dtype for rmsnorm"):
+        cb.rms_norm(x, torch.ones(8, device="cuda", dtype=torch.float16), 1e-5)
+    y = cb.rms_norm(torch.zeros(0, 8, device="cuda"), torch.ones(8, device="cuda"), 1e-5)
+    assert y.shape == (0, 8)
