@@ -56,7 +56,7 @@ def test_kat_layer_norm_module_and_doctest(cb, kats):
     for case in k["cases"]:
         x = torch.tensor(case["x"], dtype=torch.float32, device="cuda")
         h = x.shape[-1]
-        ln = cb.LayerNorm.new(torch.full((h,), k["w"][0], device="cuda"), torch.full((h,), k["b"][0], device="cuda"), k["eps"])
+        ln = cb.LayerNorm.new(torch.full((h,), float(k["w"][0]), device="cuda"), torch.full((h,), float(k["b"][0]), device="cuda"), k["eps"])
         y = ln.forward(x).cpu().numpy()
         if case.get("exact"):
             assert np.array_equal(y.reshape(-1), np.asarray(case["expected"], np.float32).reshape(-1))
