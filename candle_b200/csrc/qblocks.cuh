@@ -30,32 +30,45 @@ __host__ __device__ inline int qblock_bytes(int qtype) {
   return qtype == CB200_QTYPE_Q4_0 ? 18 : (qtype == CB200_QTYPE_Q8_0 ? 34 : 0);
 }
 
+// Small integer held in byte `k` of `w` -> float, without the slow int-to-float conversion: the
+// byte is spliced into the low mantissa bits of 2^23 (0x4B000000) and 2^23 + bias subtracted,
+// which is exact.  For a signed byte the caller flips bit 7 first and passes bias = 128.
+template <int K>
+__device__ __forceinline__ float byte_to_float(uint32_t w, float magic_plus_bias) {
+  return __fadd_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650 | K)), -magic_plus_bias);
+}
+
 // Decodes elements [8v, 8v+8) of a row of blocks starting at `row` (shared or global memory).
 template <int QT>
 __device__ __forceinline__ void decode8(const unsigned char* row, int v, float (&out)[8]) {
   const int blk = v >> 2, sub = v & 3;
   const unsigned char* b = row + blk * QBlock<QT>::kBytes;
   const float d = __half2float(*reinterpret_cast<const __half*>(b));
-  if (QT == CB200_QTYPE_Q8_0) {
-    const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + sub * 8);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint16_t w = q[i];
-      out[2 * i] = __fmul_rn(static_cast<float>(static_cast<int8_t>(w & 0xFF)), d);
-      out[2 * i + 1] = __fmul_rn(static_cast<float>(static_cast<int8_t>(w >> 8)), d);
-    }
-  } else {
-    const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + (sub & 1) * 8);
-    const int shift = (sub >> 1) * 4;  // elements 0..15 are low nibbles, 16..31 high nibbles
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint16_t w = q[i];
-      int n0 = ((w & 0xFF) >> shift) & 0xF;
-      int n1 = ((w >> 8) >> shift) & 0xF;
-      out[2 * i] = __fmul_rn(static_cast<float>(n0 - 8), d);
-      out[2 * i + 1] = __fmul_rn(static_cast<float>(n1 - 8), d);
-    }
+  uint32_t w0, w1;  // the eight source bytes
+  {
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + (QT == CB200_QTYPE_Q8_0 ? sub : (sub & 1)) * 8);
+    w0 = static_cast<uint32_t>(q[0]) | (static_cast<uint32_t>(q[1]) << 16);
+    w1 = static_cast<uint32_t>(q[2]) | (static_cast<uint32_t>(q[3]) << 16);
   }
+  float bias;
+  if (QT == CB200_QTYPE_Q8_0) {
+    w0 ^= 0x80808080u;  // signed byte q -> unsigned q + 128
+    w1 ^= 0x80808080u;
+    bias = 8388608.0f + 128.0f;
+  } else {
+    const int shift = (sub >> 1) * 4;  // elements 0..15 are low nibbles, 16..31 high nibbles
+    w0 = (w0 >> shift) & 0x0F0F0F0Fu;
+    w1 = (w1 >> shift) & 0x0F0F0F0Fu;
+    bias = 8388608.0f + 8.0f;
+  }
+  out[0] = __fmul_rn(byte_to_float<0>(w0, bias), d);
+  out[1] = __fmul_rn(byte_to_float<1>(w0, bias), d);
+  out[2] = __fmul_rn(byte_to_float<2>(w0, bias), d);
+  out[3] = __fmul_rn(byte_to_float<3>(w0, bias), d);
+  out[4] = __fmul_rn(byte_to_float<0>(w1, bias), d);
+  out[5] = __fmul_rn(byte_to_float<1>(w1, bias), d);
+  out[6] = __fmul_rn(byte_to_float<2>(w1, bias), d);
+  out[7] = __fmul_rn(byte_to_float<3>(w1, bias), d);
 }
 
 // Same, rounded to a 16-bit type and packed into one 16-byte vector.

@@ -7,8 +7,14 @@
 
 namespace cb200 {
 
-template <int DT, int VPT>
-__global__ void __launch_bounds__(512) rms_rowreg_kernel(const RmsRowRegArgs a) {
+// Registers are capped so that 1536 threads (1024 for the 8-vector variant) stay resident per SM.
+template <int VPT, int BT>
+constexpr int rowreg_min_blocks() {
+  return (VPT == 8 ? 1024 : 1536) / BT;
+}
+
+template <int DT, int VPT, int BT>
+__global__ void __launch_bounds__(BT, rowreg_min_blocks<VPT, BT>()) rms_rowreg_kernel(const RmsRowRegArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
   RowRegSmem sm(smem_raw, rpc, a.V, ty);
@@ -51,7 +57,7 @@ __global__ void __launch_bounds__(512) rms_rowreg_kernel(const RmsRowRegArgs a) 
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     int v = k * tpr + tx;
-    if (v < a.V) accumulate_vec<DT>(h[k], v * 8, a.n, lsum, lw);
+    if (v < a.V) accumulate_vec<DT>(h[k], v, a.n, lsum, lw);
   }
   if (live && a.sum_out != nullptr) {
     uint4* so = a.sum_out + row * a.V;
@@ -73,8 +79,8 @@ __global__ void __launch_bounds__(512) rms_rowreg_kernel(const RmsRowRegArgs a) 
 
 constexpr int kQStages = 2;
 
-template <int QT, int DT, int VPT>
-__global__ void __launch_bounds__(512) qrms_rowreg_kernel(const QRmsArgs a) {
+template <int QT, int DT, int VPT, int BT>
+__global__ void __launch_bounds__(BT, (VPT >= 4 ? 1024 : 1536) / BT) qrms_rowreg_kernel(const QRmsArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, tpr = blockDim.x;
   RowRegSmem sm(smem_raw, 1, a.V, 0);
@@ -82,10 +88,12 @@ __global__ void __launch_bounds__(512) qrms_rowreg_kernel(const QRmsArgs a) {
   const int stage_bytes = (a.row_bytes + 15) & ~15;
   unsigned char* stage0 = smem_raw + core_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage0 + kQStages * stage_bytes);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kQStages);
 
   if (tx == 0) {
     for (int s = 0; s < kQStages; ++s) mbar_init(&bars[s], 1);
     mbar_init_fence();
+    *abort_flag = 0;
   }
   __syncthreads();
 
@@ -107,35 +115,21 @@ __global__ void __launch_bounds__(512) qrms_rowreg_kernel(const QRmsArgs a) {
 
   const int64_t first = blockIdx.x, step = gridDim.x;
   if (a.bulk && tx == 0 && first < a.rows) issue(first, 0);
-  uint32_t phase[kQStages] = {0, 0};
+  uint32_t phase = 0;  // one parity bit per stage
   int it = 0;
   for (int64_t row = first; row < a.rows; row += step, ++it) {
     const int stage = it % kQStages;
     unsigned char* buf = stage0 + stage * stage_bytes;
     uint64_t id;
     const int kind = classify(row, id);
-    if (a.bulk) {
-      // the other stage was released by the barrier at the end of the previous iteration
-      if (tx == 0 && row + step < a.rows) issue(row + step, (it + 1) % kQStages);
-    }
+    // The other stage is free: its readers finished before the previous row's first barrier.
+    if (a.bulk && tx == 0 && row + step < a.rows) issue(row + step, (it + 1) % kQStages);
     if (kind == 0) {
       if (a.bulk) {
-        const bool ok = mbar_wait(&bars[stage], phase[stage]);
-        phase[stage] ^= 1u;
-        if (!__syncthreads_and(ok ? 1 : 0)) {
-          if (tx == 0) {
-            report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row, static_cast<int64_t>(id), a.vocab);
-            // bounded second chance for this row's copy and for the prefetch of the next one,
-            // so that no copy lands in shared memory after the CTA has retired
-            mbar_wait(&bars[stage], phase[stage] ^ 1u);
-            uint64_t nid;
-            if (row + step < a.rows && classify(row + step, nid) == 0) {
-              const int ns = (it + 1) % kQStages;
-              mbar_wait(&bars[ns], phase[ns]);
-            }
-          }
-          return;
-        }
+        // A wait that runs out is recorded and acted on after the row's barriers, where the
+        // whole CTA sees the flag and can leave together.
+        if (!mbar_wait(&bars[stage], (phase >> stage) & 1u)) *abort_flag = 1;
+        phase ^= 1u << stage;
       } else {
         // rows that are not 16-byte multiples: cooperative 2-byte copies
         const uint16_t* src =
@@ -154,22 +148,40 @@ __global__ void __launch_bounds__(512) qrms_rowreg_kernel(const QRmsArgs a) {
       int v = k * tpr + tx;
       if (v < a.V && kind == 0) {
         h[k] = decode_vec8<QT, DT>(buf, v);
-        accumulate_vec<DT>(h[k], v * 8, a.n, lsum, lw);
+        accumulate_vec<DT>(h[k], v, a.n, lsum, lw);
       } else {
         h[k] = (kind == 1) ? neg_zero_vec<DT>() : make_uint4(0, 0, 0, 0);
       }
     }
-    if (kind != 2 && a.gathered != nullptr) {
-      uint4* g = a.gathered + row * a.V;
-#pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        int v = k * tpr + tx;
-        if (v < a.V) stg_stream(g + v, h[k]);
-      }
-    }
     const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm);
-    if (kind != 2) write_rms_row<DT, VPT>(h, m, a.alpha, a.y + row * a.V, a.V);
-    __syncthreads();  // everyone is done with `buf` and with the reduction scratch
+    if (*abort_flag) {
+      if (tx == 0) {
+        report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row, static_cast<int64_t>(id), a.vocab);
+        // bounded second chance for this row's copy and for the prefetch of the next one, so
+        // that no copy lands in shared memory after the CTA has retired
+        mbar_wait(&bars[stage], ((phase >> stage) & 1u) ^ 1u);
+        uint64_t nid;
+        if (row + step < a.rows && classify(row + step, nid) == 0) {
+          const int ns = (it + 1) % kQStages;
+          mbar_wait(&bars[ns], (phase >> ns) & 1u);
+        }
+      }
+      return;
+    }
+    if (kind != 2) {
+      if (a.gathered != nullptr) {
+        uint4* g = a.gathered + row * a.V;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          int v = k * tpr + tx;
+          if (v < a.V) stg_stream(g + v, h[k]);
+        }
+      }
+      write_rms_row<DT, VPT>(h, m, a.alpha, a.y + row * a.V, a.V);
+    }
+    // No barrier here: every thread finished decoding `buf` before the row's first barrier and
+    // reads the published m before the next row's first barrier, so the prefetch issued at the
+    // top of the next iteration and the next row's scratch writes cannot race with this row.
   }
 }
 
@@ -188,11 +200,11 @@ bool rms_rowreg_supported(int dtype, int cols) {
   return (dtype == kDtBF16 || dtype == kDtF16) && cols % 8 == 0 && cols >= 8 && cols <= 32768;
 }
 
-template <int DT, int VPT>
+template <int DT, int VPT, int BT>
 static cudaError_t launch_dense_t(const RmsRowRegArgs& a, int tpr, int rpc, cudaStream_t stream) {
   const bool with_rows = !(a.flags & CB200_FLAG_FAST_SUM);
   size_t smem = RowRegSmem::bytes(rpc, a.V, with_rows);
-  auto kern = rms_rowreg_kernel<DT, VPT>;
+  auto kern = rms_rowreg_kernel<DT, VPT, BT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
@@ -203,14 +215,22 @@ static cudaError_t launch_dense_t(const RmsRowRegArgs& a, int tpr, int rpc, cuda
   return cudaGetLastError();
 }
 
+template <int DT, int VPT>
+static cudaError_t launch_dense_bt(const RmsRowRegArgs& a, int tpr, int rpc, cudaStream_t stream) {
+  const int bt = tpr * rpc;
+  if (bt <= 128) return launch_dense_t<DT, VPT, 128>(a, tpr, rpc, stream);
+  if (bt <= 256) return launch_dense_t<DT, VPT, 256>(a, tpr, rpc, stream);
+  return launch_dense_t<DT, VPT, 512>(a, tpr, rpc, stream);
+}
+
 template <int DT>
 static cudaError_t launch_dense_dt(const RmsRowRegArgs& a, cudaStream_t stream) {
   int tpr, vpt, rpc;
   rowreg_shape(a.V, tpr, vpt, rpc);
-  if (vpt <= 1) return launch_dense_t<DT, 1>(a, tpr, rpc, stream);
-  if (vpt <= 2) return launch_dense_t<DT, 2>(a, tpr, rpc, stream);
-  if (vpt <= 4) return launch_dense_t<DT, 4>(a, tpr, rpc, stream);
-  return launch_dense_t<DT, 8>(a, tpr, rpc, stream);
+  if (vpt <= 1) return launch_dense_bt<DT, 1>(a, tpr, rpc, stream);
+  if (vpt <= 2) return launch_dense_bt<DT, 2>(a, tpr, rpc, stream);
+  if (vpt <= 4) return launch_dense_bt<DT, 4>(a, tpr, rpc, stream);
+  return launch_dense_bt<DT, 8>(a, tpr, rpc, stream);
 }
 
 cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t stream) {
@@ -218,33 +238,44 @@ cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t st
   return dtype == kDtBF16 ? launch_dense_dt<kDtBF16>(a, stream) : launch_dense_dt<kDtF16>(a, stream);
 }
 
-template <int QT, int DT, int VPT>
+template <int QT, int DT, int VPT, int BT>
 static cudaError_t launch_q_t(const QRmsArgs& a, int tpr, cudaStream_t stream) {
   const int stage_bytes = (a.row_bytes + 15) & ~15;
-  size_t smem = RowRegSmem::bytes(1, a.V, true) + static_cast<size_t>(kQStages) * stage_bytes + kQStages * 8;
-  auto kern = qrms_rowreg_kernel<QT, DT, VPT>;
+  size_t smem = RowRegSmem::bytes(1, a.V, true) + static_cast<size_t>(kQStages) * stage_bytes + kQStages * 8 + 8;
+  auto kern = qrms_rowreg_kernel<QT, DT, VPT, BT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
   }
-  // persistent: a few CTAs per SM, each streaming rows through its two-stage ring
-  int ctas_per_sm = tpr >= 256 ? 4 : 8;
+  // persistent: exactly as many CTAs as fit on the device, each streaming rows through its ring
+  int ctas_per_sm = 1;
+  cudaError_t oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, tpr, smem);
+  if (oe != cudaSuccess) return oe;
+  if (ctas_per_sm < 1) ctas_per_sm = 1;
   int64_t grid = static_cast<int64_t>(kSmCount) * ctas_per_sm;
   if (grid > a.rows) grid = a.rows;
   kern<<<static_cast<unsigned>(grid), tpr, smem, stream>>>(a);
   return cudaGetLastError();
 }
 
+template <int QT, int DT, int VPT>
+static cudaError_t launch_q_bt(const QRmsArgs& a, int tpr, cudaStream_t stream) {
+  if (tpr <= 128) return launch_q_t<QT, DT, VPT, 128>(a, tpr, stream);
+  if (tpr <= 256) return launch_q_t<QT, DT, VPT, 256>(a, tpr, stream);
+  return launch_q_t<QT, DT, VPT, 512>(a, tpr, stream);
+}
+
 template <int QT, int DT>
 static cudaError_t launch_q_dt(const QRmsArgs& a, cudaStream_t stream) {
   int tpr, vpt, rpc;
   rowreg_shape(a.V, tpr, vpt, rpc);
-  if (tpr < 64) tpr = 64;  // one row per CTA here: keep at least two warps busy
+  if (tpr < 512 && vpt > 2) tpr *= 2;  // the decoder needs registers: two vectors per thread where possible
+  if (tpr < 64) tpr = 64;              // one row per CTA here: keep at least two warps busy
   vpt = (a.V + tpr - 1) / tpr;
-  if (vpt <= 1) return launch_q_t<QT, DT, 1>(a, tpr, stream);
-  if (vpt <= 2) return launch_q_t<QT, DT, 2>(a, tpr, stream);
-  if (vpt <= 4) return launch_q_t<QT, DT, 4>(a, tpr, stream);
-  return launch_q_t<QT, DT, 8>(a, tpr, stream);
+  if (vpt <= 1) return launch_q_bt<QT, DT, 1>(a, tpr, stream);
+  if (vpt <= 2) return launch_q_bt<QT, DT, 2>(a, tpr, stream);
+  if (vpt <= 4) return launch_q_bt<QT, DT, 4>(a, tpr, stream);
+  return launch_q_bt<QT, DT, 8>(a, tpr, stream);
 }
 
 cudaError_t launch_qrms_rowreg(int qtype, int dtype, const QRmsArgs& a, cudaStream_t stream) {

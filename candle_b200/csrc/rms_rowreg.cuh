@@ -14,8 +14,10 @@
 //      add up to at most W) and |tree - exact| <= 128u * exact,
 //   3. evaluates candle's f32 pipeline (all of it monotone) at both ends of the interval; if
 //      T(m) agrees at both ends it IS the sequential answer,
-//   4. otherwise (a few percent of rows at 8192 columns) replays the row from shared memory in
-//      sequential order with one thread.
+//   4. otherwise (a few percent of rows at 8192 columns) one thread replays the row, which every
+//      row parks in shared memory, in sequential order.
+// Arithmetic in T uses the packed two-element instructions (add/mul .rn .bf16x2/.f16x2): the
+// kernel is otherwise bound by instruction issue rather than by HBM.
 // The division x / m rounded to bf16 is evaluated as bf16(x * (1/m)): a quotient of two 8-bit
 // significands is never closer than 2^-17 (relative) to a bf16 rounding boundary, far more than
 // the 2^-22 error of the reciprocal product, so both round identically.  f16 has no such margin
@@ -63,33 +65,66 @@ struct QRmsArgs {
 
 // Shared-memory layout of one CTA of the row-register kernels.
 struct RowRegSmem {
-  float* red;    // [rpc][2][16] warp partials
-  float* mslot;  // [rpc] resolved T(m) of replayed rows
-  uint4* rows;   // [rpc][V] row replay buffers
+  float* red;   // [rpc][32]: warp partials of sum (0..15) and of the weighted sum (16..31)
+  float* pub;   // [rpc][4]: the resolved T(m), published by warp 0 of the row
+  uint4* rows;  // [rpc][V]: h, kept for the sequential replay
   __device__ RowRegSmem(unsigned char* base, int rpc, int V, int ty) {
     red = reinterpret_cast<float*>(base) + ty * 32;
-    mslot = reinterpret_cast<float*>(base) + rpc * 32 + ty;
-    size_t off = (static_cast<size_t>(rpc) * 33 * sizeof(float) + 15) & ~static_cast<size_t>(15);
-    rows = reinterpret_cast<uint4*>(base + off) + static_cast<size_t>(ty) * V;
+    pub = reinterpret_cast<float*>(base) + rpc * 32 + ty * 4;
+    rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * 36 * sizeof(float)) + static_cast<size_t>(ty) * V;
   }
   __host__ __device__ static size_t bytes(int rpc, int V, bool with_rows) {
-    size_t off = (static_cast<size_t>(rpc) * 33 * sizeof(float) + 15) & ~static_cast<size_t>(15);
-    return off + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
+    return static_cast<size_t>(rpc) * 36 * sizeof(float) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
   }
 };
 
+// Packed two-element arithmetic in T with one IEEE rounding per lane -- exactly what crate `half`
+// yields for `a + b` / `a * b` on T (operate in f32, round back): the exact sum or product of two
+// 16-bit values fits the f32 significand's 2p+2 bits, so rounding it once to T is the same thing.
 template <int DT>
-__device__ __forceinline__ void accumulate_vec(const uint4& h, int first_col, int n, float& lsum, float& lw) {
+__device__ __forceinline__ uint32_t add2_rn(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if constexpr (DT == kDtBF16)
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  else
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+template <int DT>
+__device__ __forceinline__ uint32_t mul2_rn(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if constexpr (DT == kDtBF16)
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  else
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+__device__ __forceinline__ void row_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// h = T(x + res) for one vector.
+template <int DT>
+__device__ __forceinline__ uint4 add_round_vec(const uint4& a, const uint4& b) {
+  return make_uint4(add2_rn<DT>(a.x, b.x), add2_rn<DT>(a.y, b.y), add2_rn<DT>(a.z, b.z), add2_rn<DT>(a.w, b.w));
+}
+
+// Adds one vector's squares to the tree-order sums.  `vec_index` is the vector's position in the
+// row; all eight elements are weighted with n - 8*vec_index, an upper bound of their own n - j.
+// h*h is exact in f32 for 16-bit h, so the fused multiply-add rounds exactly like add(s, h*h).
+template <int DT>
+__device__ __forceinline__ void accumulate_vec(const uint4& h, int vec_index, int n, float& lsum, float& lw) {
   const uint32_t w[4] = {h.x, h.y, h.z, h.w};
+  float vs = 0.0f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float2 f = unpack2<DT>(w[i]);
-    float p0 = __fmul_rn(f.x, f.x), p1 = __fmul_rn(f.y, f.y);
-    lsum += p0;
-    lsum += p1;
-    lw = fmaf(p0, static_cast<float>(n - (first_col + 2 * i)), lw);
-    lw = fmaf(p1, static_cast<float>(n - (first_col + 2 * i + 1)), lw);
+    vs = fmaf(f.x, f.x, vs);
+    vs = fmaf(f.y, f.y, vs);
   }
+  lsum += vs;
+  lw = fmaf(vs, static_cast<float>(n - 8 * vec_index), lw);
 }
 
 // Sequential replay of one row held in shared memory (candle's summation order).
@@ -110,52 +145,68 @@ __device__ __forceinline__ float sequential_sum_sq(const uint4* row, int V) {
   return s;
 }
 
-// Resolves T(m) for the row held in h[] by the tpr threads of row slot ty.  Every thread of the
-// CTA must call it (it contains CTA-wide barriers); `live` rows only matter for the result.
+// Decides T(m) from the tree-order sums (s, w); returns false if only a sequential replay can.
+template <int DT>
+__device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, float& m) {
+  constexpr float kU = 5.9604644775390625e-8f;  // 2^-24
+  // |seq - tree| <= 1.01*u*W + 160*u*s covers both bounds, the f32 rounding of w and of this
+  // expression itself.
+  const float err = 1.01f * kU * w + 160.0f * kU * s;
+  const float m_lo = round_to<DT>(rms_from_sum(s - err, nf, eps));
+  const float m_hi = round_to<DT>(rms_from_sum(s + err, nf, eps));
+  m = m_lo;
+  // Squares below 2^-149 are not exact in f32; that can only matter when the whole row is that
+  // small AND eps is too: let the replay, which rounds like the CPU, handle it.
+  const bool tiny = (s < 7.8886091e-31f) && (eps < 1e-18f) && (s != 0.0f || w != 0.0f);
+  return (m_lo == m_hi) && !tiny;  // false as well when anything is NaN
+}
+
+// Resolves T(m) for the row held in h[] by the tpr threads of row slot threadIdx.y.  All threads
+// of the row must call it; rows synchronise on their own named barrier (id 1 + threadIdx.y).
 template <int DT, int VPT>
 __device__ __forceinline__ float resolve_row_m(const uint4 (&h)[VPT], float lsum, float lw, int V, int n,
                                                float eps, int flags, RowRegSmem& sm) {
   const int tx = threadIdx.x, tpr = blockDim.x;
   const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
-  float s = warp_sum(lsum), w = warp_sum(lw);
-  if (wpr > 1) {
-    if (lane == 0) {
-      sm.red[warp] = s;
-      sm.red[16 + warp] = w;
-    }
-    __syncthreads();
-    s = 0.0f;
-    w = 0.0f;
-    for (int i = 0; i < wpr; ++i) {  // fixed order: every thread of the row gets the same bits
-      s += sm.red[i];
-      w += sm.red[16 + i];
-    }
-  }
   const float nf = static_cast<float>(n);
-  if (flags & CB200_FLAG_FAST_SUM) return round_to<DT>(rms_from_sum(s, nf, eps));
-
-  constexpr float kU = 5.9604644775390625e-8f;  // 2^-24
-  // |seq - tree| <= 1.01*u*W + 160*u*s covers both bounds and the f32 rounding of w and of
-  // this expression itself.
-  const float err = 1.01f * kU * w + 160.0f * kU * s;
-  const float m_lo = round_to<DT>(rms_from_sum(s - err, nf, eps));
-  const float m_hi = round_to<DT>(rms_from_sum(s + err, nf, eps));
-  const bool replay = !(m_lo == m_hi);  // also true when anything is NaN
-  float m = m_lo;
-  if (__syncthreads_or(replay ? 1 : 0)) {
-    if (replay) {
+  const bool fast = flags & CB200_FLAG_FAST_SUM;
+  if (!fast) {
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        int v = k * tpr + tx;
-        if (v < V) sm.rows[v] = h[k];
-      }
+    for (int k = 0; k < VPT; ++k) {
+      int v = k * tpr + tx;
+      if (v < V) sm.rows[v] = h[k];
     }
-    __syncthreads();
-    if (replay && tx == 0) *sm.mslot = round_to<DT>(rms_from_sum(sequential_sum_sq<DT>(sm.rows, V), nf, eps));
-    __syncthreads();
-    if (replay) m = *sm.mslot;
   }
-  return m;
+  float s = warp_sum(lsum), w = warp_sum(lw);
+  if (wpr == 1) {
+    if (fast) return round_to<DT>(rms_from_sum(s, nf, eps));
+    float m;
+    if (!decide_m<DT>(s, w, nf, eps, m)) {  // warp-uniform
+      __syncwarp();
+      if (lane == 0) m = round_to<DT>(rms_from_sum(sequential_sum_sq<DT>(sm.rows, V), nf, eps));
+      m = __shfl_sync(0xFFFFFFFFu, m, 0);
+    }
+    return m;
+  }
+  if (lane == 0) {
+    sm.red[warp] = s;
+    sm.red[16 + warp] = w;
+  }
+  const int bar_id = 1 + threadIdx.y;
+  row_barrier(bar_id, tpr);
+  if (warp == 0) {
+    s = warp_sum(lane < wpr ? sm.red[lane] : 0.0f);
+    w = warp_sum(lane < wpr ? sm.red[16 + lane] : 0.0f);
+    float m;
+    if (fast) {
+      m = round_to<DT>(rms_from_sum(s, nf, eps));
+    } else if (!decide_m<DT>(s, w, nf, eps, m)) {
+      if (lane == 0) m = round_to<DT>(rms_from_sum(sequential_sum_sq<DT>(sm.rows, V), nf, eps));
+    }
+    if (lane == 0) sm.pub[0] = m;
+  }
+  row_barrier(bar_id, tpr);
+  return sm.pub[0];
 }
 
 // y = T(T(h / m) * alpha) for the vectors this thread holds.
@@ -170,46 +221,42 @@ __device__ __forceinline__ void write_rms_row(const uint4 (&h)[VPT], float m, co
   for (int k = 0; k < VPT; ++k) {
     int v = k * tpr + tx;
     if (v >= V) continue;
-    uint4 av = __ldg(alpha + v);
+    const uint4 av = __ldg(alpha + v);
     const uint32_t hw[4] = {h[k].x, h[k].y, h[k].z, h[k].w};
     const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+    float q[8];
+    if (fast_div) {
+      float amin = 3.0e38f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 hf = unpack2<DT>(hw[i]);
+        q[2 * i] = __fmul_rn(hf.x, r);
+        q[2 * i + 1] = __fmul_rn(hf.y, r);
+        amin = fminf(amin, fminf(fabsf(q[2 * i]), fabsf(q[2 * i + 1])));
+      }
+      // below 2^-100 the bf16 result may be subnormal, where the margin argument does not hold:
+      // recompute such (non-zero) elements with the exact quotient.  Zeros land here too.
+      if (amin < 7.8886091e-31f) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 hf = unpack2<DT>(hw[i]);
+          if (fabsf(q[2 * i]) < 7.8886091e-31f) q[2 * i] = __fdiv_rn(hf.x, m);
+          if (fabsf(q[2 * i + 1]) < 7.8886091e-31f) q[2 * i + 1] = __fdiv_rn(hf.y, m);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 hf = unpack2<DT>(hw[i]);
+        q[2 * i] = __fdiv_rn(hf.x, m);
+        q[2 * i + 1] = __fdiv_rn(hf.y, m);
+      }
+    }
     uint32_t ow[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 hf = unpack2<DT>(hw[i]);
-      float2 af = unpack2<DT>(aw[i]);
-      float q0, q1;
-      if (fast_div) {
-        q0 = __fmul_rn(hf.x, r);
-        q1 = __fmul_rn(hf.y, r);
-        // below 2^-100 the bf16 result may be subnormal: use the exact quotient there
-        if (fabsf(q0) < 7.8886091e-31f && q0 != 0.0f) q0 = __fdiv_rn(hf.x, m);
-        if (fabsf(q1) < 7.8886091e-31f && q1 != 0.0f) q1 = __fdiv_rn(hf.y, m);
-      } else {
-        q0 = __fdiv_rn(hf.x, m);
-        q1 = __fdiv_rn(hf.y, m);
-      }
-      q0 = round_to<DT>(q0);
-      q1 = round_to<DT>(q1);
-      ow[i] = pack2<DT>(__fmul_rn(q0, af.x), __fmul_rn(q1, af.y));
-    }
+    for (int i = 0; i < 4; ++i) ow[i] = mul2_rn<DT>(pack2<DT>(q[2 * i], q[2 * i + 1]), aw[i]);
     stg_stream(yrow + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
   }
-}
-
-// h = T(x + res) for one vector.
-template <int DT>
-__device__ __forceinline__ uint4 add_round_vec(const uint4& a, const uint4& b) {
-  const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-  const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-  uint32_t ow[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 fa = unpack2<DT>(aw[i]);
-    float2 fb = unpack2<DT>(bw[i]);
-    ow[i] = pack2<DT>(__fadd_rn(fa.x, fb.x), __fadd_rn(fa.y, fb.y));
-  }
-  return make_uint4(ow[0], ow[1], ow[2], ow[3]);
 }
 
 }  // namespace cb200
