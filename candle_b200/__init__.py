@@ -12,6 +12,7 @@ from .ops import (
     FLAG_FAST_SUM,
     FLAG_FORCE_GENERIC,
     FLAG_FORCE_LANEROW,
+    FLAG_FORCE_REPLAY,
     embedding_rms_norm,
     index_select,
     layer_norm,
@@ -24,5 +25,5 @@ from .quantized import GgmlDType, QTensor
 __all__ = [
     "CandleError", "InvalidIndex", "rms_norm", "layer_norm", "index_select", "embedding_rms_norm",
     "qembedding_rms_norm", "Embedding", "LayerNorm", "RmsNorm", "QEmbedding", "QTensor", "GgmlDType",
-    "FLAG_FAST_SUM", "FLAG_FORCE_LANEROW", "FLAG_FORCE_GENERIC",
+    "FLAG_FAST_SUM", "FLAG_FORCE_LANEROW", "FLAG_FORCE_GENERIC", "FLAG_FORCE_REPLAY",
 ]

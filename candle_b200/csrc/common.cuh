@@ -229,6 +229,31 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// 16-byte asynchronous global -> shared copy that bypasses registers and L1 (LDGSTS).  A thread
+// may read what it copied itself after cp_async_wait_all(); other threads need a barrier.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// Waits until at most `pending` (0..3) of this thread's most recent copy groups are unfinished.
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+  switch (pending) {
+    case 0:
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      break;
+    case 1:
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+      break;
+    case 2:
+      asm volatile("cp.async.wait_group 2;" ::: "memory");
+      break;
+    default:
+      asm volatile("cp.async.wait_group 3;" ::: "memory");
+      break;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Warp reductions.
 // ---------------------------------------------------------------------------------------------

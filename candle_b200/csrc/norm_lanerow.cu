@@ -11,6 +11,7 @@
 // The row pitch in shared memory is an odd number of 16-byte units so the 16-byte loads of the
 // lane-per-row walk are bank-conflict free.
 #include "launch.h"
+#include "rms_rowreg.cuh"
 
 namespace cb200 {
 
@@ -108,38 +109,43 @@ __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const Lan
   } else {
     const uint4* gr = static_cast<const uint4*>(a.res);
     uint4* gs = static_cast<uint4*>(a.sum_out);
-    for (int r = warp; r < live; r += kLaneRowWarps) {
-      const int64_t base = (row0 + r) * a.V;
-      uint4* dst = reinterpret_cast<uint4*>(rowbuf + static_cast<size_t>(r) * a.pitch);
-      for (int v0 = lane; v0 < a.V; v0 += 128) {
-        uint4 xv[4], rv[4];
+    // Each warp fills rows warp, warp+8, ...; four rows at a time so that eight 16-byte loads
+    // per lane are in flight before the first one is consumed.
+    constexpr int RPW = 4;
+    for (int rb = warp; rb < live; rb += kLaneRowWarps * RPW) {
+      for (int v = lane; v < a.V; v += 32) {
+        uint4 xv[RPW], rv[RPW];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          int v = v0 + 32 * j;
-          if (v < a.V) xv[j] = ldg_stream(gx + base + v);
+        for (int j = 0; j < RPW; ++j) {
+          const int r = rb + kLaneRowWarps * j;
+          xv[j] = (r < live) ? ldg_stream(gx + (row0 + r) * a.V + v) : make_uint4(0, 0, 0, 0);
         }
         if (gr != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            int v = v0 + 32 * j;
-            if (v < a.V) rv[j] = ldg_stream(gr + base + v);
+          for (int j = 0; j < RPW; ++j) {
+            const int r = rb + kLaneRowWarps * j;
+            rv[j] = (r < live) ? ldg_stream(gr + (row0 + r) * a.V + v) : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float fa[PV], fb[PV];
-            vec_to_floats<DT>(xv[j], fa);
-            vec_to_floats<DT>(rv[j], fb);
+          for (int j = 0; j < RPW; ++j) {
+            if constexpr (DT == kDtF32) {
+              float fa[PV], fb[PV];
+              vec_to_floats<DT>(xv[j], fa);
+              vec_to_floats<DT>(rv[j], fb);
 #pragma unroll
-            for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
-            xv[j] = floats_to_vec<DT>(fa);  // rounds the sum to T, as Tensor::add does
+              for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
+              xv[j] = floats_to_vec<DT>(fa);
+            } else {
+              xv[j] = add_round_vec<DT>(xv[j], rv[j]);  // rounds the sum to T, as Tensor::add does
+            }
           }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          int v = v0 + 32 * j;
-          if (v < a.V) {
-            dst[v] = xv[j];
-            if (gs != nullptr) stg_stream(gs + base + v, xv[j]);
+        for (int j = 0; j < RPW; ++j) {
+          const int r = rb + kLaneRowWarps * j;
+          if (r < live) {
+            reinterpret_cast<uint4*>(rowbuf + static_cast<size_t>(r) * a.pitch)[v] = xv[j];
+            if (gs != nullptr) stg_stream(gs + (row0 + r) * a.V + v, xv[j]);
           }
         }
       }
@@ -277,9 +283,11 @@ static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
   const int row_bytes = a.n * Elem<DT>::kBytes;
   a.V = row_bytes / 16;
   a.pitch = row_bytes + ((a.V & 1) ? 0 : 16);
-  // rows per CTA: up to a warp's worth, sized so that about three CTAs fit in an SM's shared
-  // memory, and small enough that small problems still spread over all SMs
-  int R = static_cast<int>((72 * 1024) / a.pitch);
+  // rows per CTA: up to a warp's worth, sized so that several CTAs fit in an SM's shared memory
+  // (their load / chain / store phases overlap), and small enough that small problems still
+  // spread over all SMs
+  int R = static_cast<int>((28 * 1024) / a.pitch);  // short rows: about eight CTAs per SM
+  if (R < 4) R = static_cast<int>((72 * 1024) / a.pitch);  // long rows: about three
   if (R > 32) R = 32;
   if (R < 1) R = 1;
   int64_t spread = (a.rows + 2 * kSmCount - 1) / (2 * kSmCount);

@@ -14,8 +14,8 @@
 //      add up to at most W) and |tree - exact| <= 128u * exact,
 //   3. evaluates candle's f32 pipeline (all of it monotone) at both ends of the interval; if
 //      T(m) agrees at both ends it IS the sequential answer,
-//   4. otherwise (a few percent of rows at 8192 columns) one thread replays the row, which every
-//      row parks in shared memory, in sequential order.
+//   4. otherwise (a few percent of rows at 8192 columns) parks the row in shared memory and replays
+//      it exactly (replay_sum_sq below).
 // Arithmetic in T uses the packed two-element instructions (add/mul .rn .bf16x2/.f16x2): the
 // kernel is otherwise bound by instruction issue rather than by HBM.
 // The division x / m rounded to bf16 is evaluated as bf16(x * (1/m)): a quotient of two 8-bit
@@ -63,18 +63,23 @@ struct QRmsArgs {
   int flags;
 };
 
-// Shared-memory layout of one CTA of the row-register kernels.
+// Shared-memory layout of one CTA of the row-register kernels (per row slot `ty`).
 struct RowRegSmem {
-  float* red;   // [rpc][32]: warp partials of sum (0..15) and of the weighted sum (16..31)
-  float* pub;   // [rpc][4]: the resolved T(m), published by warp 0 of the row
-  uint4* rows;  // [rpc][V]: h, kept for the sequential replay
-  __device__ RowRegSmem(unsigned char* base, int rpc, int V, int ty) {
-    red = reinterpret_cast<float*>(base) + ty * 32;
-    pub = reinterpret_cast<float*>(base) + rpc * 32 + ty * 4;
-    rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * 36 * sizeof(float)) + static_cast<size_t>(ty) * V;
+  float* red;    // [32]: warp partials of sum (0..15) and of the weighted sum (16..31)
+  float* pub;    // [4]: the resolved T(m), published by warp 0 of the row
+  int4* chunks;  // [tpr] replay: {A, B - A, L, -}: while the sum's bit pattern stays in the
+                 // binade that starts at L, a chunk adds A to an even and B to an odd one
+  uint4* rows;   // [V]: h, parked for the replay
+  __device__ RowRegSmem(unsigned char* base, int rpc, int tpr, int V, int ty) {
+    unsigned char* mine = base + static_cast<size_t>(ty) * slot_bytes(tpr);
+    chunks = reinterpret_cast<int4*>(mine);
+    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 16);
+    pub = red + 32;
+    rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * slot_bytes(tpr)) + static_cast<size_t>(ty) * V;
   }
-  __host__ __device__ static size_t bytes(int rpc, int V, bool with_rows) {
-    return static_cast<size_t>(rpc) * 36 * sizeof(float) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
+  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 16 + 36 * sizeof(float); }
+  __host__ __device__ static size_t bytes(int rpc, int tpr, int V, bool with_rows) {
+    return static_cast<size_t>(rpc) * slot_bytes(tpr) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
   }
 };
 
@@ -127,12 +132,12 @@ __device__ __forceinline__ void accumulate_vec(const uint4& h, int vec_index, in
   lw = fmaf(vs, static_cast<float>(n - 8 * vec_index), lw);
 }
 
-// Sequential replay of one row held in shared memory (candle's summation order).
+// Sequential sum of squares over vectors [v0, v1) of a row in shared memory, continuing from s:
+// candle's order and roundings (candle-nn/src/ops.rs:484-490).
 template <int DT>
-__device__ __forceinline__ float sequential_sum_sq(const uint4* row, int V) {
-  float s = 0.0f;
-#pragma unroll 4
-  for (int v = 0; v < V; ++v) {
+__device__ __forceinline__ float sequential_sum_sq(const uint4* row, int v0, int v1, float s) {
+#pragma unroll 2
+  for (int v = v0; v < v1; ++v) {
     uint4 q = row[v];
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -143,6 +148,125 @@ __device__ __forceinline__ float sequential_sum_sq(const uint4* row, int V) {
     }
   }
   return s;
+}
+
+// Exact sequential-order sum of squares of the row parked in sm.rows, computed cooperatively by
+// the tpr threads of the row (all must call; the result is valid in thread 0 of the row).
+//
+// A chain s <- fl(s + p) with p >= 0 cannot be split naively, but while s stays inside one
+// binade [2^e, 2^(e+1)) it is integer arithmetic on the significand S: fl(S + P) = S + round(P)
+// where the tie rule only looks at the parity of S.  So the effect of a run of additions on ANY
+// start value of that binade is "S + A if S is even, S + B if S is odd", and A, B can be measured
+// by running the run twice, from an even and from an odd reference value of the same binade.
+// Every thread measures (A, B) for its own contiguous chunk, using the approximate prefix sum to
+// pick the binade; thread 0 then walks the chunks with exact integer updates, checking that the
+// true value really is in the assumed binade before and after each chunk (the sum is monotone, so
+// that covers the whole chunk) and falling back to plain sequential addition for the chunk
+// otherwise.  The checks make the result exact whatever the quality of the guesses.
+template <int DT>
+__device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, float* red, int V, int bar_id) {
+  const int tx = threadIdx.x, tpr = blockDim.x;
+  const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
+  const int vpc = (V + tpr - 1) / tpr;  // vectors per chunk
+  const int v0 = min(V, tx * vpc), v1 = min(V, v0 + vpc);
+
+  float sig = 0.0f;
+  for (int v = v0; v < v1; ++v) {
+    uint4 q = rows[v];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = unpack2<DT>(w[i]);
+      sig = fmaf(f.x, f.x, sig);
+      sig = fmaf(f.y, f.y, sig);
+    }
+  }
+  // approximate exclusive prefix of the chunk sums
+  float incl = sig;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (wpr > 1) {
+    if (lane == 31) red[warp] = incl;
+    row_barrier(bar_id, tpr);
+    float base = 0.0f;
+    for (int i = 0; i < warp; ++i) base += red[i];
+    incl += base;
+  }
+  const float prefix = incl - sig;
+
+  // measure the chunk from an even and an odd reference value next to the approximate prefix
+  const uint32_t e0 = __float_as_uint(prefix) & ~1u;
+  const int e = static_cast<int>(e0 >> 23);
+  bool ok = (v0 < v1) && (prefix > 0.0f) && (e >= 67) && (e <= 187);  // 2^-60 .. 2^60
+  float s0 = __uint_as_float(e0), s1 = __uint_as_float(e0 + 1u);
+  if (ok) {
+    for (int v = v0; v < v1; ++v) {
+      uint4 q = rows[v];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = unpack2<DT>(w[i]);
+        s0 = fmaf(f.x, f.x, s0);  // h*h is exact, so this rounds like fl(s + h*h)
+        s1 = fmaf(f.x, f.x, s1);
+        s0 = fmaf(f.y, f.y, s0);
+        s1 = fmaf(f.y, f.y, s1);
+      }
+    }
+    ok = static_cast<int>(__float_as_uint(s1) >> 23) == e;  // the references stayed in the binade
+  }
+  // record: {A, B - A, first bit pattern of the binade}; an unusable chunk gets a binade start no
+  // running sum can reach, so the range check below rejects it
+  const uint32_t inc_even = __float_as_uint(s0) - e0, inc_odd = __float_as_uint(s1) - (e0 + 1u);
+  chunks[tx] = make_int4(static_cast<int>(inc_even), static_cast<int>(inc_odd - inc_even),
+                         ok ? static_cast<int>(static_cast<uint32_t>(e) << 23) : -1, 0);
+  if (wpr > 1)
+    row_barrier(bar_id, tpr);
+  else
+    __syncwarp();
+
+  float result = 0.0f;
+  if (tx == 0) {
+    uint32_t S = 0u;  // bits of the running sum (+0.0f)
+    // One chunk: S stays in the chunk's binade before and after (the sum never decreases, so in
+    // between as well) -> exact integer update; otherwise add the chunk's elements one by one.
+    auto step = [&](const int4& k, int c) {
+      const uint32_t lo = static_cast<uint32_t>(k.z);
+      const uint32_t S2 = S + static_cast<uint32_t>(k.x) + (S & 1u) * static_cast<uint32_t>(k.y);
+      if (S >= lo && (S2 - lo) < 0x800000u) {
+        S = S2;
+      } else {
+        const int c0 = min(V, c * vpc), c1 = min(V, c0 + vpc);
+        S = __float_as_uint(sequential_sum_sq<DT>(rows, c0, c1, __uint_as_float(S)));
+      }
+    };
+    int c = 0;
+    for (; c + 4 <= tpr; c += 4) {
+      // four chunks speculatively, branch-free, and one check for all of them
+      const int4 k0 = chunks[c], k1 = chunks[c + 1], k2 = chunks[c + 2], k3 = chunks[c + 3];
+      const uint32_t T1 = S + static_cast<uint32_t>(k0.x) + (S & 1u) * static_cast<uint32_t>(k0.y);
+      const uint32_t T2 = T1 + static_cast<uint32_t>(k1.x) + (T1 & 1u) * static_cast<uint32_t>(k1.y);
+      const uint32_t T3 = T2 + static_cast<uint32_t>(k2.x) + (T2 & 1u) * static_cast<uint32_t>(k2.y);
+      const uint32_t T4 = T3 + static_cast<uint32_t>(k3.x) + (T3 & 1u) * static_cast<uint32_t>(k3.y);
+      const bool all_ok = (S >= static_cast<uint32_t>(k0.z)) && ((T1 - static_cast<uint32_t>(k0.z)) < 0x800000u) &&
+                          (T1 >= static_cast<uint32_t>(k1.z)) && ((T2 - static_cast<uint32_t>(k1.z)) < 0x800000u) &&
+                          (T2 >= static_cast<uint32_t>(k2.z)) && ((T3 - static_cast<uint32_t>(k2.z)) < 0x800000u) &&
+                          (T3 >= static_cast<uint32_t>(k3.z)) && ((T4 - static_cast<uint32_t>(k3.z)) < 0x800000u);
+      if (all_ok) {
+        S = T4;
+      } else {
+        step(k0, c);
+        step(k1, c + 1);
+        step(k2, c + 2);
+        step(k3, c + 3);
+      }
+    }
+    for (; c < tpr; ++c) step(chunks[c], c);
+    result = __uint_as_float(S);
+  }
+  return result;
 }
 
 // Decides T(m) from the tree-order sums (s, w); returns false if only a sequential replay can.
@@ -163,50 +287,67 @@ __device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, 
 
 // Resolves T(m) for the row held in h[] by the tpr threads of row slot threadIdx.y.  All threads
 // of the row must call it; rows synchronise on their own named barrier (id 1 + threadIdx.y).
+// `park` is V vectors of shared memory of this row that h can be written to when a replay is needed.
 template <int DT, int VPT>
 __device__ __forceinline__ float resolve_row_m(const uint4 (&h)[VPT], float lsum, float lw, int V, int n,
-                                               float eps, int flags, RowRegSmem& sm) {
+                                               float eps, int flags, RowRegSmem& sm, uint4* park) {
   const int tx = threadIdx.x, tpr = blockDim.x;
   const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
   const float nf = static_cast<float>(n);
   const bool fast = flags & CB200_FLAG_FAST_SUM;
-  if (!fast) {
+  const bool force = flags & CB200_FLAG_FORCE_REPLAY;
+  const int bar_id = 1 + threadIdx.y;
+
+  float s = warp_sum(lsum), w = warp_sum(lw);
+  float m = 0.0f;
+  bool replay;
+  if (wpr == 1) {
+    if (fast) return round_to<DT>(rms_from_sum(s, nf, eps));
+    replay = !decide_m<DT>(s, w, nf, eps, m) || force;  // warp-uniform
+  } else {
+    if (lane == 0) {
+      sm.red[warp] = s;
+      sm.red[16 + warp] = w;
+    }
+    row_barrier(bar_id, tpr);
+    if (warp == 0) {
+      s = warp_sum(lane < wpr ? sm.red[lane] : 0.0f);
+      w = warp_sum(lane < wpr ? sm.red[16 + lane] : 0.0f);
+      bool need = false;
+      if (fast)
+        m = round_to<DT>(rms_from_sum(s, nf, eps));
+      else
+        need = !decide_m<DT>(s, w, nf, eps, m) || force;
+      if (lane == 0) {
+        sm.pub[0] = m;
+        sm.pub[1] = need ? 1.0f : 0.0f;
+      }
+    }
+    row_barrier(bar_id, tpr);
+    m = sm.pub[0];
+    replay = sm.pub[1] != 0.0f;  // row-uniform
+  }
+  if (replay) {
+    // park h in shared memory and run the exact replay with all threads of the row
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       int v = k * tpr + tx;
-      if (v < V) sm.rows[v] = h[k];
+      if (v < V) park[v] = h[k];
     }
-  }
-  float s = warp_sum(lsum), w = warp_sum(lw);
-  if (wpr == 1) {
-    if (fast) return round_to<DT>(rms_from_sum(s, nf, eps));
-    float m;
-    if (!decide_m<DT>(s, w, nf, eps, m)) {  // warp-uniform
+    if (wpr > 1)
+      row_barrier(bar_id, tpr);
+    else
       __syncwarp();
-      if (lane == 0) m = round_to<DT>(rms_from_sum(sequential_sum_sq<DT>(sm.rows, V), nf, eps));
-      m = __shfl_sync(0xFFFFFFFFu, m, 0);
+    const float total = replay_sum_sq<DT>(park, sm.chunks, sm.red, V, bar_id);
+    if (wpr == 1) {
+      m = __shfl_sync(0xFFFFFFFFu, round_to<DT>(rms_from_sum(total, nf, eps)), 0);
+    } else {
+      if (tx == 0) sm.pub[2] = round_to<DT>(rms_from_sum(total, nf, eps));
+      row_barrier(bar_id, tpr);
+      m = sm.pub[2];
     }
-    return m;
   }
-  if (lane == 0) {
-    sm.red[warp] = s;
-    sm.red[16 + warp] = w;
-  }
-  const int bar_id = 1 + threadIdx.y;
-  row_barrier(bar_id, tpr);
-  if (warp == 0) {
-    s = warp_sum(lane < wpr ? sm.red[lane] : 0.0f);
-    w = warp_sum(lane < wpr ? sm.red[16 + lane] : 0.0f);
-    float m;
-    if (fast) {
-      m = round_to<DT>(rms_from_sum(s, nf, eps));
-    } else if (!decide_m<DT>(s, w, nf, eps, m)) {
-      if (lane == 0) m = round_to<DT>(rms_from_sum(sequential_sum_sq<DT>(sm.rows, V), nf, eps));
-    }
-    if (lane == 0) sm.pub[0] = m;
-  }
-  row_barrier(bar_id, tpr);
-  return sm.pub[0];
+  return m;
 }
 
 // y = T(T(h / m) * alpha) for the vectors this thread holds.

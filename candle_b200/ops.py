@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import _cabi
-from ._cabi import FLAG_FAST_SUM, FLAG_FORCE_GENERIC, FLAG_FORCE_LANEROW  # noqa: F401
+from ._cabi import FLAG_FAST_SUM, FLAG_FORCE_GENERIC, FLAG_FORCE_LANEROW, FLAG_FORCE_REPLAY  # noqa: F401
 from .errors import CandleError, InvalidIndex
 
 _DTYPES = {torch.float32: _cabi.DTYPE_F32, torch.float16: _cabi.DTYPE_F16, torch.bfloat16: _cabi.DTYPE_BF16}

@@ -62,6 +62,7 @@ extern "C" {
  * to cross-check the independent kernels against each other at sizes the CPU oracle is slow at. */
 #define CB200_FLAG_FORCE_LANEROW 0x100 /* lane-per-row sequential kernel even where the register kernel applies */
 #define CB200_FLAG_FORCE_GENERIC 0x200 /* any-shape scalar kernel */
+#define CB200_FLAG_FORCE_REPLAY 0x400  /* register kernels: take the exact replay path for every row */
 
 /* return codes */
 #define CB200_OK 0

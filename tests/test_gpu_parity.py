@@ -121,7 +121,7 @@ def test_kat_quantize_q4_0_dequantize(cb, kats):
 # norms against the oracle
 # ------------------------------------------------------------------------------------------------
 NORM_SHAPES = [(1, 8), (7, 3), (3, 200), (33, 64), (5, 768), (40, 1024), (64, 4096), (17, 8192), (2, 2, 16384), (3, 32768)]
-IMPLS = {"default": 0, "lanerow": 0x100, "generic": 0x200}
+IMPLS = {"default": 0, "lanerow": 0x100, "generic": 0x200, "replay": 0x400}
 
 
 @pytest.mark.parametrize("impl", list(IMPLS))
@@ -132,7 +132,8 @@ def test_rms_norm_matches_oracle(cb, dtype, residual, impl):
     for shape in NORM_SHAPES:
         if impl == "generic" and shape[-1] > 8192:
             continue
-        x = randn(rng, shape, dtype)
+        scale = 1.0 if len(shape) < 3 else 37.0  # vary the binades the running sum walks through
+        x = randn(rng, shape, dtype, 0.0, scale)
         a = randn(rng, shape[-1:], dtype, 1.0, 0.1)
         r = randn(rng, shape, dtype) if residual else None
         h = oracle.add(x, r, dtype) if residual else x
@@ -188,6 +189,9 @@ def test_rms_norm_many_rows_exercises_the_replay_path(cb):
     assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
     # the tree-order variant stays within the stated tolerance on all but a handful of rows and
     # differs from the exact result only where bf16(m) flipped
+    # ... and so does the exact replay when it is forced on every row
+    y4 = cb.rms_norm(xt, at, 1e-5, residual=rt, flags=cb.FLAG_FORCE_REPLAY)
+    assert torch.equal(y.view(torch.int16), y4.view(torch.int16))
     y3 = cb.rms_norm(xt, at, 1e-5, residual=rt, flags=cb.FLAG_FAST_SUM)
     rows_diff = (y3.view(torch.int16) != y.view(torch.int16)).any(dim=1).sum().item()
     assert rows_diff <= 64
