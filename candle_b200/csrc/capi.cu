@@ -251,7 +251,7 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
   if (!all_aligned16(alpha, y, gathered) || (reinterpret_cast<uintptr_t>(qtable) & 1u))
     return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha, y and gathered must be 16-byte aligned, the table 2-byte aligned", name);
-  const bool fused = out_dtype != CB200_DTYPE_F32 && cb200::rms_rowreg_supported(out_dtype, hidden) &&
+  const bool fused = out_dtype != CB200_DTYPE_F32 && cb200::qrms_rowreg_supported(out_dtype, hidden) &&
                      !(flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC));
   if (!fused) {
     // Two launches through the caller's `gathered` buffer (f32 output, or a forced implementation).

@@ -33,6 +33,7 @@ struct RmsRowRegArgs;
 struct QRmsArgs;
 
 bool rms_rowreg_supported(int dtype, int cols);
+bool qrms_rowreg_supported(int dtype, int cols);
 cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t stream);
 cudaError_t launch_qrms_rowreg(int qtype, int dtype, const QRmsArgs& a, cudaStream_t stream);
 

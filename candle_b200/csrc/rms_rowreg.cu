@@ -3,122 +3,85 @@
 // fly from a Q4_0 / Q8_0 table staged into shared memory by the bulk-copy engine.
 //
 // All kernels are persistent: the grid is as many CTAs as fit on the device and each CTA walks
-// rows with a stride.  Loaded HBM latency on B200 is about 3 us, so an SM needs on the order of
-// 100 KB of reads in flight at all times; the dense kernel gets there by starting the next row's
-// 16-byte asynchronous copies before it processes the current row, the quantised kernel by
-// keeping a ring of bulk copies in flight.
+// rows with a stride.  An SM needs on the order of 100 KB of reads in flight at all times to
+// saturate HBM; the dense kernel gets there with 768 resident threads that each have up to eight
+// 16-byte loads outstanding, the quantised kernel by keeping a ring of bulk copies in flight.
 #include "launch.h"
 #include "qblocks.cuh"
 #include "rms_rowreg.cuh"
 
 namespace cb200 {
 
-// Dense rows.  Every row slot of a CTA owns a ring of `stages` staging buffers in shared memory.
-// Each thread copies its own 16-byte vectors of the rows ahead (and of their residual rows) into
-// the ring with asynchronous copies, which need no registers while in flight, and only ever reads
-// back the vectors it copied itself, so no barrier guards the ring.  A buffer is refilled once its
-// row's T(m) is known; until then it doubles as the place where h is parked if the row needs the
-// exact replay.  Three 256-thread CTAs with two 32 KB buffers each keep up to 192 KB of reads in
-// flight per SM.
-template <int VPT, int BT>
-constexpr int rowreg_min_blocks() {
-  return (VPT == 8 ? 512 : 768) / BT;
-}
-
-template <int DT, int VPT, int BT>
-__global__ void __launch_bounds__(BT, rowreg_min_blocks<VPT, BT>()) rms_rowreg_kernel(const RmsRowRegArgs a, int stages) {
+// Dense rows: a grid-stride walk with the row held in registers.  Rows are exactly VPT vectors per
+// thread (the launcher picks threads-per-row so), which keeps the loop free of bounds checks;
+// alpha and the position weights stay in registers for the whole walk.  Three 256-thread CTAs per
+// SM, each thread with up to eight 16-byte loads outstanding, keep about 100 KB of reads in flight
+// per SM, which measurement shows is what saturates HBM on B200 as long as the loop stays lean:
+// the rare exact replay is kept out of line for that reason.
+template <int DT, int VPT, int BT, bool GATHER>
+__global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRegArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
   RowRegSmem sm(smem_raw, rpc, tpr, a.V, ty);
-  const bool has_res = a.res != nullptr;
-  const int buf_vecs = has_res ? 2 * a.V : a.V;
-  uint4* ring = reinterpret_cast<uint4*>(smem_raw + RowRegSmem::bytes(rpc, tpr, a.V, false)) +
-                static_cast<size_t>(ty) * stages * buf_vecs;
+  const bool has_res = !GATHER && a.res != nullptr;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * rpc;
 
-  // Starts the copies of row r into ring slot `slot` (one copy group per call, empty if there is
-  // nothing to copy); returns whether the row is live (inside the tensor and with a valid id).
-  auto issue = [&](int64_t r, int slot) -> bool {
-    bool ok = r < a.rows;
-    const uint4* xr = nullptr;
-    if (ok) {
-      if (a.ids != nullptr) {
-        const uint64_t id = read_id(a.ids, a.id_dtype, r);
-        if (id >= static_cast<uint64_t>(a.vocab)) {
-          if (tx == 0) report_status(a.status, CB200_STATUS_INVALID_INDEX, r, static_cast<int64_t>(id), a.vocab);
-          ok = false;
-        } else {
-          xr = a.x + id * a.V;
-        }
-      } else {
-        xr = a.x + r * a.V;
-      }
-    }
-    if (ok) {
-      uint4* sx = ring + static_cast<size_t>(slot) * buf_vecs;
+  uint4 al[VPT];
+  float wv[VPT];
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        const int v = k * tpr + tx;
-        if (v < a.V) cp_async16(sx + v, xr + v);
-      }
-      if (has_res) {
-        const uint4* rr = a.res + r * a.V;
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-          const int v = k * tpr + tx;
-          if (v < a.V) cp_async16(sx + a.V + v, rr + v);
-        }
-      }
-    }
-    cp_async_commit();
-    return ok;
-  };
+  for (int k = 0; k < VPT; ++k) {
+    al[k] = __ldg(a.alpha + k * tpr + tx);
+    wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
+  }
 
-  int64_t row = static_cast<int64_t>(blockIdx.x) * rpc + ty;
-  uint32_t live_bits = 0;  // bit s: the row in ring slot s is live
-  for (int j = 0; j < stages; ++j)
-    if (issue(row + j * stride, j)) live_bits |= 1u << j;
-  int slot = 0;
-  while (row < a.rows) {
-    cp_async_wait_pending(stages - 1);
-    uint4* sx = ring + static_cast<size_t>(slot) * buf_vecs;
-    const bool live = (live_bits >> slot) & 1u;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * rpc + ty; row < a.rows; row += stride) {
+    const uint4* xr;
+    bool live = true;
+    if (GATHER) {
+      const uint64_t id = read_id(a.ids, a.id_dtype, row);
+      live = id < static_cast<uint64_t>(a.vocab);
+      if (!live && tx == 0) report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
+      xr = a.x + (live ? id : 0) * a.V + tx;
+    } else {
+      xr = a.x + row * a.V + tx;
+    }
     uint4 h[VPT];
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-      const int v = k * tpr + tx;
-      if (v < a.V && live)
-        h[k] = has_res ? add_round_vec<DT>(sx[v], sx[a.V + v]) : sx[v];
-      else
-        h[k] = make_uint4(0, 0, 0, 0);
+    for (int k = 0; k < VPT; ++k) h[k] = ldg_stream(xr + k * tpr);
+    if (has_res) {
+      const uint4* rr = a.res + row * a.V + tx;
+      uint4 rv[VPT];
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) rv[k] = ldg_stream(rr + k * tpr);
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) h[k] = add_round_vec<DT>(h[k], rv[k]);
     }
     float lsum = 0.0f, lw = 0.0f;
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-      const int v = k * tpr + tx;
-      if (v < a.V) accumulate_vec<DT>(h[k], v, a.n, lsum, lw);
+    for (int k = 0; k < VPT; ++k) accumulate_vec_w<DT>(h[k], wv[k], lsum, lw);
+    bool replayed;
+    const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm, sm.rows, replayed);
+    if (replayed) {  // rare: nothing was kept in registers across the replay
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        al[k] = __ldg(a.alpha + k * tpr + tx);
+        wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
+      }
     }
-    const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm, sx);
-    // the slot is free now (a replay, if any, is over): refill it with the row `stages` ahead
-    if (issue(row + static_cast<int64_t>(stages) * stride, slot))
-      live_bits |= 1u << slot;
-    else
-      live_bits &= ~(1u << slot);
     if (live) {
       if (a.sum_out != nullptr) {
-        uint4* so = a.sum_out + row * a.V;
+        uint4* so = a.sum_out + row * a.V + tx;
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-          const int v = k * tpr + tx;
-          if (v < a.V) stg_stream(so + v, h[k]);
-        }
+        for (int k = 0; k < VPT; ++k) stg_stream(so + k * tpr, h[k]);
       }
-      write_rms_row<DT, VPT>(h, m, a.alpha, a.y + row * a.V, a.V);
+      // 2^-60 <= m <= 2^60: the reciprocal is a normal number and the margin argument applies
+      const bool fast_div = (DT == kDtBF16) && (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
+      const float r = fast_div ? __frcp_rn(m) : 0.0f;
+      uint4* yr = a.y + row * a.V + tx;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) stg_stream(yr + k * tpr, rms_output_vec<DT>(h[k], al[k], m, r, fast_div));
     }
-    row += stride;
-    slot = slot + 1 == stages ? 0 : slot + 1;
   }
-  cp_async_wait_all();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -208,7 +171,8 @@ __global__ void __launch_bounds__(BT, 1024 / BT) qrms_rowreg_kernel(const QRmsAr
         h[k] = (kind == 1) ? neg_zero_vec<DT>() : make_uint4(0, 0, 0, 0);
       }
     }
-    const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm, sm.rows);
+    bool replayed;
+    const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm, sm.rows, replayed);
     if (*abort_flag) {
       if (tx == 0) {
         report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row, static_cast<int64_t>(id), a.vocab);
@@ -245,16 +209,38 @@ __global__ void __launch_bounds__(BT, 1024 / BT) qrms_rowreg_kernel(const QRmsAr
 // ---------------------------------------------------------------------------------------------
 // Launchers
 // ---------------------------------------------------------------------------------------------
-static void rowreg_shape(int V, int& tpr, int& vpt, int& rpc) {
-  int want = (V + 3) / 4;
-  tpr = 32;
+// Threads per row and vectors per thread for a row of V vectors: V == tpr * vpt exactly, tpr a
+// multiple of 32 up to 512, preferring four vectors per thread.  Returns false if V has no such split.
+static bool rowreg_shape(int V, int& tpr, int& vpt, int& rpc) {
+  static const int prefs[] = {4, 3, 5, 2, 6, 7, 8, 1};
+  for (int cand : prefs) {
+    if (V % cand != 0) continue;
+    const int t = V / cand;
+    if (t % 32 != 0 || t > 512) continue;
+    tpr = t;
+    vpt = cand;
+    rpc = tpr >= 128 ? 1 : 128 / tpr;
+    return true;
+  }
+  return false;
+}
+
+// Shape of the quantised-source kernel (bounds-checked vectors, one row per CTA).
+static void qrowreg_shape(int V, int& tpr, int& vpt) {
+  int want = (V + 1) / 2;
+  tpr = 64;
   while (tpr < want && tpr < 512) tpr <<= 1;
   vpt = (V + tpr - 1) / tpr;
-  rpc = tpr >= 128 ? 1 : 128 / tpr;
 }
 
 bool rms_rowreg_supported(int dtype, int cols) {
-  return (dtype == kDtBF16 || dtype == kDtF16) && cols % 8 == 0 && cols >= 8 && cols <= 32768;
+  int tpr, vpt, rpc;
+  return (dtype == kDtBF16 || dtype == kDtF16) && cols % 8 == 0 && cols >= 256 && cols <= 32768 &&
+         rowreg_shape(cols / 8, tpr, vpt, rpc);
+}
+
+bool qrms_rowreg_supported(int dtype, int cols) {
+  return (dtype == kDtBF16 || dtype == kDtF16) && cols % 32 == 0 && cols >= 32 && cols <= 32768;
 }
 
 // A persistent grid: as many CTAs as are resident at once, but no more than there is work.
@@ -277,41 +263,50 @@ static cudaError_t persistent_grid(K kern, int threads, size_t smem, int64_t wor
   return cudaSuccess;
 }
 
-template <int DT, int VPT, int BT>
+template <int DT, int VPT, int BT, bool GATHER>
 static cudaError_t launch_dense_t(const RmsRowRegArgs& a, int tpr, int rpc, cudaStream_t stream) {
-  const size_t head = RowRegSmem::bytes(rpc, tpr, a.V, false);
-  const size_t buf = static_cast<size_t>(rpc) * a.V * 16 * (a.res != nullptr ? 2 : 1);  // one ring slot of the CTA
-  // ring depth: fill about 200 KB of an SM's shared memory with the CTAs the register cap admits
-  const int ctas = rowreg_min_blocks<VPT, BT>();
-  const size_t budget = (200 * 1024) / ctas;
-  int stages = budget > head ? static_cast<int>((budget - head) / buf) : 1;
-  if (stages > 4) stages = 4;
-  if (stages < 1) stages = 1;
-  const size_t smem = head + stages * buf;
-  auto kern = rms_rowreg_kernel<DT, VPT, BT>;
+  const bool with_rows = !(a.flags & CB200_FLAG_FAST_SUM);
+  const size_t smem = RowRegSmem::bytes(rpc, tpr, a.V, with_rows);
+  auto kern = rms_rowreg_kernel<DT, VPT, BT, GATHER>;
   unsigned grid = 1;
   cudaError_t e = persistent_grid(kern, tpr * rpc, smem, (a.rows + rpc - 1) / rpc, grid);
   if (e != cudaSuccess) return e;
-  kern<<<grid, dim3(tpr, rpc), smem, stream>>>(a, stages);
+  kern<<<grid, dim3(tpr, rpc), smem, stream>>>(a);
   return cudaGetLastError();
 }
 
 template <int DT, int VPT>
 static cudaError_t launch_dense_bt(const RmsRowRegArgs& a, int tpr, int rpc, cudaStream_t stream) {
-  const int bt = tpr * rpc;
-  if (bt <= 128) return launch_dense_t<DT, VPT, 128>(a, tpr, rpc, stream);
-  if (bt <= 256) return launch_dense_t<DT, VPT, 256>(a, tpr, rpc, stream);
-  return launch_dense_t<DT, VPT, 512>(a, tpr, rpc, stream);
+  const bool gather = a.ids != nullptr;
+  if (tpr * rpc <= 256)
+    return gather ? launch_dense_t<DT, VPT, 256, true>(a, tpr, rpc, stream)
+                  : launch_dense_t<DT, VPT, 256, false>(a, tpr, rpc, stream);
+  return gather ? launch_dense_t<DT, VPT, 512, true>(a, tpr, rpc, stream)
+                : launch_dense_t<DT, VPT, 512, false>(a, tpr, rpc, stream);
 }
 
 template <int DT>
 static cudaError_t launch_dense_dt(const RmsRowRegArgs& a, cudaStream_t stream) {
-  int tpr, vpt, rpc;
-  rowreg_shape(a.V, tpr, vpt, rpc);
-  if (vpt <= 1) return launch_dense_bt<DT, 1>(a, tpr, rpc, stream);
-  if (vpt <= 2) return launch_dense_bt<DT, 2>(a, tpr, rpc, stream);
-  if (vpt <= 4) return launch_dense_bt<DT, 4>(a, tpr, rpc, stream);
-  return launch_dense_bt<DT, 8>(a, tpr, rpc, stream);
+  int tpr = 0, vpt = 0, rpc = 0;
+  if (!rowreg_shape(a.V, tpr, vpt, rpc)) return cudaErrorInvalidValue;
+  switch (vpt) {
+    case 1:
+      return launch_dense_bt<DT, 1>(a, tpr, rpc, stream);
+    case 2:
+      return launch_dense_bt<DT, 2>(a, tpr, rpc, stream);
+    case 3:
+      return launch_dense_bt<DT, 3>(a, tpr, rpc, stream);
+    case 4:
+      return launch_dense_bt<DT, 4>(a, tpr, rpc, stream);
+    case 5:
+      return launch_dense_bt<DT, 5>(a, tpr, rpc, stream);
+    case 6:
+      return launch_dense_bt<DT, 6>(a, tpr, rpc, stream);
+    case 7:
+      return launch_dense_bt<DT, 7>(a, tpr, rpc, stream);
+    default:
+      return launch_dense_bt<DT, 8>(a, tpr, rpc, stream);
+  }
 }
 
 cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t stream) {
@@ -341,11 +336,8 @@ static cudaError_t launch_q_bt(const QRmsArgs& a, int tpr, cudaStream_t stream) 
 
 template <int QT, int DT>
 static cudaError_t launch_q_dt(const QRmsArgs& a, cudaStream_t stream) {
-  int tpr, vpt, rpc;
-  rowreg_shape(a.V, tpr, vpt, rpc);
-  if (tpr < 512 && vpt > 2) tpr *= 2;  // the decoder needs registers: two vectors per thread where possible
-  if (tpr < 64) tpr = 64;              // one row per CTA here: keep at least two warps busy
-  vpt = (a.V + tpr - 1) / tpr;
+  int tpr, vpt;
+  qrowreg_shape(a.V, tpr, vpt);
   if (vpt <= 1) return launch_q_bt<QT, DT, 1>(a, tpr, stream);
   if (vpt <= 2) return launch_q_bt<QT, DT, 2>(a, tpr, stream);
   if (vpt <= 4) return launch_q_bt<QT, DT, 4>(a, tpr, stream);

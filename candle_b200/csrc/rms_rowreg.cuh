@@ -69,15 +69,17 @@ struct RowRegSmem {
   float* pub;    // [4]: the resolved T(m), published by warp 0 of the row
   int4* chunks;  // [tpr] replay: {A, B - A, L, -}: while the sum's bit pattern stays in the
                  // binade that starts at L, a chunk adds A to an even and B to an odd one
+  int4* segs;    // [tpr] replay: the same for runs of chunks, {A, B - A, L, first | count << 16}
   uint4* rows;   // [V]: h, parked for the replay
   __device__ RowRegSmem(unsigned char* base, int rpc, int tpr, int V, int ty) {
     unsigned char* mine = base + static_cast<size_t>(ty) * slot_bytes(tpr);
     chunks = reinterpret_cast<int4*>(mine);
-    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 16);
+    segs = chunks + tpr;
+    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 32);
     pub = red + 32;
     rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * slot_bytes(tpr)) + static_cast<size_t>(ty) * V;
   }
-  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 16 + 36 * sizeof(float); }
+  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 32 + 36 * sizeof(float); }
   __host__ __device__ static size_t bytes(int rpc, int tpr, int V, bool with_rows) {
     return static_cast<size_t>(rpc) * slot_bytes(tpr) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
   }
@@ -164,7 +166,8 @@ __device__ __forceinline__ float sequential_sum_sq(const uint4* row, int v0, int
 // that covers the whole chunk) and falling back to plain sequential addition for the chunk
 // otherwise.  The checks make the result exact whatever the quality of the guesses.
 template <int DT>
-__device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, float* red, int V, int bar_id) {
+__device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, int4* segs, float* red, int V,
+                                            int bar_id) {
   const int tx = threadIdx.x, tpr = blockDim.x;
   const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
   const int vpc = (V + tpr - 1) / tpr;  // vectors per chunk
@@ -217,53 +220,85 @@ __device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, flo
     }
     ok = static_cast<int>(__float_as_uint(s1) >> 23) == e;  // the references stayed in the binade
   }
-  // record: {A, B - A, first bit pattern of the binade}; an unusable chunk gets a binade start no
-  // running sum can reach, so the range check below rejects it
-  const uint32_t inc_even = __float_as_uint(s0) - e0, inc_odd = __float_as_uint(s1) - (e0 + 1u);
-  chunks[tx] = make_int4(static_cast<int>(inc_even), static_cast<int>(inc_odd - inc_even),
-                         ok ? static_cast<int>(static_cast<uint32_t>(e) << 23) : -1, 0);
-  if (wpr > 1)
+  // chunk record: {A, B - A, first bit pattern of the binade}; an unusable chunk gets a binade
+  // start no running sum can reach, so the range check of the walk rejects it
+  uint32_t inc_even = __float_as_uint(s0) - e0, inc_odd = __float_as_uint(s1) - (e0 + 1u);
+  const uint32_t lo = ok ? (static_cast<uint32_t>(e) << 23) : 0xFFFFFFFFu;
+  chunks[tx] = make_int4(static_cast<int>(inc_even), static_cast<int>(inc_odd - inc_even), static_cast<int>(lo), 0);
+
+  // Runs of consecutive chunks of one warp that share a binade compose into one record: for an
+  // even start the run adds A1 + (A1 odd ? B2 : A2), for an odd start B1 + (B1 odd ? A2 : B2).
+  // A suffix scan restricted to the run leaves the whole run's record in its first lane.
+  const uint32_t key = ok ? lo : (0xFFFFFF00u | static_cast<uint32_t>(lane));  // unusable chunks stay alone
+  const uint32_t prev_key = __shfl_up_sync(0xFFFFFFFFu, key, 1);
+  const bool head = (lane == 0) || (key != prev_key);
+  const uint32_t heads = __ballot_sync(0xFFFFFFFFu, head);
+  const int sid = __popc(heads & (0xFFFFFFFFu >> (31 - lane)));  // 1-based run number inside the warp
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t nA = __shfl_down_sync(0xFFFFFFFFu, inc_even, d);
+    const uint32_t nB = __shfl_down_sync(0xFFFFFFFFu, inc_odd, d);
+    const int nsid = __shfl_down_sync(0xFFFFFFFFu, sid, d);
+    if (lane + d < 32 && nsid == sid) {
+      const uint32_t a2 = (inc_even & 1u) ? nB : nA;
+      const uint32_t b2 = (inc_odd & 1u) ? nA : nB;
+      inc_even += a2;
+      inc_odd += b2;
+    }
+  }
+  const int n_runs = __popc(heads);
+  int run_base = 0;
+  if (wpr > 1) {
+    if (lane == 0) red[16 + warp] = __int_as_float(n_runs);
     row_barrier(bar_id, tpr);
-  else
+    for (int i = 0; i < warp; ++i) run_base += __float_as_int(red[16 + i]);
+  }
+  if (head) {
+    // length of the run: distance to the next head of the warp
+    const uint32_t later = heads & ~(0xFFFFFFFFu >> (31 - lane));
+    const int len = (later ? __ffs(later) - 1 : 32) - lane;
+    segs[run_base + sid - 1] = make_int4(static_cast<int>(inc_even), static_cast<int>(inc_odd - inc_even),
+                                         static_cast<int>(lo), tx | (len << 16));
+  }
+  int total_runs = n_runs;
+  if (wpr > 1) {
+    row_barrier(bar_id, tpr);
+    total_runs = 0;
+    for (int i = 0; i < wpr; ++i) total_runs += __float_as_int(red[16 + i]);
+  } else {
     __syncwarp();
+  }
 
   float result = 0.0f;
   if (tx == 0) {
     uint32_t S = 0u;  // bits of the running sum (+0.0f)
     // One chunk: S stays in the chunk's binade before and after (the sum never decreases, so in
     // between as well) -> exact integer update; otherwise add the chunk's elements one by one.
-    auto step = [&](const int4& k, int c) {
-      const uint32_t lo = static_cast<uint32_t>(k.z);
+    auto chunk_step = [&](int c) {
+      const int4 k = chunks[c];
+      const uint32_t lo_c = static_cast<uint32_t>(k.z);
       const uint32_t S2 = S + static_cast<uint32_t>(k.x) + (S & 1u) * static_cast<uint32_t>(k.y);
-      if (S >= lo && (S2 - lo) < 0x800000u) {
+      if (S >= lo_c && (S2 - lo_c) < 0x800000u) {
         S = S2;
       } else {
         const int c0 = min(V, c * vpc), c1 = min(V, c0 + vpc);
         S = __float_as_uint(sequential_sum_sq<DT>(rows, c0, c1, __uint_as_float(S)));
       }
     };
-    int c = 0;
-    for (; c + 4 <= tpr; c += 4) {
-      // four chunks speculatively, branch-free, and one check for all of them
-      const int4 k0 = chunks[c], k1 = chunks[c + 1], k2 = chunks[c + 2], k3 = chunks[c + 3];
-      const uint32_t T1 = S + static_cast<uint32_t>(k0.x) + (S & 1u) * static_cast<uint32_t>(k0.y);
-      const uint32_t T2 = T1 + static_cast<uint32_t>(k1.x) + (T1 & 1u) * static_cast<uint32_t>(k1.y);
-      const uint32_t T3 = T2 + static_cast<uint32_t>(k2.x) + (T2 & 1u) * static_cast<uint32_t>(k2.y);
-      const uint32_t T4 = T3 + static_cast<uint32_t>(k3.x) + (T3 & 1u) * static_cast<uint32_t>(k3.y);
-      const bool all_ok = (S >= static_cast<uint32_t>(k0.z)) && ((T1 - static_cast<uint32_t>(k0.z)) < 0x800000u) &&
-                          (T1 >= static_cast<uint32_t>(k1.z)) && ((T2 - static_cast<uint32_t>(k1.z)) < 0x800000u) &&
-                          (T2 >= static_cast<uint32_t>(k2.z)) && ((T3 - static_cast<uint32_t>(k2.z)) < 0x800000u) &&
-                          (T3 >= static_cast<uint32_t>(k3.z)) && ((T4 - static_cast<uint32_t>(k3.z)) < 0x800000u);
-      if (all_ok) {
-        S = T4;
+    int4 cur = segs[0];
+    for (int r = 0; r < total_runs; ++r) {
+      const int4 nxt = segs[min(r + 1, total_runs - 1)];  // off the dependency chain
+      const uint32_t lo_r = static_cast<uint32_t>(cur.z);
+      const uint32_t S2 = S + static_cast<uint32_t>(cur.x) + (S & 1u) * static_cast<uint32_t>(cur.y);
+      if (S >= lo_r && (S2 - lo_r) < 0x800000u) {
+        S = S2;
       } else {
-        step(k0, c);
-        step(k1, c + 1);
-        step(k2, c + 2);
-        step(k3, c + 3);
+        // the run as a whole does not apply: take its chunks one at a time
+        const int first = cur.w & 0xFFFF, count = cur.w >> 16;
+        for (int c = first; c < first + count; ++c) chunk_step(c);
       }
+      cur = nxt;
     }
-    for (; c < tpr; ++c) step(chunks[c], c);
     result = __uint_as_float(S);
   }
   return result;
@@ -288,9 +323,11 @@ __device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, 
 // Resolves T(m) for the row held in h[] by the tpr threads of row slot threadIdx.y.  All threads
 // of the row must call it; rows synchronise on their own named barrier (id 1 + threadIdx.y).
 // `park` is V vectors of shared memory of this row that h can be written to when a replay is needed.
+// After a replay h is re-read from `park`, so that nothing has to stay in registers across the
+// (out-of-line) replay; `replayed` tells the caller to refresh its own long-lived registers too.
 template <int DT, int VPT>
-__device__ __forceinline__ float resolve_row_m(const uint4 (&h)[VPT], float lsum, float lw, int V, int n,
-                                               float eps, int flags, RowRegSmem& sm, uint4* park) {
+__device__ __forceinline__ float resolve_row_m(uint4 (&h)[VPT], float lsum, float lw, int V, int n, float eps,
+                                               int flags, RowRegSmem& sm, uint4* park, bool& replayed) {
   const int tx = threadIdx.x, tpr = blockDim.x;
   const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
   const float nf = static_cast<float>(n);
@@ -301,6 +338,7 @@ __device__ __forceinline__ float resolve_row_m(const uint4 (&h)[VPT], float lsum
   float s = warp_sum(lsum), w = warp_sum(lw);
   float m = 0.0f;
   bool replay;
+  replayed = false;
   if (wpr == 1) {
     if (fast) return round_to<DT>(rms_from_sum(s, nf, eps));
     replay = !decide_m<DT>(s, w, nf, eps, m) || force;  // warp-uniform
@@ -338,7 +376,7 @@ __device__ __forceinline__ float resolve_row_m(const uint4 (&h)[VPT], float lsum
       row_barrier(bar_id, tpr);
     else
       __syncwarp();
-    const float total = replay_sum_sq<DT>(park, sm.chunks, sm.red, V, bar_id);
+    const float total = replay_sum_sq<DT>(park, sm.chunks, sm.segs, sm.red, V, bar_id);
     if (wpr == 1) {
       m = __shfl_sync(0xFFFFFFFFu, round_to<DT>(rms_from_sum(total, nf, eps)), 0);
     } else {
@@ -346,6 +384,12 @@ __device__ __forceinline__ float resolve_row_m(const uint4 (&h)[VPT], float lsum
       row_barrier(bar_id, tpr);
       m = sm.pub[2];
     }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      int v = k * tpr + tx;
+      h[k] = v < V ? park[v] : make_uint4(0, 0, 0, 0);
+    }
+    replayed = true;
   }
   return m;
 }
@@ -398,6 +442,62 @@ __device__ __forceinline__ void write_rms_row(const uint4 (&h)[VPT], float m, co
     for (int i = 0; i < 4; ++i) ow[i] = mul2_rn<DT>(pack2<DT>(q[2 * i], q[2 * i + 1]), aw[i]);
     stg_stream(yrow + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
   }
+}
+
+// ---- lean variants for rows that are exactly VPT vectors per thread (no bounds guards) ----
+
+// Squares of one vector added to the tree-order sums; `weight` = n - 8 * (vector index).
+template <int DT>
+__device__ __forceinline__ void accumulate_vec_w(const uint4& h, float weight, float& lsum, float& lw) {
+  const uint32_t w[4] = {h.x, h.y, h.z, h.w};
+  float vs = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = unpack2<DT>(w[i]);
+    vs = fmaf(f.x, f.x, vs);
+    vs = fmaf(f.y, f.y, vs);
+  }
+  lsum += vs;
+  lw = fmaf(vs, weight, lw);
+}
+
+// y = T(T(h / m) * alpha) for one vector; r = 1/m when fast_div.
+template <int DT>
+__device__ __forceinline__ uint4 rms_output_vec(const uint4& h, const uint4& alpha, float m, float r, bool fast_div) {
+  const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+  const uint32_t aw[4] = {alpha.x, alpha.y, alpha.z, alpha.w};
+  float q[8];
+  if (fast_div) {
+    float amin = 3.0e38f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 hf = unpack2<DT>(hw[i]);
+      q[2 * i] = __fmul_rn(hf.x, r);
+      q[2 * i + 1] = __fmul_rn(hf.y, r);
+      amin = fminf(amin, fminf(fabsf(q[2 * i]), fabsf(q[2 * i + 1])));
+    }
+    // below 2^-100 the bf16 result may be subnormal, where the margin argument does not hold:
+    // recompute such elements with the exact quotient.  A vector with an exact zero also lands
+    // here, but costs only the comparisons.
+    if (amin < 7.8886091e-31f) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 hf = unpack2<DT>(hw[i]);
+        // exact zeros are already right; only tiny non-zero products need the division
+        if (fabsf(q[2 * i]) < 7.8886091e-31f && q[2 * i] != 0.0f) q[2 * i] = __fdiv_rn(hf.x, m);
+        if (fabsf(q[2 * i + 1]) < 7.8886091e-31f && q[2 * i + 1] != 0.0f) q[2 * i + 1] = __fdiv_rn(hf.y, m);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 hf = unpack2<DT>(hw[i]);
+      q[2 * i] = __fdiv_rn(hf.x, m);
+      q[2 * i + 1] = __fdiv_rn(hf.y, m);
+    }
+  }
+  return make_uint4(mul2_rn<DT>(pack2<DT>(q[0], q[1]), aw[0]), mul2_rn<DT>(pack2<DT>(q[2], q[3]), aw[1]),
+                    mul2_rn<DT>(pack2<DT>(q[4], q[5]), aw[2]), mul2_rn<DT>(pack2<DT>(q[6], q[7]), aw[3]));
 }
 
 }  // namespace cb200
