@@ -244,10 +244,17 @@ bool qrms_rowreg_supported(int dtype, int cols) {
 }
 
 // A persistent grid: as many CTAs as are resident at once, but no more than there is work.
+// `ctas_wanted` CTAs per SM should fit: the shared-memory carve-out is set to just what they need,
+// because every byte given to shared memory is taken from L1, and L1 is where the data of loads
+// in flight lands -- a maximal carve-out caps an SM at a fraction of the ~100 KB of outstanding
+// reads that saturating HBM takes.
 template <typename K>
-static cudaError_t persistent_grid(K kern, int threads, size_t smem, int64_t work_items, unsigned& grid) {
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                       static_cast<int>(cudaSharedmemCarveoutMaxShared));
+static cudaError_t persistent_grid(K kern, int threads, size_t smem, int ctas_wanted, int64_t work_items,
+                                   unsigned& grid) {
+  const size_t per_cta = smem + 1024;  // the driver reserves 1 KB per CTA
+  int percent = static_cast<int>((per_cta * ctas_wanted * 100 + 228 * 1024 - 1) / (228 * 1024));
+  if (percent > 100) percent = 100;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
   if (e != cudaSuccess) return e;
   if (smem > 48 * 1024) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -269,7 +276,7 @@ static cudaError_t launch_dense_t(const RmsRowRegArgs& a, int tpr, int rpc, cuda
   const size_t smem = RowRegSmem::bytes(rpc, tpr, a.V, with_rows);
   auto kern = rms_rowreg_kernel<DT, VPT, BT, GATHER>;
   unsigned grid = 1;
-  cudaError_t e = persistent_grid(kern, tpr * rpc, smem, (a.rows + rpc - 1) / rpc, grid);
+  cudaError_t e = persistent_grid(kern, tpr * rpc, smem, 768 / BT, (a.rows + rpc - 1) / rpc, grid);
   if (e != cudaSuccess) return e;
   kern<<<grid, dim3(tpr, rpc), smem, stream>>>(a);
   return cudaGetLastError();
@@ -321,7 +328,7 @@ static cudaError_t launch_q_t(const QRmsArgs& a, int tpr, cudaStream_t stream) {
       RowRegSmem::bytes(1, tpr, a.V, true) + static_cast<size_t>(kQStages) * stage_bytes + kQStages * 8 + 8;
   auto kern = qrms_rowreg_kernel<QT, DT, VPT, BT>;
   unsigned grid = 1;
-  cudaError_t e = persistent_grid(kern, tpr, smem, a.rows, grid);
+  cudaError_t e = persistent_grid(kern, tpr, smem, 1024 / BT, a.rows, grid);
   if (e != cudaSuccess) return e;
   kern<<<grid, tpr, smem, stream>>>(a);
   return cudaGetLastError();
