@@ -254,13 +254,13 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   const bool fused = out_dtype != CB200_DTYPE_F32 && cb200::qrms_rowreg_supported(out_dtype, hidden) &&
                      !(flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC));
   if (!fused) {
-    // Two launches through the caller's `gathered` buffer (f32 output, or a forced implementation).
-    if (gathered == nullptr)
-      return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: this dtype/flag combination needs a `gathered` buffer", name);
-    rc = cb200_qembedding(qtable, qtype, ids, gathered, vocab, hidden, n_ids, out_dtype, id_dtype, vocab_begin,
+    // Two launches (f32 output, a row length the fused kernel has no exact split for, or a forced
+    // implementation): decode into `gathered`, or into y itself, then normalise (in place if y).
+    void* mid = gathered != nullptr ? gathered : y;
+    rc = cb200_qembedding(qtable, qtype, ids, mid, vocab, hidden, n_ids, out_dtype, id_dtype, vocab_begin,
                           vocab_end, status, stream);
     if (rc != CB200_OK) return rc;
-    return cb200_rms_norm(gathered, nullptr, alpha, y, nullptr, n_ids, hidden, eps, out_dtype, flags, stream);
+    return cb200_rms_norm(mid, nullptr, alpha, y, nullptr, n_ids, hidden, eps, out_dtype, flags, stream);
   }
   cb200::QRmsArgs a{};
   a.qtable = static_cast<const unsigned char*>(qtable);

@@ -194,10 +194,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+#ifdef CB200_PROBE_SPINS
+__device__ unsigned long long g_probe_spins = 0;  // test-bench instrumentation only
+#endif
 // Returns false if the phase did not complete within the spin budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kWaitSpins; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) {
+#ifdef CB200_PROBE_SPINS
+      if (i > 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_probe_spins, static_cast<unsigned long long>(i));
+#endif
+      return true;
+    }
   }
   return false;
 }

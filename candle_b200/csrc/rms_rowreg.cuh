@@ -65,7 +65,7 @@ struct QRmsArgs {
 
 // Shared-memory layout of one CTA of the row-register kernels (per row slot `ty`).
 struct RowRegSmem {
-  float* red;    // [32]: warp partials of sum (0..15) and of the weighted sum (16..31)
+  float* red;    // [48]: warp partials of sum (0..15), of the weighted sum (16..31), of a minimum (32..47)
   float* pub;    // [4]: the resolved T(m), published by warp 0 of the row
   int4* chunks;  // [tpr] replay: {A, B - A, L, -}: while the sum's bit pattern stays in the
                  // binade that starts at L, a chunk adds A to an even and B to an odd one
@@ -76,10 +76,10 @@ struct RowRegSmem {
     chunks = reinterpret_cast<int4*>(mine);
     segs = chunks + tpr;
     red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 32);
-    pub = red + 32;
+    pub = red + 48;
     rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * slot_bytes(tpr)) + static_cast<size_t>(ty) * V;
   }
-  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 32 + 36 * sizeof(float); }
+  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 32 + 52 * sizeof(float); }
   __host__ __device__ static size_t bytes(int rpc, int tpr, int V, bool with_rows) {
     return static_cast<size_t>(rpc) * slot_bytes(tpr) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
   }
@@ -325,9 +325,12 @@ __device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, 
 // `park` is V vectors of shared memory of this row that h can be written to when a replay is needed.
 // After a replay h is re-read from `park`, so that nothing has to stay in registers across the
 // (out-of-line) replay; `replayed` tells the caller to refresh its own long-lived registers too.
+// `lmin` is a per-thread value whose minimum over the row is returned in `row_min` (the quantised
+// kernels use it to learn whether any block scale is small enough to need the guarded division).
 template <int DT, int VPT>
 __device__ __forceinline__ float resolve_row_m(uint4 (&h)[VPT], float lsum, float lw, int V, int n, float eps,
-                                               int flags, RowRegSmem& sm, uint4* park, bool& replayed) {
+                                               int flags, RowRegSmem& sm, uint4* park, bool& replayed,
+                                               float lmin = 0.0f, float* row_min = nullptr, bool pair_layout = false) {
   const int tx = threadIdx.x, tpr = blockDim.x;
   const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
   const float nf = static_cast<float>(n);
@@ -339,37 +342,50 @@ __device__ __forceinline__ float resolve_row_m(uint4 (&h)[VPT], float lsum, floa
   float m = 0.0f;
   bool replay;
   replayed = false;
+  if (row_min != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lmin = fminf(lmin, __shfl_xor_sync(0xFFFFFFFFu, lmin, o));
+  }
   if (wpr == 1) {
+    if (row_min != nullptr) *row_min = lmin;
     if (fast) return round_to<DT>(rms_from_sum(s, nf, eps));
     replay = !decide_m<DT>(s, w, nf, eps, m) || force;  // warp-uniform
   } else {
     if (lane == 0) {
       sm.red[warp] = s;
       sm.red[16 + warp] = w;
+      if (row_min != nullptr) sm.red[32 + warp] = lmin;
     }
     row_barrier(bar_id, tpr);
     if (warp == 0) {
       s = warp_sum(lane < wpr ? sm.red[lane] : 0.0f);
-      w = warp_sum(lane < wpr ? sm.red[16 + lane] : 0.0f);
       bool need = false;
-      if (fast)
+      if (fast) {
         m = round_to<DT>(rms_from_sum(s, nf, eps));
-      else
+      } else {
+        w = warp_sum(lane < wpr ? sm.red[16 + lane] : 0.0f);
         need = !decide_m<DT>(s, w, nf, eps, m) || force;
-      if (lane == 0) {
-        sm.pub[0] = m;
-        sm.pub[1] = need ? 1.0f : 0.0f;
       }
+      float mn = 0.0f;
+      if (row_min != nullptr) {
+        mn = lane < wpr ? sm.red[32 + lane] : 3.0e38f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
+      }
+      if (lane == 0) *reinterpret_cast<float4*>(sm.pub) = make_float4(m, need ? 1.0f : 0.0f, 0.0f, mn);
     }
     row_barrier(bar_id, tpr);
-    m = sm.pub[0];
-    replay = sm.pub[1] != 0.0f;  // row-uniform
+    const float4 pub = *reinterpret_cast<const float4*>(sm.pub);
+    m = pub.x;
+    replay = pub.y != 0.0f;  // row-uniform
+    if (row_min != nullptr) *row_min = pub.w;
   }
   if (replay) {
     // park h in shared memory and run the exact replay with all threads of the row
+    // register k holds vector k*tpr + tx, or with pair_layout vector 2*((k/2)*tpr + tx) + (k&1)
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
-      int v = k * tpr + tx;
+      int v = pair_layout ? 2 * ((k >> 1) * tpr + tx) + (k & 1) : k * tpr + tx;
       if (v < V) park[v] = h[k];
     }
     if (wpr > 1)
@@ -386,65 +402,13 @@ __device__ __forceinline__ float resolve_row_m(uint4 (&h)[VPT], float lsum, floa
     }
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
-      int v = k * tpr + tx;
+      int v = pair_layout ? 2 * ((k >> 1) * tpr + tx) + (k & 1) : k * tpr + tx;
       h[k] = v < V ? park[v] : make_uint4(0, 0, 0, 0);
     }
     replayed = true;
   }
   return m;
 }
-
-// y = T(T(h / m) * alpha) for the vectors this thread holds.
-template <int DT, int VPT>
-__device__ __forceinline__ void write_rms_row(const uint4 (&h)[VPT], float m, const uint4* __restrict__ alpha,
-                                              uint4* __restrict__ yrow, int V) {
-  const int tx = threadIdx.x, tpr = blockDim.x;
-  // 2^-60 <= m <= 2^60: the reciprocal is a normal number and the margin argument applies.
-  const bool fast_div = (DT == kDtBF16) && (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
-  const float r = fast_div ? __frcp_rn(m) : 0.0f;
-#pragma unroll
-  for (int k = 0; k < VPT; ++k) {
-    int v = k * tpr + tx;
-    if (v >= V) continue;
-    const uint4 av = __ldg(alpha + v);
-    const uint32_t hw[4] = {h[k].x, h[k].y, h[k].z, h[k].w};
-    const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
-    float q[8];
-    if (fast_div) {
-      float amin = 3.0e38f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 hf = unpack2<DT>(hw[i]);
-        q[2 * i] = __fmul_rn(hf.x, r);
-        q[2 * i + 1] = __fmul_rn(hf.y, r);
-        amin = fminf(amin, fminf(fabsf(q[2 * i]), fabsf(q[2 * i + 1])));
-      }
-      // below 2^-100 the bf16 result may be subnormal, where the margin argument does not hold:
-      // recompute such (non-zero) elements with the exact quotient.  Zeros land here too.
-      if (amin < 7.8886091e-31f) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 hf = unpack2<DT>(hw[i]);
-          if (fabsf(q[2 * i]) < 7.8886091e-31f) q[2 * i] = __fdiv_rn(hf.x, m);
-          if (fabsf(q[2 * i + 1]) < 7.8886091e-31f) q[2 * i + 1] = __fdiv_rn(hf.y, m);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 hf = unpack2<DT>(hw[i]);
-        q[2 * i] = __fdiv_rn(hf.x, m);
-        q[2 * i + 1] = __fdiv_rn(hf.y, m);
-      }
-    }
-    uint32_t ow[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) ow[i] = mul2_rn<DT>(pack2<DT>(q[2 * i], q[2 * i + 1]), aw[i]);
-    stg_stream(yrow + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
-  }
-}
-
-// ---- lean variants for rows that are exactly VPT vectors per thread (no bounds guards) ----
 
 // Squares of one vector added to the tree-order sums; `weight` = n - 8 * (vector index).
 template <int DT>
@@ -462,7 +426,8 @@ __device__ __forceinline__ void accumulate_vec_w(const uint4& h, float weight, f
 }
 
 // y = T(T(h / m) * alpha) for one vector; r = 1/m when fast_div.
-template <int DT>
+// GUARD = false is for callers that know no element of the row is tiny and non-zero.
+template <int DT, bool GUARD = true>
 __device__ __forceinline__ uint4 rms_output_vec(const uint4& h, const uint4& alpha, float m, float r, bool fast_div) {
   const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
   const uint32_t aw[4] = {alpha.x, alpha.y, alpha.z, alpha.w};
@@ -474,12 +439,12 @@ __device__ __forceinline__ uint4 rms_output_vec(const uint4& h, const uint4& alp
       float2 hf = unpack2<DT>(hw[i]);
       q[2 * i] = __fmul_rn(hf.x, r);
       q[2 * i + 1] = __fmul_rn(hf.y, r);
-      amin = fminf(amin, fminf(fabsf(q[2 * i]), fabsf(q[2 * i + 1])));
+      if (GUARD) amin = fminf(amin, fminf(fabsf(q[2 * i]), fabsf(q[2 * i + 1])));
     }
     // below 2^-100 the bf16 result may be subnormal, where the margin argument does not hold:
     // recompute such elements with the exact quotient.  A vector with an exact zero also lands
     // here, but costs only the comparisons.
-    if (amin < 7.8886091e-31f) {
+    if (GUARD && amin < 7.8886091e-31f) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float2 hf = unpack2<DT>(hw[i]);
@@ -498,6 +463,49 @@ __device__ __forceinline__ uint4 rms_output_vec(const uint4& h, const uint4& alp
   }
   return make_uint4(mul2_rn<DT>(pack2<DT>(q[0], q[1]), aw[0]), mul2_rn<DT>(pack2<DT>(q[2], q[3]), aw[1]),
                     mul2_rn<DT>(pack2<DT>(q[4], q[5]), aw[2]), mul2_rn<DT>(pack2<DT>(q[6], q[7]), aw[3]));
+}
+
+// Same as rms_output_vec for a vector whose elements are already widened to f32 (hf).
+template <int DT, bool GUARD>
+__device__ __forceinline__ uint4 rms_output_floats(const float (&hf)[8], const uint4& alpha, float m, float r,
+                                                   bool fast_div) {
+  const uint32_t aw[4] = {alpha.x, alpha.y, alpha.z, alpha.w};
+  float q[8];
+  if (fast_div) {
+    float amin = 3.0e38f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      q[i] = __fmul_rn(hf[i], r);
+      if (GUARD) amin = fminf(amin, fabsf(q[i]));
+    }
+    if (GUARD && amin < 7.8886091e-31f) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (fabsf(q[i]) < 7.8886091e-31f && q[i] != 0.0f) q[i] = __fdiv_rn(hf[i], m);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(hf[i], m);
+  }
+  return make_uint4(mul2_rn<DT>(pack2<DT>(q[0], q[1]), aw[0]), mul2_rn<DT>(pack2<DT>(q[2], q[3]), aw[1]),
+                    mul2_rn<DT>(pack2<DT>(q[4], q[5]), aw[2]), mul2_rn<DT>(pack2<DT>(q[6], q[7]), aw[3]));
+}
+
+// Widens a packed vector to f32 and adds its squares to the tree-order sums.
+template <int DT>
+__device__ __forceinline__ void widen_accumulate(const uint4& h, float weight, float (&hf)[8], float& lsum, float& lw) {
+  const uint32_t w[4] = {h.x, h.y, h.z, h.w};
+  float vs = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = unpack2<DT>(w[i]);
+    hf[2 * i] = f.x;
+    hf[2 * i + 1] = f.y;
+    vs = fmaf(f.x, f.x, vs);
+    vs = fmaf(f.y, f.y, vs);
+  }
+  lsum += vs;
+  lw = fmaf(vs, weight, lw);
 }
 
 }  // namespace cb200

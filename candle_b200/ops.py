@@ -202,8 +202,7 @@ def qembedding_rms_norm(qtensor, ids: torch.Tensor, alpha: torch.Tensor, eps: fl
         raise CandleError(f"vocab shard [{begin}, {end}) does not match the table's {local_vocab} rows")
     final = list(ids.shape) + [hidden]
     y = torch.empty(final, dtype=alpha.dtype, device=alpha.device)
-    need_g = return_gathered or alpha.dtype == torch.float32 or (flags & (FLAG_FORCE_LANEROW | FLAG_FORCE_GENERIC))
-    g = torch.empty(final, dtype=alpha.dtype, device=alpha.device) if need_g else None
+    g = torch.empty(final, dtype=alpha.dtype, device=alpha.device) if return_gathered else None
     st = status if status is not None else (new_status(alpha.device) if check else None)
     _cabi.call("cb200_qembedding_rms_norm", _ptr(qtensor.data), qtensor.dtype.value, _ptr(flat), _ptr(alpha), _ptr(y),
                _ptr(g), total, hidden, flat.shape[0], float(eps), _DTYPES[alpha.dtype], _ID_DTYPES[flat.dtype],
