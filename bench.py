@@ -3,10 +3,12 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5] [--impl reference]
 
 One "step" is one pass of the hot path over one batch of synthetic token rows.  The default
-workload is the single-GPU embed+norm configuration: C3, a GGUF Q8_0 table 128256x4096 looked up
-with Zipf(1.1) ids of shape 32x2048, decoded to bf16 and RMS-normalised (eps 1e-5).  Token rows are
-independent, so N GPUs each run the same number of rows (weak scaling, no collective); C4 is the
-vocab-sharded exception and needs N >= 2.
+workload is the largest single-GPU configuration and the one the row-sharded scaling target is
+stated on: C5, RMSNorm + fused residual add, bf16, hidden 8192, 65536 token rows (3.2 GB of
+compulsory HBM traffic per step).  Token rows are independent, so N GPUs each run the same number
+of rows (weak scaling, no collective); C4 is the vocab-sharded exception and needs N >= 2.  At
+N = 1 the other single-GPU configurations (C1, C2, C3) are measured briefly in the same run and
+reported under "other_workloads".
 
 Rank 0 prints ONE JSON line.  `value` is token rows per second with the inputs resident in HBM;
 `e2e` is the same through the public front end with ids coming from pinned host memory and the
@@ -165,15 +167,107 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+class Runner:
+    """Device-resident inputs of one workload plus the closures that launch it."""
+
+    def __init__(self, wl, dev, stream, st):
+        import torch
+
+        import candle_b200 as cb
+        from candle_b200 import _cabi
+        from helpers import from_oracle, ids_tensor, to_oracle
+        import oracle
+
+        self.wl, S = wl, wl.n_sets
+        if wl.name == "c1":
+            table = from_oracle(wl.table, wl.dtype, dev)
+            alpha = from_oracle(wl.alpha, wl.dtype, dev)
+            ids = [ids_tensor(i, dev) for i in wl.ids]
+            ys = [torch.empty(wl.rows, wl.hidden, dtype=table.dtype, device=dev) for _ in range(S)]
+
+            def launch(ids_ptr, y):
+                _cabi.call("cb200_embedding_rms_norm", table.data_ptr(), ids_ptr, alpha.data_ptr(), y.data_ptr(), None,
+                           wl.vocab, wl.hidden, wl.rows, wl.eps, 0, 1, 0, st.data_ptr(), stream.cuda_stream)
+
+            self.step = lambda i: launch(ids[i % S].data_ptr(), ys[i % S])
+            self.check = lambda: np.array_equal(
+                to_oracle(ys[0][:512]),
+                oracle.rms_norm(oracle.embedding(wl.table, wl.ids[0][:512]), wl.alpha, wl.eps, "f32"))
+            host_in = [torch.from_numpy(i.view(np.int32)).pin_memory() for i in wl.ids]
+            dev_in = torch.empty(wl.rows, dtype=torch.int32, device=dev)
+
+            def e2e_step(i, host_out):
+                dev_in.copy_(host_in[i % S], non_blocking=True)
+                launch(dev_in.data_ptr(), ys[0])
+                host_out.copy_(ys[0], non_blocking=True)
+            self.h2d = wl.rows * 4
+        elif wl.name == "c3":
+            q = cb.QTensor.from_raw(torch.from_numpy(wl.qtable), cb.GgmlDType.Q8_0, (wl.vocab, wl.hidden), device=dev)
+            alpha = from_oracle(wl.alpha, "bf16", dev)
+            ids = [ids_tensor(i, dev) for i in wl.ids]
+            ys = [torch.empty(wl.rows, wl.hidden, dtype=torch.bfloat16, device=dev) for _ in range(S)]
+
+            def launch(ids_ptr, y):
+                _cabi.call("cb200_qembedding_rms_norm", q.data.data_ptr(), q.dtype.value, ids_ptr, alpha.data_ptr(),
+                           y.data_ptr(), None, wl.vocab, wl.hidden, wl.rows, wl.eps, 2, 1, 0, wl.vocab, 0,
+                           st.data_ptr(), stream.cuda_stream)
+
+            self.step = lambda i: launch(ids[i % S].data_ptr(), ys[i % S])
+            self.check = lambda: np.array_equal(
+                to_oracle(ys[0][:512]),
+                oracle.rms_norm(oracle.qembedding(wl.qtable, wl.qtype, wl.ids[0][:512], "bf16"), wl.alpha, wl.eps, "bf16"))
+            host_in = [torch.from_numpy(i.view(np.int32)).pin_memory() for i in wl.ids]
+            dev_in = torch.empty(wl.rows, dtype=torch.int32, device=dev)
+
+            def e2e_step(i, host_out):
+                dev_in.copy_(host_in[i % S], non_blocking=True)
+                launch(dev_in.data_ptr(), ys[0])
+                host_out.copy_(ys[0], non_blocking=True)
+            self.h2d = wl.rows * 4
+        else:  # c2 / c5: dense rows + residual
+            reps = -(-wl.rows // wl.x[0].shape[0])
+            xs, rs, ys = [], [], []
+            for s in range(S):
+                bx = from_oracle(wl.x[s % len(wl.x)], "bf16", dev)
+                br = from_oracle(wl.res[s % len(wl.res)], "bf16", dev)
+                xs.append(bx.repeat(reps, 1)[: wl.rows].contiguous())
+                rs.append(br.repeat(reps, 1)[: wl.rows].contiguous())
+                ys.append(torch.empty(wl.rows, wl.hidden, dtype=torch.bfloat16, device=dev))
+            n = min(512, wl.x[0].shape[0])
+            h = oracle.add(wl.x[0][:n], wl.res[0][:n], "bf16")
+            if wl.name == "c2":
+                g, b = from_oracle(wl.gamma, "bf16", dev), from_oracle(wl.beta, "bf16", dev)
+
+                def launch(x, r, y):
+                    _cabi.call("cb200_layer_norm", x.data_ptr(), r.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(),
+                               None, wl.rows, wl.hidden, wl.eps, 2, 0, stream.cuda_stream)
+                self.check = lambda: np.array_equal(
+                    to_oracle(ys[0][:n]), oracle.layer_norm(h, wl.gamma, wl.beta, wl.eps, "bf16"))
+            else:
+                a = from_oracle(wl.alpha, "bf16", dev)
+
+                def launch(x, r, y):
+                    _cabi.call("cb200_rms_norm", x.data_ptr(), r.data_ptr(), a.data_ptr(), y.data_ptr(), None, wl.rows,
+                               wl.hidden, wl.eps, 2, 0, stream.cuda_stream)
+                self.check = lambda: np.array_equal(to_oracle(ys[0][:n]), oracle.rms_norm(h, wl.alpha, wl.eps, "bf16"))
+            self.step = lambda i: launch(xs[i % S], rs[i % S], ys[i % S])
+            host_x, host_r = xs[0].cpu().pin_memory(), rs[0].cpu().pin_memory()
+
+            def e2e_step(i, host_out):
+                xs[0].copy_(host_x, non_blocking=True)
+                rs[0].copy_(host_r, non_blocking=True)
+                launch(xs[0], rs[0], ys[0])
+                host_out.copy_(ys[0], non_blocking=True)
+            self.h2d = 2 * wl.rows * wl.hidden * 2
+        self.e2e_step = e2e_step
+        self.out_dtype = ys[0].dtype
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
 
-    import candle_b200 as cb
-    from candle_b200 import _cabi
-    from candle_b200.ops import _stream, new_status, raise_for_status
-    from helpers import from_oracle, ids_tensor, to_oracle
-    import oracle
+    from candle_b200.ops import new_status, raise_for_status
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -184,109 +278,13 @@ def gpu_arm(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "c4":
+        from candle_b200 import parallel
 
-    wl = Workload(args.workload, args.rows_scale)
-    if wl.name == "c4":
-        raise SystemExit("the vocab-sharded C4 workload needs the NCCL library: use --workload c4 with --gpus >= 2 "
-                         "once candle_b200.parallel is built")
+        return parallel.bench_c4(args, rank, world, dev)
+
     stream = torch.cuda.current_stream()
     st = new_status(dev)
-    S = wl.n_sets
-
-    # ---- device-resident inputs and the step closure ----
-    if wl.name in ("c1",):
-        table = from_oracle(wl.table, wl.dtype, dev)
-        alpha = from_oracle(wl.alpha, wl.dtype, dev)
-        ids = [ids_tensor(i, dev) for i in wl.ids]
-        ys = [torch.empty(wl.rows, wl.hidden, dtype=table.dtype, device=dev) for _ in range(S)]
-
-        def step(i):
-            _cabi.call("cb200_embedding_rms_norm", table.data_ptr(), ids[i % S].data_ptr(), alpha.data_ptr(),
-                       ys[i % S].data_ptr(), None, wl.vocab, wl.hidden, wl.rows, wl.eps, 0, 1, 0, st.data_ptr(),
-                       stream.cuda_stream)
-
-        def check():
-            want = oracle.rms_norm(oracle.embedding(wl.table, wl.ids[0][:512]), wl.alpha, wl.eps, "f32")
-            return np.array_equal(to_oracle(ys[0][:512]), want)
-        host_in = [torch.from_numpy(i.view(np.int32)).pin_memory() for i in wl.ids]
-        dev_in = [torch.empty(wl.rows, dtype=torch.int32, device=dev)]
-
-        def e2e_step(i, host_out):
-            dev_in[0].copy_(host_in[i % S], non_blocking=True)
-            _cabi.call("cb200_embedding_rms_norm", table.data_ptr(), dev_in[0].data_ptr(), alpha.data_ptr(),
-                       ys[0].data_ptr(), None, wl.vocab, wl.hidden, wl.rows, wl.eps, 0, 1, 0, st.data_ptr(),
-                       stream.cuda_stream)
-            host_out.copy_(ys[0], non_blocking=True)
-        h2d = wl.rows * 4
-    elif wl.name == "c3":
-        q = cb.QTensor.from_raw(torch.from_numpy(wl.qtable), cb.GgmlDType.Q8_0, (wl.vocab, wl.hidden), device=dev)
-        alpha = from_oracle(wl.alpha, "bf16", dev)
-        ids = [ids_tensor(i, dev) for i in wl.ids]
-        ys = [torch.empty(wl.rows, wl.hidden, dtype=torch.bfloat16, device=dev) for _ in range(S)]
-
-        def launch(ids_ptr, y):
-            _cabi.call("cb200_qembedding_rms_norm", q.data.data_ptr(), q.dtype.value, ids_ptr, alpha.data_ptr(),
-                       y.data_ptr(), None, wl.vocab, wl.hidden, wl.rows, wl.eps, 2, 1, 0, wl.vocab, 0, st.data_ptr(),
-                       stream.cuda_stream)
-
-        def step(i):
-            launch(ids[i % S].data_ptr(), ys[i % S])
-
-        def check():
-            sample = wl.ids[0][:512]
-            want = oracle.rms_norm(oracle.qembedding(wl.qtable, wl.qtype, sample, "bf16"), wl.alpha, wl.eps, "bf16")
-            return np.array_equal(to_oracle(ys[0][:512]), want)
-        host_in = [torch.from_numpy(i.view(np.int32)).pin_memory() for i in wl.ids]
-        dev_in = [torch.empty(wl.rows, dtype=torch.int32, device=dev)]
-
-        def e2e_step(i, host_out):
-            dev_in[0].copy_(host_in[i % S], non_blocking=True)
-            launch(dev_in[0].data_ptr(), ys[0])
-            host_out.copy_(ys[0], non_blocking=True)
-        h2d = wl.rows * 4
-    else:  # c2 / c5: dense rows + residual
-        tdt = torch.bfloat16
-        reps = -(-wl.rows // wl.x[0].shape[0])
-        xs, rs, ys = [], [], []
-        for s in range(S):
-            bx = from_oracle(wl.x[s % len(wl.x)], "bf16", dev)
-            br = from_oracle(wl.res[s % len(wl.res)], "bf16", dev)
-            xs.append(bx.repeat(reps, 1)[: wl.rows].contiguous())
-            rs.append(br.repeat(reps, 1)[: wl.rows].contiguous())
-            ys.append(torch.empty(wl.rows, wl.hidden, dtype=tdt, device=dev))
-        if wl.name == "c2":
-            g, b = from_oracle(wl.gamma, "bf16", dev), from_oracle(wl.beta, "bf16", dev)
-
-            def launch(x, r, y):
-                _cabi.call("cb200_layer_norm", x.data_ptr(), r.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), None,
-                           wl.rows, wl.hidden, wl.eps, 2, 0, stream.cuda_stream)
-
-            def check():
-                n = min(512, wl.x[0].shape[0])
-                want = oracle.layer_norm(oracle.add(wl.x[0][:n], wl.res[0][:n], "bf16"), wl.gamma, wl.beta, wl.eps, "bf16")
-                return np.array_equal(to_oracle(ys[0][:n]), want)
-        else:
-            a = from_oracle(wl.alpha, "bf16", dev)
-
-            def launch(x, r, y):
-                _cabi.call("cb200_rms_norm", x.data_ptr(), r.data_ptr(), a.data_ptr(), y.data_ptr(), None, wl.rows,
-                           wl.hidden, wl.eps, 2, 0, stream.cuda_stream)
-
-            def check():
-                n = min(512, wl.x[0].shape[0])
-                want = oracle.rms_norm(oracle.add(wl.x[0][:n], wl.res[0][:n], "bf16"), wl.alpha, wl.eps, "bf16")
-                return np.array_equal(to_oracle(ys[0][:n]), want)
-
-        def step(i):
-            launch(xs[i % S], rs[i % S], ys[i % S])
-        host_x, host_r = xs[0].cpu().pin_memory(), rs[0].cpu().pin_memory()
-
-        def e2e_step(i, host_out):
-            xs[0].copy_(host_x, non_blocking=True)
-            rs[0].copy_(host_r, non_blocking=True)
-            launch(xs[0], rs[0], ys[0])
-            host_out.copy_(ys[0], non_blocking=True)
-        h2d = 2 * wl.rows * wl.hidden * 2
 
     def barrier():
         if world > 1:
@@ -310,27 +308,52 @@ def gpu_arm(args):
             ms = t.item()
         return ms
 
+    wl = Workload(args.workload, args.rows_scale)
+    run = Runner(wl, dev, stream, st)
+
     # ---- parity spot check on this very workload before anything is timed ----
-    step(0)
+    run.step(0)
     torch.cuda.synchronize()
     raise_for_status(st)
-    parity_ok = bool(check())
+    parity_ok = bool(run.check())
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms = timed(step, args.steps, args.warmup)
+    ms = timed(run.step, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
     raise_for_status(st)
 
-    # ---- end to end: host ids in, host rows out, through the same call ----
-    host_out = torch.empty(wl.rows, wl.hidden, dtype=ys[0].dtype).pin_memory()
+    # ---- end to end: host buffers in, host rows out, through the same call ----
+    host_out = torch.empty(wl.rows, wl.hidden, dtype=run.out_dtype).pin_memory()
     e2e_steps = max(2, min(args.steps, 10))
-    e2e_ms = timed(lambda i: e2e_step(i, host_out), e2e_steps, 1)
+    e2e_ms = timed(lambda i: run.e2e_step(i, host_out), e2e_steps, 1)
     d2h = host_out.numel() * host_out.element_size()
 
+    peak, peak_kind = measured_peak()
+    others = {}
+    if world == 1 and not args.no_sweep:
+        del run, host_out
+        torch.cuda.empty_cache()
+        for name in ("c1", "c2", "c3", "c5"):
+            if name == wl.name:
+                continue
+            w2 = Workload(name)
+            r2 = Runner(w2, dev, stream, st)
+            r2.step(0)
+            torch.cuda.synchronize()
+            ok2 = bool(r2.check())
+            k = 20
+            ms2 = timed(r2.step, k, 3) / k
+            gbs = w2.bytes_per_step / (ms2 * 1e-3) / 1e9
+            others[name] = {"workload": w2.desc, "ms_per_step": ms2, "tokens_per_s": w2.rows / (ms2 * 1e-3),
+                            "achieved_gbs": gbs, "frac_of_measured_peak": gbs / peak,
+                            "parity": "bit-exact on 512 rows" if ok2 else "MISMATCH"}
+            parity_ok = parity_ok and ok2
+            del r2, w2
+            torch.cuda.empty_cache()
+
     if rank == 0:
-        peak, peak_kind = measured_peak()
         ms_per_step = ms / args.steps
         achieved = wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9
         out = {
@@ -342,17 +365,20 @@ def gpu_arm(args):
             "dtype": wl.dtype, "data": "synthetic (seed 0)",
             "config": {"workload": wl.desc, "rows_per_gpu": wl.rows, "hidden": wl.hidden,
                        "parallelism": f"token rows x{world}, no collective",
-                       "l2": f"rotating {S} buffer set(s); working set per step {wl.bytes_per_step / 1e6:.0f} MB vs 126 MB L2"},
+                       "l2": f"rotating {wl.n_sets} buffer set(s); working set per step "
+                             f"{wl.bytes_per_step / 1e6:.0f} MB vs 126 MB L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": wl.bytes_per_step,
                          "traffic": NCU_TRAFFIC_BYTES.get(wl.name)},
             "e2e": {"value": world * wl.rows * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
+                    "h2d_bytes_per_step": run_h2d(wl), "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": args.steps,
             "parity": "bit-exact vs CPU oracle on the first 512 rows" if parity_ok else "MISMATCH vs CPU oracle",
             "clocks": clocks,
         }
+        if others:
+            out["other_workloads"] = others
         if not args.no_cpu and world == 1:
             out["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(out), flush=True)
@@ -360,6 +386,10 @@ def gpu_arm(args):
         dist.destroy_process_group()
     if not parity_ok:
         raise SystemExit(3)
+
+
+def run_h2d(wl):
+    return wl.rows * 4 if wl.name in ("c1", "c3") else 2 * wl.rows * wl.hidden * 2
 
 
 # ------------------------------------------------------------------------------------------------
@@ -463,7 +493,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the brief runs of the other workloads")
     ap.add_argument("--rows-scale", type=float, default=1.0, help="c5 only: fraction of 65536 rows")
     ap.add_argument("--impl", default="candle_b200", choices=["candle_b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
