@@ -38,7 +38,9 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (null until a capture of that kernel exists)
-NCU_TRAFFIC_BYTES = {"c3": None, "c5": None, "c2": None, "c1": None, "c4": None}
+# c5: 364.5 MB measured on the 8192-row capture, scaled x8 (traffic grows with rows);
+# see profiles/rms_rowreg_kernel__c5_rmsnorm_residual_bf16_h8192.md
+NCU_TRAFFIC_BYTES = {"c3": None, "c5": 2916000000, "c2": None, "c1": None, "c4": None}
 
 
 def measured_peak():
