@@ -214,6 +214,166 @@ __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const Lan
 }
 
 // ---------------------------------------------------------------------------------------------
+// Short rows (V = 32 * VPL 16-byte vectors, VPL <= 4; e.g. 768 bf16 columns): a pipelined,
+// persistent version of the same scheme.  One 512-thread CTA per SM walks tiles of 32 rows.
+//   * the tile's x rows (and residual rows) arrive in shared memory by asynchronous 16-byte
+//     copies, which bypass L1 and registers, so the large shared-memory carve-out this kernel
+//     needs does not limit the bytes in flight;
+//   * each thread turns the vectors it copied itself into h = T(x + residual) in place;
+//   * warp 0 walks the 32 rows sequentially, one lane per row, while ALL warps have already
+//     started the copies of the next tile into the other buffer;
+//   * every warp then normalises two rows with gamma / beta held widened in registers.
+// ---------------------------------------------------------------------------------------------
+constexpr int kShortThreads = 512;
+constexpr int kShortWarps = kShortThreads / 32;
+constexpr int kShortRows = 32;
+
+template <int DT, int OP, int VPL>
+__global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const LaneRowArgs a) {
+  constexpr int PV = Elem<DT>::kPerVec;
+  constexpr int V = 32 * VPL;
+  constexpr int kPitchVecs = V + 1;  // odd number of 16-byte units: conflict-free lane-per-row walk
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* xbuf[2] = {reinterpret_cast<uint4*>(smem_raw), reinterpret_cast<uint4*>(smem_raw) + kShortRows * kPitchVecs};
+  uint4* rbuf = reinterpret_cast<uint4*>(smem_raw) + 2 * kShortRows * kPitchVecs;
+  float2* stats = reinterpret_cast<float2*>(rbuf + kShortRows * kPitchVecs);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint4* gx = static_cast<const uint4*>(a.x);
+  const uint4* gr = static_cast<const uint4*>(a.res);
+  uint4* gs = static_cast<uint4*>(a.sum_out);
+  uint4* gy = static_cast<uint4*>(a.y);
+  const bool has_res = gr != nullptr;
+  const int64_t n_tiles = (a.rows + kShortRows - 1) / kShortRows;
+
+  // gamma / beta of this lane's vectors, widened once
+  float gam[VPL][PV], bet[VPL][PV];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    vec_to_floats<DT>(__ldg(static_cast<const uint4*>(a.alpha) + lane + 32 * j), gam[j]);
+    if (OP == kOpLayerNorm) vec_to_floats<DT>(__ldg(static_cast<const uint4*>(a.beta) + lane + 32 * j), bet[j]);
+  }
+
+  // this thread copies / converts / normalises rows warp and warp + 16 of a tile, vectors lane + 32 j
+  auto issue_tile = [&](int64_t tile, int buf) {
+    if (tile < n_tiles) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int r = warp + kShortWarps * rr;
+        const int64_t row = tile * kShortRows + r;
+        if (row < a.rows) {
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) {
+            const int v = lane + 32 * j;
+            cp_async16(xbuf[buf] + r * kPitchVecs + v, gx + row * V + v);
+            if (has_res) cp_async16(rbuf + r * kPitchVecs + v, gr + row * V + v);
+          }
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  int buf = 0;
+  issue_tile(blockIdx.x, 0);
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, buf ^= 1) {
+    const int64_t row0 = tile * kShortRows;
+    const int live = static_cast<int>(min(static_cast<int64_t>(kShortRows), a.rows - row0));
+    cp_async_wait_all();
+    if (has_res) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int r = warp + kShortWarps * rr;
+        if (r < live) {
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) {
+            const int v = lane + 32 * j;
+            uint4* px = xbuf[buf] + r * kPitchVecs + v;
+            uint4 h;
+            if constexpr (DT == kDtF32) {
+              float fa[PV], fb[PV];
+              vec_to_floats<DT>(*px, fa);
+              vec_to_floats<DT>(rbuf[r * kPitchVecs + v], fb);
+#pragma unroll
+              for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
+              h = floats_to_vec<DT>(fa);
+            } else {
+              h = add_round_vec<DT>(*px, rbuf[r * kPitchVecs + v]);  // rounds the sum to T, as Tensor::add does
+            }
+            *px = h;
+            if (gs != nullptr) stg_stream(gs + (row0 + r) * V + v, h);
+          }
+        }
+      }
+    } else if (gs != nullptr) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int r = warp + kShortWarps * rr;
+        if (r < live) {
+#pragma unroll
+          for (int j = 0; j < VPL; ++j) stg_stream(gs + (row0 + r) * V + lane + 32 * j, xbuf[buf][r * kPitchVecs + lane + 32 * j]);
+        }
+      }
+    }
+    __syncthreads();  // the tile's h is complete; rbuf and the other x buffer are free
+    issue_tile(tile + gridDim.x, buf ^ 1);
+
+    // ---- pass 1: one lane per row, strictly sequential f32 accumulation ----
+    if (warp == 0 && lane < live) {
+      const uint4* row = xbuf[buf] + lane * kPitchVecs;
+      float s = 0.0f, s2 = 0.0f;
+#pragma unroll 4
+      for (int v = 0; v < V; ++v) {
+        float f[PV];
+        vec_to_floats<DT>(row[v], f);
+#pragma unroll
+        for (int e = 0; e < PV; ++e) {
+          if (OP == kOpLayerNorm) s = __fadd_rn(s, f[e]);
+          // for 16-bit inputs f*f is exact in f32, so the fused form rounds like add(s2, mul(f, f))
+          s2 = (DT == kDtF32) ? __fadd_rn(s2, __fmul_rn(f[e], f[e])) : fmaf(f[e], f[e], s2);
+        }
+      }
+      const float nf = static_cast<float>(a.n);
+      if (OP == kOpLayerNorm) {
+        float mean = __fdiv_rn(s, nf);
+        float var = __fsub_rn(__fdiv_rn(s2, nf), __fmul_rn(mean, mean));
+        stats[lane] = make_float2(mean, __frcp_rn(__fsqrt_rn(__fadd_rn(var, a.eps))));
+      } else {
+        stats[lane] = make_float2(round_to<DT>(rms_from_sum(s2, nf, a.eps)), 0.0f);
+      }
+    }
+    __syncthreads();
+
+    // ---- pass 2: normalise and store ----
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int r = warp + kShortWarps * rr;
+      if (r < live) {
+        const float2 st = stats[r];
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          const int v = lane + 32 * j;
+          float h[PV], o[PV];
+          vec_to_floats<DT>(xbuf[buf][r * kPitchVecs + v], h);
+          if (OP == kOpLayerNorm) {
+#pragma unroll
+            for (int e = 0; e < PV; ++e)
+              o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), gam[j][e]), bet[j][e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), gam[j][e]);
+          }
+          stg_stream(gy + (row0 + r) * V + v, floats_to_vec<DT>(o));
+        }
+      }
+    }
+    // no barrier: the next iteration writes the other x buffer and rbuf, and `stats` only after
+    // its own first barrier, which every thread reaches after finishing this pass
+  }
+  cp_async_wait_all();
+}
+
+// ---------------------------------------------------------------------------------------------
 // Any-shape fallback: one thread per row, scalar accesses, same arithmetic and order.  Used for
 // rows that are not 16-byte multiples, misaligned bases, and rows too long for shared memory.
 // ---------------------------------------------------------------------------------------------
@@ -304,6 +464,43 @@ static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+template <int DT, int OP, int VPL>
+static cudaError_t launch_shortrow_t(const LaneRowArgs& a, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(3) * kShortRows * (32 * VPL + 1) * 16 + kShortRows * sizeof(float2);
+  auto kern = norm_shortrow_kernel<DT, OP, VPL>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           static_cast<int>((smem + 1024) * 100 / (228 * 1024) + 1));
+  if (e != cudaSuccess) return e;
+  int64_t tiles = (a.rows + kShortRows - 1) / kShortRows;
+  int64_t grid = tiles < kSmCount ? tiles : kSmCount;
+  kern<<<static_cast<unsigned>(grid), kShortThreads, smem, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// Rows of exactly 32, 64, 96 or 128 vectors, dense source, enough rows to fill the device.
+static bool shortrow_applies(int dtype, const LaneRowArgs& a) {
+  const int esz = dtype == kDtF32 ? 4 : 2;
+  const int64_t row_bytes = static_cast<int64_t>(a.n) * esz;
+  return a.ids == nullptr && row_bytes % 512 == 0 && row_bytes / 512 >= 1 && row_bytes / 512 <= 4 &&
+         a.rows >= 2 * kShortRows * kSmCount;
+}
+
+template <int DT, int OP>
+static cudaError_t launch_shortrow_dt(const LaneRowArgs& a, cudaStream_t stream) {
+  switch (a.n * Elem<DT>::kBytes / 512) {
+    case 1:
+      return launch_shortrow_t<DT, OP, 1>(a, stream);
+    case 2:
+      return launch_shortrow_t<DT, OP, 2>(a, stream);
+    case 3:
+      return launch_shortrow_t<DT, OP, 3>(a, stream);
+    default:
+      return launch_shortrow_t<DT, OP, 4>(a, stream);
+  }
+}
+
 template <int DT, int OP>
 static cudaError_t launch_generic_t(const LaneRowArgs& a, cudaStream_t stream) {
   const int threads = 64;
@@ -314,6 +511,16 @@ static cudaError_t launch_generic_t(const LaneRowArgs& a, cudaStream_t stream) {
 
 template <int OP>
 static cudaError_t dispatch_dt(int dtype, bool generic, const LaneRowArgs& a, cudaStream_t stream) {
+  if (!generic && shortrow_applies(dtype, a)) {
+    switch (dtype) {
+      case kDtF32:
+        return launch_shortrow_dt<kDtF32, OP>(a, stream);
+      case kDtF16:
+        return launch_shortrow_dt<kDtF16, OP>(a, stream);
+      default:
+        return launch_shortrow_dt<kDtBF16, OP>(a, stream);
+    }
+  }
   switch (dtype) {
     case kDtF32:
       return generic ? launch_generic_t<kDtF32, OP>(a, stream) : launch_lanerow_t<kDtF32, OP>(a, stream);

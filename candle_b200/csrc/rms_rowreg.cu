@@ -91,30 +91,56 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
 }
 
 // ---------------------------------------------------------------------------------------------
-// Quantised source: each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... through a ring of
-// shared-memory row buffers that thread 0 keeps filled with bulk copies kQStages-1 rows ahead.
-// Thread 0 is the only reader of the ids; it loads each id one iteration before it needs it and
-// publishes what kind of row a ring slot holds, so no id load sits on anybody's critical path.
+// Quantised source.  A CTA is a set of independent row slots (threadIdx.y), each served by a
+// warp (two for rows beyond 4096 columns): a slot walks its own rows, owns a small ring of
+// shared-memory row buffers that its first lane keeps filled with bulk copies, and synchronises
+// with nobody else -- per row there is one decode, one set of warp shuffles, no CTA barrier.
+// The slot's first lane is the only reader of the ids: it loads each id one iteration before it
+// needs it and publishes what kind of row a ring slot holds.  A replay decodes the staged blocks
+// again in contiguous chunks instead of parking h.
 // ---------------------------------------------------------------------------------------------
-constexpr int kQStages = 8;
 constexpr int kRowDecode = 0, kRowMasked = 1, kRowBadId = 2;
 
-template <int QT, int DT, int VPT, int BT>
-__global__ void __launch_bounds__(BT, 1024 / BT) qrms_rowreg_kernel(const QRmsArgs a) {
+template <int QT, int DT>
+struct QuantRow {
+  const unsigned char* buf;
+  __device__ __forceinline__ uint4 vec(int v) const { return decode_vec8<QT, DT>(buf, v); }
+};
+
+// Per-slot shared-memory layout; `stages` buffers of `stage_bytes` first (16-byte aligned).
+struct QSlot {
+  unsigned char* ring;
+  unsigned char* head;  // RowRegSmem area
+  uint64_t* bars;
+  volatile int* kinds;       // [stages]
+  volatile int* abort_flag;  // a bounded wait of this slot ran out
+  __device__ QSlot(unsigned char* base, int stages, int stage_bytes, int tpr) {
+    ring = base;
+    head = base + static_cast<size_t>(stages) * stage_bytes;
+    bars = reinterpret_cast<uint64_t*>(head + RowRegSmem::slot_bytes(tpr));
+    kinds = reinterpret_cast<volatile int*>(bars + stages);
+    abort_flag = kinds + stages;
+  }
+  __host__ __device__ static size_t bytes(int stages, int stage_bytes, int tpr) {
+    size_t b = static_cast<size_t>(stages) * stage_bytes + RowRegSmem::slot_bytes(tpr) + stages * 8 + (stages + 1) * 4;
+    return (b + 15) & ~static_cast<size_t>(15);
+  }
+};
+
+template <int QT, int DT, int HB>
+__global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, int stages) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int tx = threadIdx.x, tpr = blockDim.x;
-  RowRegSmem sm(smem_raw, 1, tpr, a.V, 0);
-  const size_t core_bytes = RowRegSmem::bytes(1, tpr, a.V, true);
+  const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
   const int stage_bytes = (a.row_bytes + 15) & ~15;
-  unsigned char* stage0 = smem_raw + core_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage0 + kQStages * stage_bytes);
-  volatile int* kinds = reinterpret_cast<volatile int*>(bars + kQStages);  // [kQStages]
-  volatile int* abort_flag = kinds + kQStages;
+  QSlot slot(smem_raw + ty * QSlot::bytes(stages, stage_bytes, tpr), stages, stage_bytes, tpr);
+  RowRegSmem sm(slot.head, 1, tpr, a.V, 0);
+  const int bar_id = 1 + ty;
 
-  const int64_t first = blockIdx.x, step = gridDim.x;
-  uint64_t id_ahead = 0;  // thread 0: id of the next row to be issued, already loaded
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * rpc + ty;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * rpc;
+  uint64_t id_ahead = 0;  // issuing lane: id of the next row to be issued, already loaded
 
-  // thread 0: classify row (whose id is `id`), publish its kind and start its copy into `stage`
+  // issuing lane: classify row (whose id is `id`), publish its kind, start its copy into `stage`
   auto issue = [&](int64_t row, uint64_t id, int stage) {
     int kind = kRowDecode;
     if (id >= static_cast<uint64_t>(a.vocab)) {
@@ -123,123 +149,89 @@ __global__ void __launch_bounds__(BT, 1024 / BT) qrms_rowreg_kernel(const QRmsAr
     } else if (id < static_cast<uint64_t>(a.vocab_begin) || id >= static_cast<uint64_t>(a.vocab_end)) {
       kind = kRowMasked;
     }
-    kinds[stage] = kind;
-    if (kind == kRowDecode && a.bulk) {
+    slot.kinds[stage] = kind;
+    if (kind == kRowDecode) {
       const unsigned char* src = a.qtable + (id - a.vocab_begin) * static_cast<uint64_t>(a.row_bytes);
-      mbar_expect_tx(&bars[stage], static_cast<uint32_t>(a.row_bytes));
-      bulk_g2s(stage0 + stage * stage_bytes, src, static_cast<uint32_t>(a.row_bytes), &bars[stage]);
+      mbar_expect_tx(&slot.bars[stage], static_cast<uint32_t>(a.row_bytes));
+      bulk_g2s(slot.ring + stage * stage_bytes, src, static_cast<uint32_t>(a.row_bytes), &slot.bars[stage]);
     }
   };
 
   if (tx == 0) {
-    for (int s = 0; s < kQStages; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < stages; ++s) mbar_init(&slot.bars[s], 1);
     mbar_init_fence();
-    *abort_flag = 0;
-    for (int j = 0; j < kQStages - 1; ++j) {
+    *slot.abort_flag = 0;
+    for (int j = 0; j < stages - 1; ++j) {
       const int64_t r = first + j * step;
       if (r < a.rows) issue(r, read_id(a.ids, a.id_dtype, r), j);
     }
-    const int64_t r = first + static_cast<int64_t>(kQStages - 1) * step;
+    const int64_t r = first + static_cast<int64_t>(stages - 1) * step;
     if (r < a.rows) id_ahead = read_id(a.ids, a.id_dtype, r);
   }
-  __syncthreads();
-
-  // Each thread owns VPT/2 half blocks: vectors 2p and 2p+1 for p = j*tpr + tx.  They share one
-  // block scale and make 32 contiguous output bytes.
-  constexpr int HB = VPT / 2;
-  uint4 al[VPT];
-  float wv[VPT];
-#pragma unroll
-  for (int j = 0; j < HB; ++j) {
-    const int p = j * tpr + tx;
-    al[2 * j] = __ldg(a.alpha + 2 * p);
-    al[2 * j + 1] = __ldg(a.alpha + 2 * p + 1);
-    wv[2 * j] = static_cast<float>(a.n - 16 * p);
-    wv[2 * j + 1] = static_cast<float>(a.n - 16 * p - 8);
-  }
+  if (tpr > 32)
+    row_barrier(bar_id, tpr);
+  else
+    __syncwarp();
 
   uint32_t phase = 0;  // one parity bit per stage
   int stage = 0;
   for (int64_t row = first; row < a.rows; row += step) {
-    unsigned char* buf = stage0 + stage * stage_bytes;
-    // The stage used by the previous row is free: its readers finished before that row's first
-    // barrier, which thread 0 has passed.  Refill it with the row kQStages-1 ahead, then start
-    // loading the id that the next iteration will need.
+    unsigned char* buf = slot.ring + stage * stage_bytes;
+    // The buffer of the previous row is free (its readers are past that row's last use of it,
+    // which precedes the slot-wide synchronisation every row ends with).  Refill it with the row
+    // stages-1 ahead, then start loading the id the next iteration will need.
     if (tx == 0) {
-      const int64_t ahead = row + static_cast<int64_t>(kQStages - 1) * step;
+      const int64_t ahead = row + static_cast<int64_t>(stages - 1) * step;
       if (ahead < a.rows) {
-        issue(ahead, id_ahead, stage == 0 ? kQStages - 1 : stage - 1);
+        issue(ahead, id_ahead, stage == 0 ? stages - 1 : stage - 1);
         if (ahead + step < a.rows) id_ahead = read_id(a.ids, a.id_dtype, ahead + step);
       }
     }
-    const int kind = kinds[stage];
+    const int kind = slot.kinds[stage];
     if (kind == kRowDecode) {
-      if (a.bulk) {
-        // A wait that runs out is recorded and acted on after the row's barriers, where the
-        // whole CTA sees the flag and can leave together.
-        if (!mbar_wait(&bars[stage], (phase >> stage) & 1u)) *abort_flag = 1;
-        phase ^= 1u << stage;
-      } else {
-        // rows that are not 16-byte multiples: cooperative 2-byte copies (ids re-read: slow path)
-        const uint64_t id = read_id(a.ids, a.id_dtype, row);
-        const uint16_t* src =
-            reinterpret_cast<const uint16_t*>(a.qtable + (id - a.vocab_begin) * static_cast<uint64_t>(a.row_bytes));
-        uint16_t* dst = reinterpret_cast<uint16_t*>(buf);
-        for (int i = tx; i < a.row_bytes / 2; i += tpr) dst[i] = src[i];
-        __syncthreads();
-      }
+      // a wait that runs out is recorded and acted on after the row's synchronisation points,
+      // where the whole slot sees the flag and can leave together
+      if (!mbar_wait(&slot.bars[stage], (phase >> stage) & 1u)) *slot.abort_flag = 1;
+      phase ^= 1u << stage;
     }
 
-    uint4 h[VPT];
-    float hf[VPT][8];
+    // Each thread owns HB half blocks: vectors 2p and 2p+1 for p = j*tpr + tx share one scale
+    // and make 32 contiguous output bytes.
+    uint4 h[2 * HB];
     float lsum = 0.0f, lw = 0.0f, dmin = 3.0e38f;
     if (kind == kRowDecode) {
 #pragma unroll
       for (int j = 0; j < HB; ++j) {
+        const int p = j * tpr + tx;
         float d;
-        decode_half_block<QT, DT>(buf, j * tpr + tx, h[2 * j], h[2 * j + 1], d);
-        widen_accumulate<DT>(h[2 * j], wv[2 * j], hf[2 * j], lsum, lw);
-        widen_accumulate<DT>(h[2 * j + 1], wv[2 * j + 1], hf[2 * j + 1], lsum, lw);
+        decode_half_block<QT, DT>(buf, p, h[2 * j], h[2 * j + 1], d);
+        const float w0 = static_cast<float>(a.n - 16 * p);
+        accumulate_vec_w<DT>(h[2 * j], w0, lsum, lw);
+        accumulate_vec_w<DT>(h[2 * j + 1], w0 - 8.0f, lsum, lw);
         d = fabsf(d);
         dmin = fminf(dmin, d == 0.0f ? 3.0e38f : d);  // a zero scale makes exact zeros only
       }
     } else {
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        h[k] = (kind == kRowMasked) ? neg_zero_vec<DT>() : make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) hf[k][i] = (kind == kRowMasked) ? -0.0f : 0.0f;
-      }
+      for (int k = 0; k < 2 * HB; ++k) h[k] = (kind == kRowMasked) ? neg_zero_vec<DT>() : make_uint4(0, 0, 0, 0);
     }
-    bool replayed;
+    bool need;
     float row_dmin;
-    const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm, sm.rows, replayed, dmin, &row_dmin,
-                                           /*pair_layout=*/true);
-    if (replayed) {  // rare: nothing was kept in registers across the replay
-      float s0 = 0.0f, s1 = 0.0f;
+    float m = decide_row<DT>(lsum, lw, a.n, a.eps, a.flags, sm, need, dmin, &row_dmin);
+    if (need && kind == kRowDecode) {
+      m = replay_row<DT, QuantRow<QT, DT>>(QuantRow<QT, DT>{buf}, a.V, a.n, a.eps, sm);
 #pragma unroll
-      for (int j = 0; j < HB; ++j) {
-        const int p = j * tpr + tx;
-        al[2 * j] = __ldg(a.alpha + 2 * p);
-        al[2 * j + 1] = __ldg(a.alpha + 2 * p + 1);
-        wv[2 * j] = static_cast<float>(a.n - 16 * p);
-        wv[2 * j + 1] = static_cast<float>(a.n - 16 * p - 8);
-        widen_accumulate<DT>(h[2 * j], 0.0f, hf[2 * j], s0, s1);
-        widen_accumulate<DT>(h[2 * j + 1], 0.0f, hf[2 * j + 1], s0, s1);
+      for (int j = 0; j < HB; ++j) {  // nothing was kept in registers across the replay
+        float d;
+        decode_half_block<QT, DT>(buf, j * tpr + tx, h[2 * j], h[2 * j + 1], d);
       }
     }
-    if (*abort_flag) {
+    if (tpr == 32) __syncwarp();  // (wider slots passed named barriers inside decide_row)
+    if (*slot.abort_flag) {
       if (tx == 0) {
         report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row, 0, a.vocab);
-        // bounded second chance for every copy still in flight, so that none lands in shared
-        // memory after the CTA has retired
-        for (int j = 0; j < kQStages - 1; ++j) {
-          const int64_t r = row + static_cast<int64_t>(j) * step;
-          const int s = (stage + j) % kQStages;
-          if (r >= a.rows || kinds[s] != kRowDecode) continue;
-          const uint32_t par = (j == 0) ? (((phase >> s) & 1u) ^ 1u) : ((phase >> s) & 1u);
-          mbar_wait(&bars[s], par);
-        }
+        for (int j = 0; j < stages; ++j)  // bounded second chance for the copies still in flight
+          if (slot.kinds[j] == kRowDecode) mbar_wait(&slot.bars[j], (phase >> j) & 1u);
       }
       return;
     }
@@ -262,22 +254,24 @@ __global__ void __launch_bounds__(BT, 1024 / BT) qrms_rowreg_kernel(const QRmsAr
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          stg_stream(yr + 2 * p, rms_output_floats<DT, false>(hf[2 * j], al[2 * j], m, r, fast_div));
-          stg_stream(yr + 2 * p + 1, rms_output_floats<DT, false>(hf[2 * j + 1], al[2 * j + 1], m, r, fast_div));
+          stg_stream(yr + 2 * p, rms_output_vec<DT, false>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div));
+          stg_stream(yr + 2 * p + 1, rms_output_vec<DT, false>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
         }
       } else {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          stg_stream(yr + 2 * p, rms_output_floats<DT, true>(hf[2 * j], al[2 * j], m, r, fast_div));
-          stg_stream(yr + 2 * p + 1, rms_output_floats<DT, true>(hf[2 * j + 1], al[2 * j + 1], m, r, fast_div));
+          stg_stream(yr + 2 * p, rms_output_vec<DT, true>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div));
+          stg_stream(yr + 2 * p + 1, rms_output_vec<DT, true>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
         }
       }
     }
-    stage = stage + 1 == kQStages ? 0 : stage + 1;
-    // No barrier here: every thread finished decoding `buf` before the row's first barrier and
-    // reads the published m before the next row's first barrier, so the refill issued at the
-    // top of the next iteration and the next row's scratch writes cannot race with this row.
+    // all lanes are done with `buf` (decode and, if any, replay) before the next refill
+    if (tpr > 32)
+      row_barrier(bar_id, tpr);
+    else
+      __syncwarp();
+    stage = stage + 1 == stages ? 0 : stage + 1;
   }
 }
 
@@ -300,17 +294,17 @@ static bool rowreg_shape(int V, int& tpr, int& vpt, int& rpc) {
   return false;
 }
 
-// Shape of the quantised-source kernel: one row per CTA, V == tpr * vpt exactly, preferring two
-// vectors per thread (the decoder needs the registers).
-static bool qrowreg_shape(int V, int& tpr, int& vpt) {
-  static const int prefs[] = {2, 4, 6, 8};  // whole half blocks (vector pairs) per thread
-  for (int cand : prefs) {
-    if (V % cand != 0) continue;
-    const int t = V / cand;
-    if (t % 32 != 0 || t < 64 || t > 512) continue;
-    tpr = t;
-    vpt = cand;
-    return true;
+// Shape of the quantised-source kernel: HB half blocks (16 elements) per thread, a warp per row
+// up to 4096 columns.  V == 2 * HB * tpr exactly.
+static bool qrowreg_shape(int V, int& tpr, int& hb) {
+  for (int t = 32; t <= 128; t <<= 1) {
+    for (int cand = 4; cand >= 1; --cand) {
+      if (V == 2 * cand * t) {
+        tpr = t;
+        hb = cand;
+        return true;
+      }
+    }
   }
   return false;
 }
@@ -322,8 +316,8 @@ bool rms_rowreg_supported(int dtype, int cols) {
 }
 
 bool qrms_rowreg_supported(int dtype, int cols) {
-  int tpr, vpt;
-  return (dtype == kDtBF16 || dtype == kDtF16) && cols % 32 == 0 && cols <= 32768 && qrowreg_shape(cols / 8, tpr, vpt);
+  int tpr, hb;
+  return (dtype == kDtBF16 || dtype == kDtF16) && cols % 32 == 0 && qrowreg_shape(cols / 8, tpr, hb);
 }
 
 // A persistent grid: as many CTAs as are resident at once, but no more than there is work.
@@ -404,39 +398,37 @@ cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t st
   return dtype == kDtBF16 ? launch_dense_dt<kDtBF16>(a, stream) : launch_dense_dt<kDtF16>(a, stream);
 }
 
-template <int QT, int DT, int VPT, int BT>
+template <int QT, int DT, int HB>
 static cudaError_t launch_q_t(const QRmsArgs& a, int tpr, cudaStream_t stream) {
+  const int rpc = 128 / tpr;  // row slots per 128-thread CTA
+  const int ctas = 5;         // CTAs per SM the register cap admits (640 threads); more ran slower
   const int stage_bytes = (a.row_bytes + 15) & ~15;
-  const size_t smem = RowRegSmem::bytes(1, tpr, a.V, true) + static_cast<size_t>(kQStages) * stage_bytes +
-                      kQStages * 8 + (kQStages + 1) * 4 + 4;
-  auto kern = qrms_rowreg_kernel<QT, DT, VPT, BT>;
+  // ring depth: what about 200 KB of shared memory per SM allows, at least 2 (one row ahead)
+  int stages = 2;
+  while (stages < 4 && QSlot::bytes(stages + 1, stage_bytes, tpr) * rpc * ctas <= 200 * 1024) ++stages;
+  const size_t smem = QSlot::bytes(stages, stage_bytes, tpr) * rpc;
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  auto kern = qrms_rowslot_kernel<QT, DT, HB>;
   unsigned grid = 1;
-  cudaError_t e = persistent_grid(kern, tpr, smem, 1024 / BT, a.rows, grid);
+  cudaError_t e = persistent_grid(kern, 128, smem, ctas, (a.rows + rpc - 1) / rpc, grid);
   if (e != cudaSuccess) return e;
-  kern<<<grid, tpr, smem, stream>>>(a);
+  kern<<<grid, dim3(tpr, rpc), smem, stream>>>(a, stages);
   return cudaGetLastError();
-}
-
-template <int QT, int DT, int VPT>
-static cudaError_t launch_q_bt(const QRmsArgs& a, int tpr, cudaStream_t stream) {
-  if (tpr <= 128) return launch_q_t<QT, DT, VPT, 128>(a, tpr, stream);
-  if (tpr <= 256) return launch_q_t<QT, DT, VPT, 256>(a, tpr, stream);
-  return launch_q_t<QT, DT, VPT, 512>(a, tpr, stream);
 }
 
 template <int QT, int DT>
 static cudaError_t launch_q_dt(const QRmsArgs& a, cudaStream_t stream) {
-  int tpr = 0, vpt = 0;
-  if (!qrowreg_shape(a.V, tpr, vpt)) return cudaErrorInvalidValue;
-  switch (vpt) {
+  int tpr = 0, hb = 0;
+  if (!qrowreg_shape(a.V, tpr, hb)) return cudaErrorInvalidValue;
+  switch (hb) {
+    case 1:
+      return launch_q_t<QT, DT, 1>(a, tpr, stream);
     case 2:
-      return launch_q_bt<QT, DT, 2>(a, tpr, stream);
-    case 4:
-      return launch_q_bt<QT, DT, 4>(a, tpr, stream);
-    case 6:
-      return launch_q_bt<QT, DT, 6>(a, tpr, stream);
+      return launch_q_t<QT, DT, 2>(a, tpr, stream);
+    case 3:
+      return launch_q_t<QT, DT, 3>(a, tpr, stream);
     default:
-      return launch_q_bt<QT, DT, 8>(a, tpr, stream);
+      return launch_q_t<QT, DT, 4>(a, tpr, stream);
   }
 }
 

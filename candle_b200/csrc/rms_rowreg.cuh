@@ -136,11 +136,18 @@ __device__ __forceinline__ void accumulate_vec(const uint4& h, int vec_index, in
 
 // Sequential sum of squares over vectors [v0, v1) of a row in shared memory, continuing from s:
 // candle's order and roundings (candle-nn/src/ops.rs:484-490).
-template <int DT>
-__device__ __forceinline__ float sequential_sum_sq(const uint4* row, int v0, int v1, float s) {
+// A row of 16-bit elements as seen by the replay: vector v = elements [8v, 8v+8).  ParkedRow reads
+// h parked in shared memory; the quantised kernels pass an accessor that decodes on the fly.
+struct ParkedRow {
+  const uint4* p;
+  __device__ __forceinline__ uint4 vec(int v) const { return p[v]; }
+};
+
+template <int DT, typename Row>
+__device__ __forceinline__ float sequential_sum_sq(const Row& row, int v0, int v1, float s) {
 #pragma unroll 2
   for (int v = v0; v < v1; ++v) {
-    uint4 q = row[v];
+    uint4 q = row.vec(v);
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -165,8 +172,8 @@ __device__ __forceinline__ float sequential_sum_sq(const uint4* row, int v0, int
 // true value really is in the assumed binade before and after each chunk (the sum is monotone, so
 // that covers the whole chunk) and falling back to plain sequential addition for the chunk
 // otherwise.  The checks make the result exact whatever the quality of the guesses.
-template <int DT>
-__device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, int4* segs, float* red, int V,
+template <int DT, typename Row>
+__device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* segs, float* red, int V,
                                             int bar_id) {
   const int tx = threadIdx.x, tpr = blockDim.x;
   const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
@@ -175,7 +182,7 @@ __device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, int
 
   float sig = 0.0f;
   for (int v = v0; v < v1; ++v) {
-    uint4 q = rows[v];
+    uint4 q = rows.vec(v);
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -207,7 +214,7 @@ __device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, int
   float s0 = __uint_as_float(e0), s1 = __uint_as_float(e0 + 1u);
   if (ok) {
     for (int v = v0; v < v1; ++v) {
-      uint4 q = rows[v];
+      uint4 q = rows.vec(v);
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -282,7 +289,7 @@ __device__ __noinline__ float replay_sum_sq(const uint4* rows, int4* chunks, int
         S = S2;
       } else {
         const int c0 = min(V, c * vpc), c1 = min(V, c0 + vpc);
-        S = __float_as_uint(sequential_sum_sq<DT>(rows, c0, c1, __uint_as_float(S)));
+        S = __float_as_uint(sequential_sum_sq<DT, Row>(rows, c0, c1, __uint_as_float(S)));
       }
     };
     int4 cur = segs[0];
@@ -323,14 +330,14 @@ __device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, 
 // Resolves T(m) for the row held in h[] by the tpr threads of row slot threadIdx.y.  All threads
 // of the row must call it; rows synchronise on their own named barrier (id 1 + threadIdx.y).
 // `park` is V vectors of shared memory of this row that h can be written to when a replay is needed.
-// After a replay h is re-read from `park`, so that nothing has to stay in registers across the
-// (out-of-line) replay; `replayed` tells the caller to refresh its own long-lived registers too.
-// `lmin` is a per-thread value whose minimum over the row is returned in `row_min` (the quantised
-// kernels use it to learn whether any block scale is small enough to need the guarded division).
-template <int DT, int VPT>
-__device__ __forceinline__ float resolve_row_m(uint4 (&h)[VPT], float lsum, float lw, int V, int n, float eps,
-                                               int flags, RowRegSmem& sm, uint4* park, bool& replayed,
-                                               float lmin = 0.0f, float* row_min = nullptr, bool pair_layout = false) {
+// Step 1 of resolving T(m) for the row whose per-thread partial sums are (lsum, lw): the tpr
+// threads of row slot threadIdx.y reduce them (named barrier id 1 + threadIdx.y for rows wider
+// than a warp) and warp 0 of the row decides.  Returns T(m) if `need_replay` comes back false;
+// otherwise only replay_row can tell.  `lmin` is a per-thread value whose minimum over the row
+// is returned in `row_min` when that pointer is given.
+template <int DT>
+__device__ __forceinline__ float decide_row(float lsum, float lw, int n, float eps, int flags, RowRegSmem& sm,
+                                            bool& need_replay, float lmin = 0.0f, float* row_min = nullptr) {
   const int tx = threadIdx.x, tpr = blockDim.x;
   const int lane = tx & 31, warp = tx >> 5, wpr = tpr >> 5;
   const float nf = static_cast<float>(n);
@@ -340,69 +347,88 @@ __device__ __forceinline__ float resolve_row_m(uint4 (&h)[VPT], float lsum, floa
 
   float s = warp_sum(lsum), w = warp_sum(lw);
   float m = 0.0f;
-  bool replay;
-  replayed = false;
   if (row_min != nullptr) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) lmin = fminf(lmin, __shfl_xor_sync(0xFFFFFFFFu, lmin, o));
   }
   if (wpr == 1) {
     if (row_min != nullptr) *row_min = lmin;
-    if (fast) return round_to<DT>(rms_from_sum(s, nf, eps));
-    replay = !decide_m<DT>(s, w, nf, eps, m) || force;  // warp-uniform
-  } else {
-    if (lane == 0) {
-      sm.red[warp] = s;
-      sm.red[16 + warp] = w;
-      if (row_min != nullptr) sm.red[32 + warp] = lmin;
+    if (fast) {
+      need_replay = false;
+      return round_to<DT>(rms_from_sum(s, nf, eps));
     }
-    row_barrier(bar_id, tpr);
-    if (warp == 0) {
-      s = warp_sum(lane < wpr ? sm.red[lane] : 0.0f);
-      bool need = false;
-      if (fast) {
-        m = round_to<DT>(rms_from_sum(s, nf, eps));
-      } else {
-        w = warp_sum(lane < wpr ? sm.red[16 + lane] : 0.0f);
-        need = !decide_m<DT>(s, w, nf, eps, m) || force;
-      }
-      float mn = 0.0f;
-      if (row_min != nullptr) {
-        mn = lane < wpr ? sm.red[32 + lane] : 3.0e38f;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
-      }
-      if (lane == 0) *reinterpret_cast<float4*>(sm.pub) = make_float4(m, need ? 1.0f : 0.0f, 0.0f, mn);
-    }
-    row_barrier(bar_id, tpr);
-    const float4 pub = *reinterpret_cast<const float4*>(sm.pub);
-    m = pub.x;
-    replay = pub.y != 0.0f;  // row-uniform
-    if (row_min != nullptr) *row_min = pub.w;
+    need_replay = !decide_m<DT>(s, w, nf, eps, m) || force;  // warp-uniform
+    return m;
   }
-  if (replay) {
-    // park h in shared memory and run the exact replay with all threads of the row
-    // register k holds vector k*tpr + tx, or with pair_layout vector 2*((k/2)*tpr + tx) + (k&1)
+  if (lane == 0) {
+    sm.red[warp] = s;
+    sm.red[16 + warp] = w;
+    if (row_min != nullptr) sm.red[32 + warp] = lmin;
+  }
+  row_barrier(bar_id, tpr);
+  if (warp == 0) {
+    s = warp_sum(lane < wpr ? sm.red[lane] : 0.0f);
+    bool need = false;
+    if (fast) {
+      m = round_to<DT>(rms_from_sum(s, nf, eps));
+    } else {
+      w = warp_sum(lane < wpr ? sm.red[16 + lane] : 0.0f);
+      need = !decide_m<DT>(s, w, nf, eps, m) || force;
+    }
+    float mn = 0.0f;
+    if (row_min != nullptr) {
+      mn = lane < wpr ? sm.red[32 + lane] : 3.0e38f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
+    }
+    if (lane == 0) *reinterpret_cast<float4*>(sm.pub) = make_float4(m, need ? 1.0f : 0.0f, 0.0f, mn);
+  }
+  row_barrier(bar_id, tpr);
+  const float4 pub = *reinterpret_cast<const float4*>(sm.pub);
+  need_replay = pub.y != 0.0f;  // row-uniform
+  if (row_min != nullptr) *row_min = pub.w;
+  return pub.x;
+}
+
+// Step 2, for the few rows that need it: T(m) from the exact sequential-order sum of the row as
+// `row` presents it.  All tpr threads of the row call it; whatever `row` reads must be complete
+// and visible to them (the caller synchronises after parking).
+template <int DT, typename Row>
+__device__ __forceinline__ float replay_row(const Row& row, int V, int n, float eps, RowRegSmem& sm) {
+  const int tx = threadIdx.x, tpr = blockDim.x, wpr = tpr >> 5;
+  const int bar_id = 1 + threadIdx.y;
+  const float nf = static_cast<float>(n);
+  const float total = replay_sum_sq<DT, Row>(row, sm.chunks, sm.segs, sm.red, V, bar_id);
+  if (wpr == 1) return __shfl_sync(0xFFFFFFFFu, round_to<DT>(rms_from_sum(total, nf, eps)), 0);
+  if (tx == 0) sm.pub[2] = round_to<DT>(rms_from_sum(total, nf, eps));
+  row_barrier(bar_id, tpr);
+  return sm.pub[2];
+}
+
+// Both steps for a row held in registers (register k = vector k*tpr + tx): on a replay h is parked
+// in `park`, and re-read from it afterwards so that nothing has to stay in registers across the
+// out-of-line replay; `replayed` tells the caller to refresh its own long-lived registers too.
+template <int DT, int VPT>
+__device__ __forceinline__ float resolve_row_m(uint4 (&h)[VPT], float lsum, float lw, int V, int n, float eps,
+                                               int flags, RowRegSmem& sm, uint4* park, bool& replayed) {
+  const int tx = threadIdx.x, tpr = blockDim.x, wpr = tpr >> 5;
+  bool need;
+  float m = decide_row<DT>(lsum, lw, n, eps, flags, sm, need);
+  replayed = false;
+  if (need) {
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
-      int v = pair_layout ? 2 * ((k >> 1) * tpr + tx) + (k & 1) : k * tpr + tx;
+      int v = k * tpr + tx;
       if (v < V) park[v] = h[k];
     }
     if (wpr > 1)
-      row_barrier(bar_id, tpr);
+      row_barrier(1 + threadIdx.y, tpr);
     else
       __syncwarp();
-    const float total = replay_sum_sq<DT>(park, sm.chunks, sm.segs, sm.red, V, bar_id);
-    if (wpr == 1) {
-      m = __shfl_sync(0xFFFFFFFFu, round_to<DT>(rms_from_sum(total, nf, eps)), 0);
-    } else {
-      if (tx == 0) sm.pub[2] = round_to<DT>(rms_from_sum(total, nf, eps));
-      row_barrier(bar_id, tpr);
-      m = sm.pub[2];
-    }
+    m = replay_row<DT, ParkedRow>(ParkedRow{park}, V, n, eps, sm);
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
-      int v = pair_layout ? 2 * ((k >> 1) * tpr + tx) + (k & 1) : k * tpr + tx;
+      int v = k * tpr + tx;
       h[k] = v < V ? park[v] : make_uint4(0, 0, 0, 0);
     }
     replayed = true;

@@ -174,6 +174,25 @@ def test_layer_norm_matches_oracle(cb, dtype, residual, impl):
         assert_norm_equal(y, want, dtype)
 
 
+@pytest.mark.parametrize("dtype,cols", [("bf16", 768), ("f16", 1024), ("f32", 384), ("bf16", 256), ("f32", 128)])
+def test_short_rows_many_rows_take_the_pipelined_kernel(cb, dtype, cols):
+    # >= 9472 short rows: layer norm (all dtypes) and f32 RMS norm run the pipelined 32-row-tile
+    # kernel; a ragged last tile is included.
+    rng = np.random.default_rng(31)
+    rows = 9472 + 37
+    x, r = randn(rng, (rows, cols), dtype), randn(rng, (rows, cols), dtype)
+    g, b = randn(rng, (cols,), dtype, 1.0, 0.1), randn(rng, (cols,), dtype, 0.0, 0.1)
+    h = oracle.add(x, r, dtype, threads=0)
+    xt, rt, gt, bt = (from_oracle(v, dtype) for v in (x, r, g, b))
+    y, hs = cb.layer_norm(xt, gt, bt, 1e-12, residual=rt, return_sum=True)
+    assert np.array_equal(to_oracle(hs), h)
+    assert_norm_equal(y, oracle.layer_norm(h, g, b, 1e-12, dtype), dtype)
+    assert_norm_equal(cb.layer_norm(xt, gt, bt, 1e-5), oracle.layer_norm(x, g, b, 1e-5, dtype), dtype)
+    # RMS norm through the same kernel (forced for the 16-bit types, native for f32)
+    y = cb.rms_norm(xt, gt, 1e-5, residual=rt, flags=cb.FLAG_FORCE_LANEROW)
+    assert_norm_equal(y, oracle.rms_norm(h, g, 1e-5, dtype), dtype)
+
+
 def test_rms_norm_many_rows_exercises_the_replay_path(cb):
     # 8192 rows of 8192 bf16 columns: a few percent of the rows cannot be decided by the interval
     # test and are replayed sequentially; the result must still be bit-equal everywhere.
