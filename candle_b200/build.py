@@ -30,7 +30,8 @@ def _stale(target: str, sources: list[str]) -> bool:
         return True
     t = os.path.getmtime(target)
     deps = list(sources) + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    deps.append(os.path.join(os.path.dirname(_HERE), "include", "candle_b200.h"))
+    inc = os.path.join(os.path.dirname(_HERE), "include")
+    deps += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
@@ -64,3 +65,4 @@ if __name__ == "__main__":
     import sys
 
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_nccl(force="--force" in sys.argv))

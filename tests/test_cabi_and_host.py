@@ -18,12 +18,12 @@ def built_lib():
     return build.build()  # no-op when up to date
 
 
-def header_functions():
-    """name -> number of parameters, parsed from every include/*.h."""
+def header_functions(only=None):
+    """name -> number of parameters, parsed from every include/*.h (or just the file `only`)."""
     out = {}
     inc = os.path.join(ROOT, "include")
     for fn in sorted(os.listdir(inc)):
-        if not fn.endswith(".h"):
+        if not fn.endswith(".h") or (only is not None and fn != only):
             continue
         text = open(os.path.join(inc, fn)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
@@ -34,21 +34,33 @@ def header_functions():
 
 
 def test_library_exports_every_declared_symbol(built_lib):
+    from candle_b200 import build
+
     lib = ctypes.CDLL(built_lib)
-    declared = header_functions()
+    declared = header_functions("candle_b200.h")
     assert len(declared) >= 10
     for name in declared:
-        assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
+        assert hasattr(lib, name), f"{name} is declared in include/candle_b200.h but not exported"
     assert lib.cb200_version() == 100
+    nccl_path = build.build_nccl()
+    import torch  # noqa: F401  (its libnccl.so.2 satisfies the dependency, as in a real process)
+
+    nccl_lib = ctypes.CDLL(nccl_path)
+    declared = header_functions("candle_b200_nccl.h")
+    assert len(declared) >= 4
+    for name in declared:
+        assert hasattr(nccl_lib, name), f"{name} is declared in include/candle_b200_nccl.h but not exported"
+    assert len(header_functions()) == len(header_functions("candle_b200.h")) + len(declared)
 
 
 def test_ctypes_signatures_match_the_header(built_lib):
-    from candle_b200 import _cabi
+    from candle_b200 import _cabi, _nccl
 
-    declared = header_functions()
-    assert set(_cabi.SIGNATURES) == set(declared)
-    for name, argtypes in _cabi.SIGNATURES.items():
-        assert len(argtypes) == declared[name], name
+    for mod, header in ((_cabi, "candle_b200.h"), (_nccl, "candle_b200_nccl.h")):
+        declared = header_functions(header)
+        assert set(mod.SIGNATURES) == set(declared)
+        for name, argtypes in mod.SIGNATURES.items():
+            assert len(argtypes) == declared[name], name
 
 
 def test_argument_validation_needs_no_device(built_lib):

@@ -1,0 +1,89 @@
+"""Multi-GPU checks (need >= 2 CUDA devices; skipped otherwise): the vocab-sharded lookup summed by
+NCCL equals the unsharded CPU oracle bit for bit (-0.0 included), with and without the
+reduce-scatter variant, and row sharding reproduces the unsharded rows."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import candle_b200 as cb
+        import oracle
+        from candle_b200.parallel import ShardedQEmbedding, row_shard, vocab_shard
+        from helpers import from_oracle, ids_tensor, make_qtable, randn, to_oracle
+
+        ok = True
+        for qtype, gq in (("q4_0", cb.GgmlDType.Q4_0), ("q8_0", cb.GgmlDType.Q8_0)):
+            rng = np.random.default_rng(41)
+            vocab, hidden, n = 256 * world, 4096, 512 * world
+            qt = make_qtable(rng, qtype, vocab, hidden)
+            qt[:, :2] = 0  # scale +0 in the first block of every row: +-0.0 values
+            ids = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+            alpha = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+            b, e = vocab_shard(vocab, rank, world)
+            local = cb.QTensor.from_raw(torch.from_numpy(qt[b:e]), gq, (e - b, hidden), device=dev)
+            emb = ShardedQEmbedding(local, vocab, rank, world, torch.bfloat16)
+            want_rows = oracle.qembedding(qt, qtype, ids, "bf16")
+            want = oracle.rms_norm(want_rows, alpha, 1e-5, "bf16")
+            got_rows = emb.forward(ids_tensor(ids, dev))
+            ok = ok and np.array_equal(to_oracle(got_rows), want_rows)
+            y = emb.forward_rms_norm(ids_tensor(ids, dev), from_oracle(alpha, "bf16", dev), 1e-5)
+            ok = ok and np.array_equal(to_oracle(y), want)
+            ys = emb.forward_rms_norm(ids_tensor(ids, dev), from_oracle(alpha, "bf16", dev), 1e-5, scatter=True)
+            rb, re = row_shard(n, rank, world)
+            ok = ok and np.array_equal(to_oracle(ys), want[rb:re])
+        # the same through the C entry point with a communicator of its own
+        from candle_b200 import _nccl
+        from candle_b200.ops import _stream, new_status
+
+        uid = [_nccl.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        comm = _nccl.comm_init(world, uid[0], rank)
+        tq, tids, ta = torch.from_numpy(qt[b:e]).to(dev), ids_tensor(ids, dev), from_oracle(alpha, "bf16", dev)
+        y = torch.empty(n, hidden, dtype=torch.bfloat16, device=dev)
+        scratch = torch.empty(n, hidden, dtype=torch.bfloat16, device=dev)
+        st = new_status(dev)
+        _nccl.call("cb200_sharded_qembedding_rms_norm", comm, tq.data_ptr(), 8, tids.data_ptr(), ta.data_ptr(),
+                   y.data_ptr(), scratch.data_ptr(), scratch.numel() * 2, vocab, hidden, n, 1e-5, 2, 1, b, e, 0,
+                   st.data_ptr(), _stream(y))
+        torch.cuda.synchronize()
+        ok = ok and np.array_equal(to_oracle(y), want) and st[0].item() == 0
+        _nccl.comm_destroy(comm)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_sharded_lookup_over_nccl():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two CUDA devices")
+    import torch.multiprocessing as mp
+
+    world = min(4, torch.cuda.device_count())
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)

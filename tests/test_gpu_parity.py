@@ -363,6 +363,41 @@ def test_qembedding_rms_norm_matches_oracle(cb, qtype, dtype):
                            y.view(torch.int16 if dtype != "f32" else torch.int32))
 
 
+def test_sharded_entry_point_single_rank(cb):
+    # cb200_sharded_qembedding_rms_norm with a one-rank communicator: lookup into caller scratch,
+    # all-reduce (identity), norm.  Must equal the oracle and the fused single-GPU call.
+    from candle_b200 import _nccl
+    from candle_b200.ops import _stream, new_status, raise_for_status
+
+    rng = np.random.default_rng(29)
+    vocab, hidden, n = 300, 4096, 700
+    comm = _nccl.comm_init(1, _nccl.unique_id(), 0)
+    try:
+        for qtype, code in (("q8_0", 8), ("q4_0", 2)):
+            qt = make_qtable(rng, qtype, vocab, hidden)
+            ids = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+            alpha = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+            want_rows = oracle.qembedding(qt, qtype, ids, "bf16")
+            want = oracle.rms_norm(want_rows, alpha, 1e-5, "bf16")
+            tq, tids, ta = torch.from_numpy(qt).cuda(), ids_tensor(ids), from_oracle(alpha, "bf16")
+            y = torch.empty(n, hidden, dtype=torch.bfloat16, device="cuda")
+            scratch = torch.empty(n, hidden, dtype=torch.bfloat16, device="cuda")
+            st = new_status("cuda")
+            _nccl.call("cb200_sharded_qembedding_rms_norm", comm, tq.data_ptr(), code, tids.data_ptr(), ta.data_ptr(),
+                       y.data_ptr(), scratch.data_ptr(), scratch.numel() * 2, vocab, hidden, n, 1e-5, 2, 1, 0, vocab, 0,
+                       st.data_ptr(), _stream(y))
+            raise_for_status(st)
+            assert np.array_equal(to_oracle(scratch), want_rows)
+            assert_norm_equal(y, want, "bf16")
+            rc = _nccl.lib.cb200_sharded_qembedding_rms_norm(comm, tq.data_ptr(), code, tids.data_ptr(), ta.data_ptr(),
+                                                             y.data_ptr(), scratch.data_ptr(), 16, vocab, hidden, n,
+                                                             1e-5, 2, 1, 0, vocab, 0, st.data_ptr(), _stream(y))
+            assert rc == -1  # scratch too small is refused on the host
+    finally:
+        torch.cuda.synchronize()
+        _nccl.comm_destroy(comm)
+
+
 # ------------------------------------------------------------------------------------------------
 # front-end error behaviour (candle's messages)
 # ------------------------------------------------------------------------------------------------
