@@ -16,8 +16,12 @@ SIGNATURES = {
     "cb200_sharded_qembedding_rms_norm": [
         _vp, _vp, _int, _vp, _vp, _vp, _vp, _sz, _i64, _i32, _i64, _f32, _int, _int, _i64, _i64, _int, _vp, _vp,
     ],
+    "cb200_sharded_qembedding_rms_norm_static": [
+        _vp, _vp, _int, _vp, _vp, _vp, _i64, _i32, _i64, _f32, _int, _int, _i64, _i64, _int, _vp, _vp,
+    ],
 }
 UNIQUE_ID_BYTES = 128
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 
 def _load() -> ctypes.CDLL:

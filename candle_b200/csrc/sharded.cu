@@ -2,6 +2,7 @@
 // RMS norm.  Built into its own library (libcandle_b200_nccl.so).
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 
 #include <cuda_runtime.h>
 #include <nccl.h>
@@ -47,6 +48,34 @@ int sharded_steps(void* comm, const void* qtable, int qtype, const void* ids, co
   return CB200_OK;
 }
 
+// Scratch for the allocation-free entry point.  It lives in the library image: every GPU that loads
+// the library carries these bytes until the process exits.  In host code the array's name is only
+// a host-side handle, not a device address, so the address is looked up once per device (below)
+// and that pointer is what the kernels get.
+__device__ __align__(256) unsigned char g_static_scratch[CB200_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+
+// Device address of the static scratch on the CURRENT device; resolved on the first call per device.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(CB200_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(CB200_E_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(CB200_E_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return CB200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -83,6 +112,30 @@ int cb200_sharded_qembedding_rms_norm(void* comm, const void* qtable, int qtype,
   if (scratch == nullptr || scratch_bytes < need)
     return fail(CB200_E_INVALID_ARGUMENT, "cb200_sharded_qembedding_rms_norm: scratch of %zu bytes needed, %zu given", need,
                 scratch_bytes);
+  return sharded_steps(comm, qtable, qtype, ids, alpha, y, scratch, vocab, hidden, n_ids, eps, out_dtype, id_dtype,
+                       vocab_begin, vocab_end, flags, status, stream);
+}
+
+int cb200_sharded_qembedding_rms_norm_static(void* comm, const void* qtable, int qtype, const void* ids,
+                                             const void* alpha, void* y, int64_t vocab, int32_t hidden, int64_t n_ids,
+                                             float eps, int out_dtype, int id_dtype, int64_t vocab_begin,
+                                             int64_t vocab_end, int flags, cb200_status* status,
+                                             cb200_stream_t stream) {
+  const char* name = "cb200_sharded_qembedding_rms_norm_static";
+  if (n_ids < 0 || hidden < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape", name);
+  if (out_dtype != CB200_DTYPE_F32 && out_dtype != CB200_DTYPE_F16 && out_dtype != CB200_DTYPE_BF16)
+    return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
+  const size_t need = static_cast<size_t>(n_ids) * hidden * elem_bytes(out_dtype);
+  if (need == 0) return CB200_OK;
+  if (need > CB200_STATIC_SCRATCH_BYTES)
+    return fail(CB200_E_UNSUPPORTED_SHAPE,
+                "%s: %lld rows x %d columns need %zu bytes of scratch, the built-in scratch holds %zu; use "
+                "cb200_sharded_qembedding_rms_norm with a buffer of your own",
+                name, (long long)n_ids, hidden, need, static_cast<size_t>(CB200_STATIC_SCRATCH_BYTES));
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != CB200_OK) return rc;
+  // nothing in the scratch has to start at zero: the lookup writes every byte the later steps read
   return sharded_steps(comm, qtable, qtype, ids, alpha, y, scratch, vocab, hidden, n_ids, eps, out_dtype, id_dtype,
                        vocab_begin, vocab_end, flags, status, stream);
 }

@@ -43,6 +43,35 @@ CB200_API int cb200_sharded_qembedding_rms_norm(void* comm, const void* qtable, 
                                                 int64_t vocab_end, int flags, cb200_status* status,
                                                 cb200_stream_t stream);
 
+/*
+ * The same operation for callers that must not allocate device memory and have no buffer to lend:
+ * code that runs after the application's memory pool has claimed the whole device (a cudaMalloc
+ * there fails, or fragments what the pool thinks it owns), and latency-critical serving loops,
+ * where the device-wide synchronisation a cudaMalloc / cudaFree implies stalls every stream.
+ * It has no counterpart in the reference.
+ *
+ * Instead of a `scratch` argument it uses a fixed array of CB200_STATIC_SCRATCH_BYTES that is part
+ * of the library image (each GPU that loads the library holds it until the process exits), so
+ * n_ids * hidden * sizeof(out_dtype) must not exceed that size; larger requests are refused with
+ * CB200_E_UNSUPPORTED_SHAPE and a message, and should go to the entry point above.  Inputs and
+ * outputs are still the caller's.  The call itself performs no cudaMalloc, cudaFree or other
+ * allocating call; with a non-NULL `comm` it issues one ncclAllReduce on a communicator the caller
+ * created earlier (pass NULL for a single rank: no NCCL call is made).
+ *
+ * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+ * that device current) and keeps it; make that first call outside any stream capture.  All calls
+ * share the one array, which keeps the previous call's rows: nothing in it needs clearing, because
+ * the lookup rewrites every byte the later steps read, but two calls whose work overlaps on the GPU
+ * (different streams, or threads) race on it -- serialise them.
+ */
+#define CB200_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+CB200_API int cb200_sharded_qembedding_rms_norm_static(void* comm, const void* qtable, int qtype, const void* ids,
+                                                       const void* alpha, void* y, int64_t vocab, int32_t hidden,
+                                                       int64_t n_ids, float eps, int out_dtype, int id_dtype,
+                                                       int64_t vocab_begin, int64_t vocab_end, int flags,
+                                                       cb200_status* status, cb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
