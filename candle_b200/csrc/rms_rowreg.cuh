@@ -312,24 +312,24 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
 }
 
 // Decides T(m) from the tree-order sums (s, w); returns false if only a sequential replay can.
+// Must be called by a full warp with the same (s, w) in every lane: even lanes evaluate the lower
+// end of the interval and odd lanes the upper end, side by side, and swap results.
 template <int DT>
 __device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, float& m) {
   constexpr float kU = 5.9604644775390625e-8f;  // 2^-24
   // |seq - tree| <= 1.01*u*W + 160*u*s covers both bounds, the f32 rounding of w and of this
   // expression itself.
   const float err = 1.01f * kU * w + 160.0f * kU * s;
-  const float m_lo = round_to<DT>(rms_from_sum(s - err, nf, eps));
-  const float m_hi = round_to<DT>(rms_from_sum(s + err, nf, eps));
-  m = m_lo;
+  const bool upper = threadIdx.x & 1;
+  const float mine = round_to<DT>(rms_from_sum(upper ? s + err : s - err, nf, eps));
+  const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 1);
+  m = upper ? other : mine;  // T(m) at the lower end, in every lane
   // Squares below 2^-149 are not exact in f32; that can only matter when the whole row is that
   // small AND eps is too: let the replay, which rounds like the CPU, handle it.
   const bool tiny = (s < 7.8886091e-31f) && (eps < 1e-18f) && (s != 0.0f || w != 0.0f);
-  return (m_lo == m_hi) && !tiny;  // false as well when anything is NaN
+  return (mine == other) && !tiny;  // false as well when anything is NaN
 }
 
-// Resolves T(m) for the row held in h[] by the tpr threads of row slot threadIdx.y.  All threads
-// of the row must call it; rows synchronise on their own named barrier (id 1 + threadIdx.y).
-// `park` is V vectors of shared memory of this row that h can be written to when a replay is needed.
 // Step 1 of resolving T(m) for the row whose per-thread partial sums are (lsum, lw): the tpr
 // threads of row slot threadIdx.y reduce them (named barrier id 1 + threadIdx.y for rows wider
 // than a warp) and warp 0 of the row decides.  Returns T(m) if `need_replay` comes back false;
