@@ -214,29 +214,40 @@ __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const Lan
 }
 
 // ---------------------------------------------------------------------------------------------
-// Short rows (V = 32 * VPL 16-byte vectors, VPL <= 4; e.g. 768 bf16 columns): a pipelined,
-// persistent version of the same scheme.  One 512-thread CTA per SM walks tiles of 32 rows.
-//   * the tile's x rows (and residual rows) arrive in shared memory by asynchronous 16-byte
+// Short rows (V = 32 * VPL 16-byte vectors, VPL <= 4; e.g. 768 bf16 columns): a software-
+// pipelined, persistent version of the same scheme.  One 512-thread CTA per SM walks tiles of
+// 32 rows (24 for VPL = 4) through a ring of three row buffers:
+//   * a tile's x rows (and residual rows) arrive in shared memory by asynchronous 16-byte
 //     copies, which bypass L1 and registers, so the large shared-memory carve-out this kernel
-//     needs does not limit the bytes in flight;
-//   * each thread turns the vectors it copied itself into h = T(x + residual) in place;
-//   * warp 0 walks the 32 rows sequentially, one lane per row, while ALL warps have already
-//     started the copies of the next tile into the other buffer;
-//   * every warp then normalises two rows with gamma / beta held widened in registers.
+//     needs does not limit the bytes in flight; the copies of tile t+1 are started as soon as
+//     tile t has been turned into h = T(x + residual) (in place, each thread its own vectors);
+//   * warp 0 then walks tile t sequentially, one lane per row, while the mover warps normalise
+//     and store tile t-1 with gamma / beta held widened in registers and then refill its buffer
+//     with the x rows of tile t+2.  The walk is a chain of dependent additions that runs at the
+//     floating-point latency only while nothing else competes for its scheduler, so the movers
+//     are the warps of the three other schedulers (warp index not a multiple of four); warps
+//     4, 8 and 12 only take part in the CTA barriers.
 // ---------------------------------------------------------------------------------------------
 constexpr int kShortThreads = 512;
 constexpr int kShortWarps = kShortThreads / 32;
-constexpr int kShortRows = 32;
+
+// rows per tile: four buffers of (rows x (32 VPL + 1)) vectors must fit in 227 KB
+template <int VPL>
+struct ShortTile {
+  static constexpr int kRows = VPL == 4 ? 24 : 32;
+};
 
 template <int DT, int OP, int VPL>
 __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const LaneRowArgs a) {
   constexpr int PV = Elem<DT>::kPerVec;
   constexpr int V = 32 * VPL;
+  constexpr int TR = ShortTile<VPL>::kRows;
   constexpr int kPitchVecs = V + 1;  // odd number of 16-byte units: conflict-free lane-per-row walk
+  constexpr int kBufVecs = TR * kPitchVecs;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint4* xbuf[2] = {reinterpret_cast<uint4*>(smem_raw), reinterpret_cast<uint4*>(smem_raw) + kShortRows * kPitchVecs};
-  uint4* rbuf = reinterpret_cast<uint4*>(smem_raw) + 2 * kShortRows * kPitchVecs;
-  float2* stats = reinterpret_cast<float2*>(rbuf + kShortRows * kPitchVecs);
+  uint4* const smem_v = reinterpret_cast<uint4*>(smem_raw);  // x ring: buffers 0..2, then the residual buffer
+  uint4* const rbuf = smem_v + 3 * kBufVecs;
+  float2* const stats = reinterpret_cast<float2*>(rbuf + kBufVecs);  // [2][TR]: {sum, sum of squares}
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint4* gx = static_cast<const uint4*>(a.x);
@@ -244,7 +255,7 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
   uint4* gs = static_cast<uint4*>(a.sum_out);
   uint4* gy = static_cast<uint4*>(a.y);
   const bool has_res = gr != nullptr;
-  const int64_t n_tiles = (a.rows + kShortRows - 1) / kShortRows;
+  const int64_t n_tiles = (a.rows + TR - 1) / TR;
 
   // gamma / beta of this lane's vectors, widened once
   float gam[VPL][PV], bet[VPL][PV];
@@ -254,107 +265,51 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
     if (OP == kOpLayerNorm) vec_to_floats<DT>(__ldg(static_cast<const uint4*>(a.beta) + lane + 32 * j), bet[j]);
   }
 
-  // this thread copies / converts / normalises rows warp and warp + 16 of a tile, vectors lane + 32 j
-  auto issue_tile = [&](int64_t tile, int buf) {
-    if (tile < n_tiles) {
+  // Mover m owns rows m + 12 k of every tile, vectors lane + 32 j, for the copies, the in-place
+  // conversion and the stores alike, so a thread converts only what it copied itself.
+  constexpr int kMovers = kShortWarps - kShortWarps / 4;
+  const bool is_mover = (warp & 3) != 0;
+  const int mover = (warp >> 2) * 3 + (warp & 3) - 1;
+  constexpr int kRowsPerMover = (TR + kMovers - 1) / kMovers;
+  auto issue_rows = [&](const uint4* __restrict__ g, uint4* buf, int64_t tile) {
+    if (g != nullptr && tile < n_tiles && is_mover) {
 #pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
-        const int r = warp + kShortWarps * rr;
-        const int64_t row = tile * kShortRows + r;
-        if (row < a.rows) {
+      for (int k = 0; k < kRowsPerMover; ++k) {
+        const int r = mover + kMovers * k;
+        const int64_t row = tile * TR + r;
+        if (r < TR && row < a.rows) {
 #pragma unroll
-          for (int j = 0; j < VPL; ++j) {
-            const int v = lane + 32 * j;
-            cp_async16(xbuf[buf] + r * kPitchVecs + v, gx + row * V + v);
-            if (has_res) cp_async16(rbuf + r * kPitchVecs + v, gr + row * V + v);
-          }
+          for (int j = 0; j < VPL; ++j) cp_async16(buf + r * kPitchVecs + lane + 32 * j, g + row * V + lane + 32 * j);
         }
       }
     }
-    cp_async_commit();
+    cp_async_commit();  // an empty group keeps the group count in step
   };
 
-  int buf = 0;
-  issue_tile(blockIdx.x, 0);
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, buf ^= 1) {
-    const int64_t row0 = tile * kShortRows;
-    const int live = static_cast<int>(min(static_cast<int64_t>(kShortRows), a.rows - row0));
-    cp_async_wait_all();
-    if (has_res) {
+  // pass 2 of one tile
+  auto store_tile = [&](int64_t tile, int slot, int parity) {
+    const int64_t row0 = tile * TR;
+    const int live = static_cast<int>(min(static_cast<int64_t>(TR), a.rows - row0));
+    const uint4* xb = smem_v + slot * kBufVecs;
 #pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
-        const int r = warp + kShortWarps * rr;
-        if (r < live) {
-#pragma unroll
-          for (int j = 0; j < VPL; ++j) {
-            const int v = lane + 32 * j;
-            uint4* px = xbuf[buf] + r * kPitchVecs + v;
-            uint4 h;
-            if constexpr (DT == kDtF32) {
-              float fa[PV], fb[PV];
-              vec_to_floats<DT>(*px, fa);
-              vec_to_floats<DT>(rbuf[r * kPitchVecs + v], fb);
-#pragma unroll
-              for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
-              h = floats_to_vec<DT>(fa);
-            } else {
-              h = add_round_vec<DT>(*px, rbuf[r * kPitchVecs + v]);  // rounds the sum to T, as Tensor::add does
-            }
-            *px = h;
-            if (gs != nullptr) stg_stream(gs + (row0 + r) * V + v, h);
-          }
-        }
-      }
-    } else if (gs != nullptr) {
-#pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
-        const int r = warp + kShortWarps * rr;
-        if (r < live) {
-#pragma unroll
-          for (int j = 0; j < VPL; ++j) stg_stream(gs + (row0 + r) * V + lane + 32 * j, xbuf[buf][r * kPitchVecs + lane + 32 * j]);
-        }
-      }
-    }
-    __syncthreads();  // the tile's h is complete; rbuf and the other x buffer are free
-    issue_tile(tile + gridDim.x, buf ^ 1);
-
-    // ---- pass 1: one lane per row, strictly sequential f32 accumulation ----
-    if (warp == 0 && lane < live) {
-      const uint4* row = xbuf[buf] + lane * kPitchVecs;
-      float s = 0.0f, s2 = 0.0f;
-#pragma unroll 4
-      for (int v = 0; v < V; ++v) {
-        float f[PV];
-        vec_to_floats<DT>(row[v], f);
-#pragma unroll
-        for (int e = 0; e < PV; ++e) {
-          if (OP == kOpLayerNorm) s = __fadd_rn(s, f[e]);
-          // for 16-bit inputs f*f is exact in f32, so the fused form rounds like add(s2, mul(f, f))
-          s2 = (DT == kDtF32) ? __fadd_rn(s2, __fmul_rn(f[e], f[e])) : fmaf(f[e], f[e], s2);
-        }
-      }
-      const float nf = static_cast<float>(a.n);
-      if (OP == kOpLayerNorm) {
-        float mean = __fdiv_rn(s, nf);
-        float var = __fsub_rn(__fdiv_rn(s2, nf), __fmul_rn(mean, mean));
-        stats[lane] = make_float2(mean, __frcp_rn(__fsqrt_rn(__fadd_rn(var, a.eps))));
-      } else {
-        stats[lane] = make_float2(round_to<DT>(rms_from_sum(s2, nf, a.eps)), 0.0f);
-      }
-    }
-    __syncthreads();
-
-    // ---- pass 2: normalise and store ----
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      const int r = warp + kShortWarps * rr;
+    for (int k = 0; k < kRowsPerMover; ++k) {
+      const int r = mover + kMovers * k;
       if (r < live) {
-        const float2 st = stats[r];
+        const float2 sums = stats[parity * TR + r];
+        const float nf = static_cast<float>(a.n);
+        float2 st;
+        if (OP == kOpLayerNorm) {
+          const float mean = __fdiv_rn(sums.x, nf);
+          const float var = __fsub_rn(__fdiv_rn(sums.y, nf), __fmul_rn(mean, mean));
+          st = make_float2(mean, __frcp_rn(__fsqrt_rn(__fadd_rn(var, a.eps))));
+        } else {
+          st = make_float2(round_to<DT>(rms_from_sum(sums.y, nf, a.eps)), 0.0f);
+        }
 #pragma unroll
         for (int j = 0; j < VPL; ++j) {
           const int v = lane + 32 * j;
           float h[PV], o[PV];
-          vec_to_floats<DT>(xbuf[buf][r * kPitchVecs + v], h);
+          vec_to_floats<DT>(xb[r * kPitchVecs + v], h);
           if (OP == kOpLayerNorm) {
 #pragma unroll
             for (int e = 0; e < PV; ++e)
@@ -367,9 +322,98 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
         }
       }
     }
-    // no barrier: the next iteration writes the other x buffer and rbuf, and `stats` only after
-    // its own first barrier, which every thread reaches after finishing this pass
+  };
+
+  // Copy groups of a mover thread, in order: x(0), r(0), x(1), then per iteration r(t+1), x(t+2).
+  // At the top of iteration t the groups x(t) and r(t) must have landed and only x(t+1), the
+  // newest, may still be in flight.
+  const int64_t stride = gridDim.x;
+  issue_rows(gx, smem_v, blockIdx.x);
+  issue_rows(gr, rbuf, blockIdx.x);
+  issue_rows(gx, smem_v + kBufVecs, blockIdx.x + stride);
+
+  int slot = 0, it = 0;
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += stride, ++it) {
+    const int64_t row0 = tile * TR;
+    const int live = static_cast<int>(min(static_cast<int64_t>(TR), a.rows - row0));
+    uint4* xb = smem_v + slot * kBufVecs;
+    const int next_slot = slot == 2 ? 0 : slot + 1;
+    const int prev_slot = slot == 0 ? 2 : slot - 1;
+    if (is_mover) {
+      cp_async_wait_pending(1);
+      if (has_res || gs != nullptr) {
+#pragma unroll
+        for (int k = 0; k < kRowsPerMover; ++k) {
+          const int r = mover + kMovers * k;
+          if (r < live) {
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+              const int v = lane + 32 * j;
+              uint4* px = xb + r * kPitchVecs + v;
+              uint4 h = *px;
+              if (has_res) {
+                if constexpr (DT == kDtF32) {
+                  float fa[PV], fb[PV];
+                  vec_to_floats<DT>(h, fa);
+                  vec_to_floats<DT>(rbuf[r * kPitchVecs + v], fb);
+#pragma unroll
+                  for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
+                  h = floats_to_vec<DT>(fa);
+                } else {
+                  h = add_round_vec<DT>(h, rbuf[r * kPitchVecs + v]);  // rounds the sum to T, as Tensor::add does
+                }
+                *px = h;
+              }
+              if (gs != nullptr) stg_stream(gs + (row0 + r) * V + v, h);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();  // tile t is h everywhere, the residual buffer is free, pass 1 of tile t-1 is done
+
+    if (warp == 0) {
+      // ---- pass 1 of tile t: one lane per row, strictly sequential f32 accumulation ----
+      if (lane < live) {
+        const uint4* row = xb + lane * kPitchVecs;
+        float s = 0.0f, s2 = 0.0f;
+        // four vectors are fetched while the previous four are accumulated, so the chains of
+        // dependent additions never wait for shared memory
+        uint4 cur[4], nxt[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cur[q] = row[q];
+#pragma unroll 1
+        for (int v = 0; v < V; v += 4) {
+          const int vn = v + 4 < V ? v + 4 : 0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) nxt[q] = row[vn + q];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float f[PV];
+            vec_to_floats<DT>(cur[q], f);
+#pragma unroll
+            for (int e = 0; e < PV; ++e) {
+              if (OP == kOpLayerNorm) s = __fadd_rn(s, f[e]);
+              // for 16-bit inputs f*f is exact in f32, so the fused form rounds like add(s2, mul(f, f))
+              s2 = (DT == kDtF32) ? __fadd_rn(s2, __fmul_rn(f[e], f[e])) : fmaf(f[e], f[e], s2);
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) cur[q] = nxt[q];
+        }
+        stats[(it & 1) * TR + lane] = make_float2(s, s2);
+      }
+    } else if (is_mover) {
+      issue_rows(gr, rbuf, tile + stride);
+      // ---- pass 2 of tile t-1, then its buffer takes the x rows of tile t+2 ----
+      if (it > 0) store_tile(tile - stride, prev_slot, (it - 1) & 1);
+      row_barrier(1, kMovers * 32);  // every mover is done reading that buffer
+      issue_rows(gx, smem_v + prev_slot * kBufVecs, tile + 2 * stride);
+    }
+    slot = next_slot;
   }
+  __syncthreads();
+  if (is_mover && it > 0) store_tile(blockIdx.x + static_cast<int64_t>(it - 1) * stride, slot == 0 ? 2 : slot - 1, (it - 1) & 1);
   cp_async_wait_all();
 }
 
@@ -466,14 +510,15 @@ static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
 
 template <int DT, int OP, int VPL>
 static cudaError_t launch_shortrow_t(const LaneRowArgs& a, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(3) * kShortRows * (32 * VPL + 1) * 16 + kShortRows * sizeof(float2);
+  constexpr int TR = ShortTile<VPL>::kRows;
+  const size_t smem = static_cast<size_t>(4) * TR * (32 * VPL + 1) * 16 + 2 * TR * sizeof(float2);
   auto kern = norm_shortrow_kernel<DT, OP, VPL>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                            static_cast<int>((smem + 1024) * 100 / (228 * 1024) + 1));
   if (e != cudaSuccess) return e;
-  int64_t tiles = (a.rows + kShortRows - 1) / kShortRows;
+  int64_t tiles = (a.rows + TR - 1) / TR;
   int64_t grid = tiles < kSmCount ? tiles : kSmCount;
   kern<<<static_cast<unsigned>(grid), kShortThreads, smem, stream>>>(a);
   return cudaGetLastError();
@@ -484,7 +529,7 @@ static bool shortrow_applies(int dtype, const LaneRowArgs& a) {
   const int esz = dtype == kDtF32 ? 4 : 2;
   const int64_t row_bytes = static_cast<int64_t>(a.n) * esz;
   return a.ids == nullptr && row_bytes % 512 == 0 && row_bytes / 512 >= 1 && row_bytes / 512 <= 4 &&
-         a.rows >= 2 * kShortRows * kSmCount;
+         a.rows >= 2 * 32 * kSmCount;
 }
 
 template <int DT, int OP>
