@@ -18,13 +18,22 @@ namespace cb200 {
 // SM, each thread with up to eight 16-byte loads outstanding, keep about 100 KB of reads in flight
 // per SM, which measurement shows is what saturates HBM on B200 as long as the loop stays lean:
 // the rare exact replay is kept out of line for that reason.
-template <int DT, int VPT, int BT, bool GATHER>
+// Without a residual a row brings only half the bytes, and the loads of one row at a time no
+// longer cover the memory latency: with kModeAhead set (rows without residual of at most four
+// vectors per thread, where the registers allow it) the next row is loaded into a second set of
+// registers before the current one is worked on.  kModeGather: rows come from a table by id.
+constexpr int kModeGather = 1, kModeAhead = 2;
+
+template <int DT, int VPT, int BT, int MODE>
 __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRegArgs a) {
+  constexpr bool GATHER = (MODE & kModeGather) != 0;
+  constexpr bool AHEAD = (MODE & kModeAhead) != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
   RowRegSmem sm(smem_raw, rpc, tpr, a.V, ty);
-  const bool has_res = !GATHER && a.res != nullptr;
+  const bool has_res = MODE == 0 && a.res != nullptr;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * rpc;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * rpc + ty;
 
   uint4 al[VPT];
   float wv[VPT];
@@ -34,33 +43,63 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
     wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
   }
 
-  // gathered rows: the id of the next row is loaded one iteration early, off the critical path
-  uint64_t id_next = 0;
-  if (GATHER && static_cast<int64_t>(blockIdx.x) * rpc + ty < a.rows)
-    id_next = read_id(a.ids, a.id_dtype, static_cast<int64_t>(blockIdx.x) * rpc + ty);
-
-  for (int64_t row = static_cast<int64_t>(blockIdx.x) * rpc + ty; row < a.rows; row += stride) {
-    const uint4* xr;
-    bool live = true;
+  // The row one step ahead (AHEAD) and, for gathered rows, its id and the id two steps ahead:
+  // ids are loaded a whole iteration before the address they make is needed.
+  uint4 nx[AHEAD ? VPT : 1];
+  uint64_t id_ahead = 0, id_ahead2 = 0;
+  if (GATHER && !AHEAD && first < a.rows) id_ahead = read_id(a.ids, a.id_dtype, first);
+  if (AHEAD && first < a.rows) {
     if (GATHER) {
-      const uint64_t id = id_next;
-      if (row + stride < a.rows) id_next = read_id(a.ids, a.id_dtype, row + stride);
-      live = id < static_cast<uint64_t>(a.vocab);
-      if (!live && tx == 0) report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
-      xr = a.x + (live ? id : 0) * a.V + tx;
-    } else {
-      xr = a.x + row * a.V + tx;
+      id_ahead = read_id(a.ids, a.id_dtype, first);
+      if (first + stride < a.rows) id_ahead2 = read_id(a.ids, a.id_dtype, first + stride);
     }
+    const uint4* xr = a.x + (GATHER ? (id_ahead < static_cast<uint64_t>(a.vocab) ? id_ahead : 0) : first) * a.V + tx;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) nx[k] = ldg_stream(xr + k * tpr);
+  }
+
+  for (int64_t row = first; row < a.rows; row += stride) {
+    bool live = true;
     uint4 h[VPT];
+    if (AHEAD) {
+      const uint64_t id = id_ahead;
+      if (GATHER) {
+        live = id < static_cast<uint64_t>(a.vocab);
+        if (!live && tx == 0) report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
+      }
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) h[k] = ldg_stream(xr + k * tpr);
-    if (has_res) {
-      const uint4* rr = a.res + row * a.V + tx;
-      uint4 rv[VPT];
+      for (int k = 0; k < VPT; ++k) h[k] = nx[k];
+      if (row + stride < a.rows) {
+        if (GATHER) {
+          id_ahead = id_ahead2;
+          if (row + 2 * stride < a.rows) id_ahead2 = read_id(a.ids, a.id_dtype, row + 2 * stride);
+        }
+        const uint4* xn =
+            a.x + (GATHER ? (id_ahead < static_cast<uint64_t>(a.vocab) ? id_ahead : 0) : row + stride) * a.V + tx;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) rv[k] = ldg_stream(rr + k * tpr);
+        for (int k = 0; k < VPT; ++k) nx[k] = ldg_stream(xn + k * tpr);
+      }
+    } else {
+      const uint4* xr;
+      if (GATHER) {  // the id of the next row is loaded one iteration early, off the critical path
+        const uint64_t id = id_ahead;
+        if (row + stride < a.rows) id_ahead = read_id(a.ids, a.id_dtype, row + stride);
+        live = id < static_cast<uint64_t>(a.vocab);
+        if (!live && tx == 0) report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
+        xr = a.x + (live ? id : 0) * a.V + tx;
+      } else {
+        xr = a.x + row * a.V + tx;
+      }
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) h[k] = add_round_vec<DT>(h[k], rv[k]);
+      for (int k = 0; k < VPT; ++k) h[k] = ldg_stream(xr + k * tpr);
+      if (has_res) {
+        const uint4* rr = a.res + row * a.V + tx;
+        uint4 rv[VPT];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) rv[k] = ldg_stream(rr + k * tpr);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) h[k] = add_round_vec<DT>(h[k], rv[k]);
+      }
     }
     float lsum = 0.0f, lw = 0.0f;
 #pragma unroll
@@ -72,6 +111,12 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
       for (int k = 0; k < VPT; ++k) {
         al[k] = __ldg(a.alpha + k * tpr + tx);
         wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
+      }
+      if (AHEAD && row + stride < a.rows) {
+        const uint4* xn =
+            a.x + (GATHER ? (id_ahead < static_cast<uint64_t>(a.vocab) ? id_ahead : 0) : row + stride) * a.V + tx;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) nx[k] = ldg_stream(xn + k * tpr);
       }
     }
     if (live) {
@@ -347,11 +392,11 @@ static cudaError_t persistent_grid(K kern, int threads, size_t smem, int ctas_wa
   return cudaSuccess;
 }
 
-template <int DT, int VPT, int BT, bool GATHER>
+template <int DT, int VPT, int BT, int MODE>
 static cudaError_t launch_dense_t(const RmsRowRegArgs& a, int tpr, int rpc, cudaStream_t stream) {
   const bool with_rows = !(a.flags & CB200_FLAG_FAST_SUM);
   const size_t smem = RowRegSmem::bytes(rpc, tpr, a.V, with_rows);
-  auto kern = rms_rowreg_kernel<DT, VPT, BT, GATHER>;
+  auto kern = rms_rowreg_kernel<DT, VPT, BT, MODE>;
   unsigned grid = 1;
   cudaError_t e = persistent_grid(kern, tpr * rpc, smem, 768 / BT, (a.rows + rpc - 1) / rpc, grid);
   if (e != cudaSuccess) return e;
@@ -361,12 +406,18 @@ static cudaError_t launch_dense_t(const RmsRowRegArgs& a, int tpr, int rpc, cuda
 
 template <int DT, int VPT>
 static cudaError_t launch_dense_bt(const RmsRowRegArgs& a, int tpr, int rpc, cudaStream_t stream) {
-  const bool gather = a.ids != nullptr;
-  if (tpr * rpc <= 256)
-    return gather ? launch_dense_t<DT, VPT, 256, true>(a, tpr, rpc, stream)
-                  : launch_dense_t<DT, VPT, 256, false>(a, tpr, rpc, stream);
-  return gather ? launch_dense_t<DT, VPT, 512, true>(a, tpr, rpc, stream)
-                : launch_dense_t<DT, VPT, 512, false>(a, tpr, rpc, stream);
+  // beyond these sizes the second set of registers spills
+  constexpr int kAhead = VPT <= 4 ? kModeAhead : 0;
+  constexpr int kAheadG = VPT <= 3 ? kModeAhead : 0;
+  const bool gather = a.ids != nullptr, plain = a.res != nullptr;
+  if (tpr * rpc <= 256) {
+    if (gather) return launch_dense_t<DT, VPT, 256, kModeGather | kAheadG>(a, tpr, rpc, stream);
+    if (plain) return launch_dense_t<DT, VPT, 256, 0>(a, tpr, rpc, stream);
+    return launch_dense_t<DT, VPT, 256, kAhead>(a, tpr, rpc, stream);
+  }
+  if (gather) return launch_dense_t<DT, VPT, 512, kModeGather | kAheadG>(a, tpr, rpc, stream);
+  if (plain) return launch_dense_t<DT, VPT, 512, 0>(a, tpr, rpc, stream);
+  return launch_dense_t<DT, VPT, 512, kAhead>(a, tpr, rpc, stream);
 }
 
 template <int DT>
