@@ -77,6 +77,7 @@ int norm_impl(int op, const void* x, const void* residual, const void* alpha, co
   a.rows = rows;
   a.n = cols;
   a.eps = eps;
+  a.classic = force_lane ? 1 : 0;
   if (vec_ok && !force_generic && cb200::norm_lanerow_supported(dtype, cols))
     return cuda_result(cb200::launch_norm_lanerow(dtype, op, a, stream), name);
   return cuda_result(cb200::launch_norm_generic(dtype, op, a, stream), name);
@@ -228,6 +229,7 @@ int cb200_embedding_rms_norm(const void* table, const void* ids, const void* alp
   a.n = hidden;
   a.eps = eps;
   a.bulk = 1;
+  a.classic = force_lane ? 1 : 0;
   if (vec_ok && !force_generic && cb200::norm_lanerow_supported(dtype, hidden))
     return cuda_result(cb200::launch_norm_lanerow(dtype, cb200::kOpRmsNorm, a, stream), name);
   return cuda_result(cb200::launch_norm_generic(dtype, cb200::kOpRmsNorm, a, stream), name);

@@ -244,7 +244,7 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-// Waits until at most `pending` (0..3) of this thread's most recent copy groups are unfinished.
+// Waits until at most `pending` (0..7) of this thread's most recent copy groups are unfinished.
 __device__ __forceinline__ void cp_async_wait_pending(int pending) {
   switch (pending) {
     case 0:
@@ -256,8 +256,20 @@ __device__ __forceinline__ void cp_async_wait_pending(int pending) {
     case 2:
       asm volatile("cp.async.wait_group 2;" ::: "memory");
       break;
-    default:
+    case 3:
       asm volatile("cp.async.wait_group 3;" ::: "memory");
+      break;
+    case 4:
+      asm volatile("cp.async.wait_group 4;" ::: "memory");
+      break;
+    case 5:
+      asm volatile("cp.async.wait_group 5;" ::: "memory");
+      break;
+    case 6:
+      asm volatile("cp.async.wait_group 6;" ::: "memory");
+      break;
+    default:
+      asm volatile("cp.async.wait_group 7;" ::: "memory");
       break;
   }
 }

@@ -27,6 +27,7 @@ struct LaneRowArgs {
   int V;      // filled by the launcher: 16-byte vectors per row
   int pitch;  // filled by the launcher: shared-memory row pitch in bytes
   int R;      // filled by the launcher: rows per CTA
+  int classic;  // keep to the whole-row kernel where the streaming one would apply (cross-checks)
 };
 
 struct RmsRowRegArgs;

@@ -418,6 +418,293 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
 }
 
 // ---------------------------------------------------------------------------------------------
+// Long rows: the sequential walk over rows that are STREAMED through shared memory instead of
+// staged whole.  The walk is bound by the floating-point latency of its dependent additions, so
+// a warp that walks 32 rows side by side consumes about as many bytes per second as an SM's share
+// of HBM delivers -- provided the rows do not have to fit in shared memory.  Per CTA (one per SM,
+// persistent over tiles of TR <= 32 rows):
+//   * warp 0 owns a ring of D stages; a stage holds one chunk of CV vectors of each of the
+//     tile's rows (and of the residual rows).  Each lane copies the chunks of its own row with
+//     the bulk-copy engine, completion counted on the stage's mbarrier; the lane then walks the
+//     chunk and refills the stage with the chunk D steps ahead, across tile boundaries.  No
+//     other warp takes part, so the walk never waits for anything but memory.  The engine takes
+//     about 35 ns per copy whatever its size, so one warp's copies deliver an SM's share of HBM
+//     only from 2 KB per copy on, which is the chunk size (CV = 128).
+//   * the other warps (those of the three schedulers warp 0 is not on) normalise the previous
+//     tile meanwhile: they read its rows a second time -- from L2 as long as the tiles in flight
+//     on all SMs fit there -- and store the result.
+// ---------------------------------------------------------------------------------------------
+constexpr int kStreamThreads = 768;
+constexpr int kStreamWarps = kStreamThreads / 32;
+constexpr int kStreamFinishers = kStreamWarps - kStreamWarps / 4;
+constexpr int kStreamMaxStages = 8;
+// vectors of a row per stage, and the bytes of a row's slot (an odd number of 16-byte units)
+__host__ __device__ inline int stream_chunk_pitch(int cv) { return (cv + 1) * 16; }
+
+struct StreamSmem {
+  unsigned char* xring;
+  unsigned char* rring;
+  uint64_t* bars;    // [D]
+  float2* stats;     // [2][32]: {sum, sum of squares} of the tile walked in iteration it & 1
+  int64_t* src;      // [4][32]: source row of each tile row (-1: none), iteration it & 3
+  volatile int* abort_flag;
+  __device__ StreamSmem(unsigned char* base, int TR, int D, int cv, bool res) {
+    const size_t ring = static_cast<size_t>(D) * TR * stream_chunk_pitch(cv);
+    xring = base;
+    rring = base + ring;
+    bars = reinterpret_cast<uint64_t*>(base + ring * (res ? 2 : 1));
+    stats = reinterpret_cast<float2*>(bars + kStreamMaxStages);
+    src = reinterpret_cast<int64_t*>(stats + 64);
+    abort_flag = reinterpret_cast<volatile int*>(src + 128);
+  }
+  static size_t bytes(int TR, int D, int cv, bool res) {
+    return static_cast<size_t>(D) * TR * stream_chunk_pitch(cv) * (res ? 2 : 1) + kStreamMaxStages * 8 + 64 * 8 + 128 * 8 + 16;
+  }
+};
+
+template <int DT, int OP, bool RES>
+__global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const LaneRowArgs a, int TR, int D, int CV) {
+  constexpr int PV = Elem<DT>::kPerVec;
+  constexpr int G = RES ? 2 : 4;  // vectors fetched from shared memory ahead of the chain
+  const int kChunkVecs = CV;  // vectors of a row per stage
+  const int kChunkPitch = stream_chunk_pitch(CV);
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  StreamSmem sm(smem_raw, TR, D, CV, RES);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int V = a.V;
+  const int nc = (V + kChunkVecs - 1) / kChunkVecs;
+  const int64_t tiles = (a.rows + TR - 1) / TR;
+  const int64_t stride = gridDim.x;
+  const bool gather = a.ids != nullptr;
+  const uint4* gx = static_cast<const uint4*>(a.x);
+  const uint4* gr = static_cast<const uint4*>(a.res);
+
+  if (tid == 0) {
+    for (int s = 0; s < D; ++s) mbar_init(&sm.bars[s], 1);
+    mbar_init_fence();
+    *sm.abort_flag = 0;
+  }
+  __syncthreads();
+
+  // ---- pass 2 of one tile: finisher f takes rows f, f + 18 ----
+  const bool is_finisher = (warp & 3) != 0;
+  const int finisher = (warp >> 2) * 3 + (warp & 3) - 1;
+  auto finish_tile = [&](int64_t tile, int it_t) {
+    const uint4* ga = static_cast<const uint4*>(a.alpha);
+    const uint4* gb = static_cast<const uint4*>(a.beta);
+    uint4* gy = static_cast<uint4*>(a.y);
+    uint4* gs = static_cast<uint4*>(a.sum_out);
+    const float nf = static_cast<float>(a.n);
+    for (int r = finisher; r < TR; r += kStreamFinishers) {
+      const int64_t src = sm.src[(it_t & 3) * 32 + r];
+      if (src < 0) continue;
+      const int64_t row = tile * TR + r;
+      const float2 sums = sm.stats[(it_t & 1) * 32 + r];
+      float2 st;
+      if (OP == kOpLayerNorm) {
+        const float mean = __fdiv_rn(sums.x, nf);  // candle-nn/src/ops.rs:716-718
+        const float var = __fsub_rn(__fdiv_rn(sums.y, nf), __fmul_rn(mean, mean));
+        st = make_float2(mean, __frcp_rn(__fsqrt_rn(__fadd_rn(var, a.eps))));
+      } else {
+        st = make_float2(round_to<DT>(rms_from_sum(sums.y, nf, a.eps)), 0.0f);  // ops.rs:491-492
+      }
+      const uint4* xr = gx + src * V;
+      const uint4* rr = RES ? gr + row * V : nullptr;
+      uint4* yr = gy + row * V;
+      uint4* so = gs != nullptr ? gs + row * V : nullptr;
+      // 64 registers of loads in flight per thread: the second read has to cover the latency of
+      // L2, or of HBM where the rows have left L2, with twelve warps
+      constexpr int U = RES ? 4 : 8;
+      for (int v0 = lane; v0 < V; v0 += 32 * U) {
+        uint4 hv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) hv[u] = (v0 + 32 * u < V) ? __ldg(xr + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
+        if (RES) {
+          uint4 rv[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) rv[u] = (v0 + 32 * u < V) ? __ldg(rr + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if constexpr (DT == kDtF32) {
+              float fa[PV], fb[PV];
+              vec_to_floats<DT>(hv[u], fa);
+              vec_to_floats<DT>(rv[u], fb);
+#pragma unroll
+              for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
+              hv[u] = floats_to_vec<DT>(fa);
+            } else {
+              hv[u] = add_round_vec<DT>(hv[u], rv[u]);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < V) {
+            float h[PV], g[PV], o[PV];
+            vec_to_floats<DT>(hv[u], h);
+            vec_to_floats<DT>(__ldg(ga + v), g);
+            if (OP == kOpLayerNorm) {
+              float b[PV];
+              vec_to_floats<DT>(__ldg(gb + v), b);
+#pragma unroll
+              for (int e = 0; e < PV; ++e)
+                o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), g[e]), b[e]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), g[e]);
+            }
+            stg_stream(yr + v, floats_to_vec<DT>(o));
+            if (so != nullptr) stg_stream(so + v, hv[u]);
+          }
+        }
+      }
+    }
+  };
+
+  // ---- the walker's copy stream: chunk number g goes to stage g % D, parity (g / D) & 1 ----
+  int64_t tile_i = blockIdx.x;  // tile, chunk and iteration the next copy belongs to
+  int chunk_i = 0, it_i = 0;
+  uint32_t g_i = 0, g_c = 0;    // chunks issued / consumed so far
+  const unsigned char* xs_i = nullptr;
+  const unsigned char* rs_i = nullptr;
+  bool live_i = false;
+  int nlive_i = 0;
+  const size_t row_bytes = static_cast<size_t>(V) * 16;
+  auto open_tile = [&]() {  // warp 0: sources of tile_i
+    const int64_t row = tile_i * TR + lane;
+    bool live = lane < TR && row < a.rows;
+    int64_t src = row;
+    if (gather && live) {
+      const uint64_t id = read_id(a.ids, a.id_dtype, row);
+      if (id >= static_cast<uint64_t>(a.vocab)) {
+        report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
+        live = false;
+      } else {
+        src = static_cast<int64_t>(id);
+      }
+    }
+    sm.src[(it_i & 3) * 32 + lane] = live ? src : -1;
+    xs_i = static_cast<const unsigned char*>(a.x) + (live ? src : 0) * row_bytes;
+    rs_i = RES ? static_cast<const unsigned char*>(a.res) + (live ? row : 0) * row_bytes : nullptr;
+    live_i = live;
+    nlive_i = __popc(__ballot_sync(0xffffffffu, live));
+  };
+  auto issue_chunk = [&]() {
+    const int stage = static_cast<int>(g_i % static_cast<uint32_t>(D));
+    const int vecs = min(kChunkVecs, V - kChunkVecs * chunk_i);
+    const uint32_t bytes = static_cast<uint32_t>(vecs) * 16u;
+    if (lane == 0) mbar_expect_tx(&sm.bars[stage], static_cast<uint32_t>(nlive_i) * bytes * (RES ? 2u : 1u));
+    if (live_i) {
+      const size_t slot = (static_cast<size_t>(stage) * TR + lane) * kChunkPitch;
+      const size_t off = static_cast<size_t>(chunk_i) * kChunkVecs * 16;
+      bulk_g2s(sm.xring + slot, xs_i + off, bytes, &sm.bars[stage]);
+      if (RES) bulk_g2s(sm.rring + slot, rs_i + off, bytes, &sm.bars[stage]);
+    }
+    ++g_i;
+    if (++chunk_i == nc) {
+      chunk_i = 0;
+      tile_i += stride;
+      ++it_i;
+      if (tile_i < tiles) open_tile();
+    }
+  };
+
+  if (warp == 0) {
+    open_tile();
+    while (g_i < static_cast<uint32_t>(D) && tile_i < tiles && it_i <= 1) issue_chunk();
+  }
+
+  int it = 0;
+  int64_t tile = blockIdx.x;
+  for (; tile < tiles; tile += stride, ++it) {
+    if (warp == 0) {
+      // ---- pass 1 of tile `tile`: strictly sequential f32 accumulation, one lane per row ----
+      const bool live = sm.src[(it & 3) * 32 + lane] >= 0;
+      float s = 0.0f, s2 = 0.0f;
+      bool ok = true;
+      for (int c = 0; c < nc && ok; ++c) {
+        const int stage = static_cast<int>(g_c % static_cast<uint32_t>(D));
+        ok = __all_sync(0xffffffffu, mbar_wait(&sm.bars[stage], (g_c / static_cast<uint32_t>(D)) & 1u));
+        if (!ok) break;
+        const int cnt = min(kChunkVecs, V - kChunkVecs * c);
+        if (live) {
+          const size_t slot = (static_cast<size_t>(stage) * TR + lane) * kChunkPitch;
+          const uint4* xq = reinterpret_cast<const uint4*>(sm.xring + slot);
+          const uint4* rq = reinterpret_cast<const uint4*>(sm.rring + slot);
+          auto fetch = [&](int v) -> uint4 {
+            uint4 hv = xq[v];  // v may run past cnt inside the padded slot; such vectors are not used
+            if (RES) {
+              if constexpr (DT == kDtF32) {
+                float fa[PV], fb[PV];
+                vec_to_floats<DT>(hv, fa);
+                vec_to_floats<DT>(rq[v], fb);
+#pragma unroll
+                for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
+                hv = floats_to_vec<DT>(fa);
+              } else {
+                hv = add_round_vec<DT>(hv, rq[v]);  // rounds the sum to T, as Tensor::add does
+              }
+            }
+            return hv;
+          };
+          auto add_vec = [&](const uint4& hv) {
+            float f[PV];
+            vec_to_floats<DT>(hv, f);
+#pragma unroll
+            for (int e = 0; e < PV; ++e) {
+              if (OP == kOpLayerNorm) s = __fadd_rn(s, f[e]);
+              // for 16-bit inputs f*f is exact in f32, so the fused form rounds like add(s2, mul(f, f))
+              s2 = (DT == kDtF32) ? __fadd_rn(s2, __fmul_rn(f[e], f[e])) : fmaf(f[e], f[e], s2);
+            }
+          };
+          const int full = cnt / G * G;
+          uint4 cur[G], nxt[G];
+#pragma unroll
+          for (int q = 0; q < G; ++q) cur[q] = fetch(q);
+#pragma unroll 1
+          for (int v = 0; v < full; v += G) {
+            const int vn = v + G < kChunkVecs ? v + G : 0;
+#pragma unroll
+            for (int q = 0; q < G; ++q) nxt[q] = fetch(vn + q);
+#pragma unroll
+            for (int q = 0; q < G; ++q) add_vec(cur[q]);
+#pragma unroll
+            for (int q = 0; q < G; ++q) cur[q] = nxt[q];
+          }
+#pragma unroll
+          for (int q = 0; q < G; ++q)
+            if (full + q < cnt) add_vec(cur[q]);
+        }
+        __syncwarp();
+        ++g_c;
+        // refill: keep the copy stream D chunks ahead, at most into the next tile
+        while (g_i - g_c < static_cast<uint32_t>(D) && tile_i < tiles && it_i <= it + 1) issue_chunk();
+      }
+      if (!ok) {
+        if (lane == 0) {
+          report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, tile * TR, 0, a.vocab);
+          *sm.abort_flag = 1;
+        }
+      } else if (live) {
+        sm.stats[(it & 1) * 32 + lane] = make_float2(s, s2);
+      }
+    } else if (is_finisher && it > 0) {
+      finish_tile(tile - stride, it - 1);
+    }
+    __syncthreads();
+    if (*sm.abort_flag) {
+      // bounded second chance for the copies still in flight before the CTA retires
+      if (warp == 0)
+        for (uint32_t g = g_c; g != g_i; ++g)
+          mbar_wait(&sm.bars[g % static_cast<uint32_t>(D)], (g / static_cast<uint32_t>(D)) & 1u);
+      return;
+    }
+  }
+  if (is_finisher && it > 0) finish_tile(tile - stride, it - 1);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Any-shape fallback: one thread per row, scalar accesses, same arithmetic and order.  Used for
 // rows that are not 16-byte multiples, misaligned bases, and rows too long for shared memory.
 // ---------------------------------------------------------------------------------------------
@@ -479,6 +766,7 @@ bool norm_lanerow_supported(int dtype, int cols) {
   int esz = dtype == kDtF32 ? 4 : 2;
   int64_t row_bytes = static_cast<int64_t>(cols) * esz;
   if (cols <= 0 || row_bytes % 16 != 0) return false;
+  if (row_bytes >= 512) return true;  // streamed: any length
   return lanerow_smem(1, static_cast<int>(row_bytes) + 16) <= kMaxDynSmem;
 }
 
@@ -546,6 +834,56 @@ static cudaError_t launch_shortrow_dt(const LaneRowArgs& a, cudaStream_t stream)
   }
 }
 
+// Rows per tile, ring depth and grid of the streaming kernel.  Problems with fewer rows than the
+// device has row slots get smaller tiles, so that every SM has one.
+static void stream_shape(int64_t rows, bool res, int& TR, int& D, int& CV, int64_t& grid) {
+  TR = 32;
+  if (rows < static_cast<int64_t>(32) * kSmCount) TR = static_cast<int>((rows + kSmCount - 1) / kSmCount);
+  if (TR < 1) TR = 1;
+  // 2 KB per copy: the copy engine takes about 35 ns per copy whatever its size, and one warp's
+  // copies deliver an SM's share of HBM only from that size on.  The ring is kept to 135 KB: what
+  // shared memory does not take stays L1, which bounds the loads pass 2 can have in flight.
+  CV = 128;
+  const int budget = 135;
+  const size_t stage = static_cast<size_t>(TR) * stream_chunk_pitch(CV) * (res ? 2 : 1);
+  D = static_cast<int>((budget * 1024) / stage);
+  if (D < 1) D = 1;
+  if (D > kStreamMaxStages) D = kStreamMaxStages;
+  const int64_t tiles = (rows + TR - 1) / TR;
+  grid = tiles < kSmCount ? tiles : kSmCount;
+}
+
+static bool stream_applies(int dtype, const LaneRowArgs& a) {
+  const int esz = dtype == kDtF32 ? 4 : 2;
+  const int64_t row_bytes = static_cast<int64_t>(a.n) * esz;
+  const bool fits_whole = lanerow_smem(1, static_cast<int>(row_bytes) + 16) <= kMaxDynSmem;
+  return (!a.classic || !fits_whole) && row_bytes % 16 == 0 && row_bytes >= 512;
+}
+
+template <int DT, int OP, bool RES>
+static cudaError_t launch_stream_r(LaneRowArgs a, cudaStream_t stream) {
+  a.V = a.n * Elem<DT>::kBytes / 16;
+  int TR, D, CV;
+  int64_t grid;
+  stream_shape(a.rows, RES, TR, D, CV, grid);
+  const size_t smem = StreamSmem::bytes(TR, D, CV, RES);
+  auto kern = norm_stream_kernel<DT, OP, RES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  int percent = static_cast<int>((smem + 1024) * 100 / (228 * 1024) + 1);
+  if (percent > 100) percent = 100;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+  if (e != cudaSuccess) return e;
+  kern<<<static_cast<unsigned>(grid), kStreamThreads, smem, stream>>>(a, TR, D, CV);
+  return cudaGetLastError();
+}
+
+template <int DT, int OP>
+static cudaError_t launch_stream_t(const LaneRowArgs& a, cudaStream_t stream) {
+  return (a.ids == nullptr && a.res != nullptr) ? launch_stream_r<DT, OP, true>(a, stream)
+                                                : launch_stream_r<DT, OP, false>(a, stream);
+}
+
 template <int DT, int OP>
 static cudaError_t launch_generic_t(const LaneRowArgs& a, cudaStream_t stream) {
   const int threads = 64;
@@ -564,6 +902,16 @@ static cudaError_t dispatch_dt(int dtype, bool generic, const LaneRowArgs& a, cu
         return launch_shortrow_dt<kDtF16, OP>(a, stream);
       default:
         return launch_shortrow_dt<kDtBF16, OP>(a, stream);
+    }
+  }
+  if (!generic && stream_applies(dtype, a)) {
+    switch (dtype) {
+      case kDtF32:
+        return launch_stream_t<kDtF32, OP>(a, stream);
+      case kDtF16:
+        return launch_stream_t<kDtF16, OP>(a, stream);
+      default:
+        return launch_stream_t<kDtBF16, OP>(a, stream);
     }
   }
   switch (dtype) {

@@ -149,7 +149,7 @@ def test_rms_norm_matches_oracle(cb, dtype, residual, impl):
         assert_norm_equal(y, want, dtype)
 
 
-@pytest.mark.parametrize("impl", ["default", "generic"])
+@pytest.mark.parametrize("impl", ["default", "lanerow", "generic"])
 @pytest.mark.parametrize("residual", [False, True])
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
 def test_layer_norm_matches_oracle(cb, dtype, residual, impl):
@@ -191,6 +191,37 @@ def test_short_rows_many_rows_take_the_pipelined_kernel(cb, dtype, cols):
     # RMS norm through the same kernel (forced for the 16-bit types, native for f32)
     y = cb.rms_norm(xt, gt, 1e-5, residual=rt, flags=cb.FLAG_FORCE_LANEROW)
     assert_norm_equal(y, oracle.rms_norm(h, g, 1e-5, dtype), dtype)
+
+
+@pytest.mark.parametrize("dtype,rows,cols", [("f32", 5000, 1000), ("bf16", 4800, 1160), ("f16", 300, 520),
+                                             ("f32", 4736 + 33, 4096), ("bf16", 150, 20000)])
+def test_long_rows_take_the_streaming_kernel(cb, dtype, rows, cols):
+    # Rows of 512 bytes and more that the pipelined short-row kernel does not take are streamed
+    # through shared memory in 512-byte chunks: ragged last chunks, ragged last tiles, several
+    # tiles per CTA and tiles smaller than a warp are all in here.
+    rng = np.random.default_rng(77)
+    x, r = randn(rng, (rows, cols), dtype), randn(rng, (rows, cols), dtype)
+    g, b = randn(rng, (cols,), dtype, 1.0, 0.1), randn(rng, (cols,), dtype, 0.0, 0.1)
+    h = oracle.add(x, r, dtype, threads=0)
+    xt, rt, gt, bt = (from_oracle(v, dtype) for v in (x, r, g, b))
+    y, hs = cb.layer_norm(xt, gt, bt, 1e-12, residual=rt, return_sum=True)
+    assert np.array_equal(to_oracle(hs), h)
+    assert_norm_equal(y, oracle.layer_norm(h, g, b, 1e-12, dtype, threads=0), dtype)
+    assert_norm_equal(cb.layer_norm(xt, gt, bt, 1e-5), oracle.layer_norm(x, g, b, 1e-5, dtype, threads=0), dtype)
+    want = oracle.rms_norm(h, g, 1e-5, dtype, threads=0)
+    y = cb.rms_norm(xt, gt, 1e-5, residual=rt)
+    assert_norm_equal(y, want, dtype)
+    if cols <= 8192:  # the whole-row kernel agrees bit for bit where a row fits in shared memory
+        y2 = cb.rms_norm(xt, gt, 1e-5, residual=rt, flags=cb.FLAG_FORCE_LANEROW)
+        assert torch.equal(y.view(torch.uint8), y2.view(torch.uint8))
+    # in place
+    y3 = cb.layer_norm(xt.clone(), gt, bt, 1e-5)
+    xc = xt.clone()
+    from candle_b200 import _cabi
+    from candle_b200.ops import _DTYPES, _stream
+    _cabi.call("cb200_layer_norm", xc.data_ptr(), None, gt.data_ptr(), bt.data_ptr(), xc.data_ptr(), None, rows, cols,
+               1e-5, _DTYPES[xc.dtype], 0, _stream(xc))
+    assert torch.equal(xc.view(torch.uint8), y3.view(torch.uint8))
 
 
 def test_rms_norm_many_rows_exercises_the_replay_path(cb):
