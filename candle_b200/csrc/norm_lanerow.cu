@@ -486,16 +486,22 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
   }
   __syncthreads();
 
-  // ---- pass 2 of one tile: finisher f takes rows f, f + 18 ----
+  // ---- pass 2 of one tile: the rows are cut into segments of 32 U vectors and the segments
+  // dealt round-robin to `workers` warps (the finishers; every warp for the last tile) ----
   const bool is_finisher = (warp & 3) != 0;
   const int finisher = (warp >> 2) * 3 + (warp & 3) - 1;
-  auto finish_tile = [&](int64_t tile, int it_t) {
+  auto finish_tile = [&](int64_t tile, int it_t, int worker, int workers) {
     const uint4* ga = static_cast<const uint4*>(a.alpha);
     const uint4* gb = static_cast<const uint4*>(a.beta);
     uint4* gy = static_cast<uint4*>(a.y);
     uint4* gs = static_cast<uint4*>(a.sum_out);
     const float nf = static_cast<float>(a.n);
-    for (int r = finisher; r < TR; r += kStreamFinishers) {
+    // 32 registers of loads in flight per thread: the second read has to cover the latency of
+    // L2, or of HBM where the rows have left L2
+    constexpr int U = RES ? 4 : 8;
+    const int segs = (V + 32 * U - 1) / (32 * U);
+    for (int item = worker; item < TR * segs; item += workers) {
+      const int r = item / segs;
       const int64_t src = sm.src[(it_t & 3) * 32 + r];
       if (src < 0) continue;
       const int64_t row = tile * TR + r;
@@ -512,51 +518,47 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
       const uint4* rr = RES ? gr + row * V : nullptr;
       uint4* yr = gy + row * V;
       uint4* so = gs != nullptr ? gs + row * V : nullptr;
-      // 64 registers of loads in flight per thread: the second read has to cover the latency of
-      // L2, or of HBM where the rows have left L2, with twelve warps
-      constexpr int U = RES ? 4 : 8;
-      for (int v0 = lane; v0 < V; v0 += 32 * U) {
-        uint4 hv[U];
+      const int v0 = (item - r * segs) * 32 * U + lane;
+      uint4 hv[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) hv[u] = (v0 + 32 * u < V) ? __ldg(xr + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
-        if (RES) {
-          uint4 rv[U];
+      for (int u = 0; u < U; ++u) hv[u] = (v0 + 32 * u < V) ? __ldg(xr + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
+      if (RES) {
+        uint4 rv[U];
 #pragma unroll
-          for (int u = 0; u < U; ++u) rv[u] = (v0 + 32 * u < V) ? __ldg(rr + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            if constexpr (DT == kDtF32) {
-              float fa[PV], fb[PV];
-              vec_to_floats<DT>(hv[u], fa);
-              vec_to_floats<DT>(rv[u], fb);
-#pragma unroll
-              for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
-              hv[u] = floats_to_vec<DT>(fa);
-            } else {
-              hv[u] = add_round_vec<DT>(hv[u], rv[u]);
-            }
-          }
-        }
+        for (int u = 0; u < U; ++u) rv[u] = (v0 + 32 * u < V) ? __ldg(rr + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const int v = v0 + 32 * u;
-          if (v < V) {
-            float h[PV], g[PV], o[PV];
-            vec_to_floats<DT>(hv[u], h);
-            vec_to_floats<DT>(__ldg(ga + v), g);
-            if (OP == kOpLayerNorm) {
-              float b[PV];
-              vec_to_floats<DT>(__ldg(gb + v), b);
+          if constexpr (DT == kDtF32) {
+            float fa[PV], fb[PV];
+            vec_to_floats<DT>(hv[u], fa);
+            vec_to_floats<DT>(rv[u], fb);
 #pragma unroll
-              for (int e = 0; e < PV; ++e)
-                o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), g[e]), b[e]);
-            } else {
-#pragma unroll
-              for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), g[e]);
-            }
-            stg_stream(yr + v, floats_to_vec<DT>(o));
-            if (so != nullptr) stg_stream(so + v, hv[u]);
+            for (int e = 0; e < PV; ++e) fa[e] = __fadd_rn(fa[e], fb[e]);
+            hv[u] = floats_to_vec<DT>(fa);
+          } else {
+            hv[u] = add_round_vec<DT>(hv[u], rv[u]);
           }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + 32 * u;
+        if (v < V) {
+          float h[PV], g[PV], o[PV];
+          vec_to_floats<DT>(hv[u], h);
+          vec_to_floats<DT>(__ldg(ga + v), g);
+          if (OP == kOpLayerNorm) {
+            float b[PV];
+            vec_to_floats<DT>(__ldg(gb + v), b);
+#pragma unroll
+            for (int e = 0; e < PV; ++e)
+              o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), g[e]), b[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), g[e]);
+          }
+          stg_stream(yr + v, floats_to_vec<DT>(o));
+          if (so != nullptr) stg_stream(so + v, hv[u]);
         }
       }
     }
@@ -690,7 +692,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
         sm.stats[(it & 1) * 32 + lane] = make_float2(s, s2);
       }
     } else if (is_finisher && it > 0) {
-      finish_tile(tile - stride, it - 1);
+      finish_tile(tile - stride, it - 1, finisher, kStreamFinishers);
     }
     __syncthreads();
     if (*sm.abort_flag) {
@@ -701,7 +703,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
       return;
     }
   }
-  if (is_finisher && it > 0) finish_tile(tile - stride, it - 1);
+  if (it > 0) finish_tile(tile - stride, it - 1, warp, kStreamWarps);  // nothing left to walk: all warps
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -454,9 +454,10 @@ static cudaError_t launch_q_t(const QRmsArgs& a, int tpr, cudaStream_t stream) {
   const int rpc = 128 / tpr;  // row slots per 128-thread CTA
   const int ctas = 5;         // CTAs per SM the register cap admits (640 threads); more ran slower
   const int stage_bytes = (a.row_bytes + 15) & ~15;
-  // ring depth: what about 200 KB of shared memory per SM allows, at least 2 (one row ahead)
+  // ring depth: what 196 KB of shared memory per SM (a carve-out the hardware offers; the next one
+  // is all 228 KB) allows with `ctas` CTAs resident and 1 KB reserved per CTA; at least 2 (one row ahead)
   int stages = 2;
-  while (stages < 4 && QSlot::bytes(stages + 1, stage_bytes, tpr) * rpc * ctas <= 200 * 1024) ++stages;
+  while (stages < 4 && (QSlot::bytes(stages + 1, stage_bytes, tpr) * rpc + 1024) * ctas <= 196 * 1024) ++stages;
   const size_t smem = QSlot::bytes(stages, stage_bytes, tpr) * rpc;
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   auto kern = qrms_rowslot_kernel<QT, DT, HB>;
