@@ -238,10 +238,10 @@ struct ShortTile {
 };
 
 template <int DT, int OP, int VPL>
-__global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const LaneRowArgs a) {
+__global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const LaneRowArgs a, const int tile_rows) {
   constexpr int PV = Elem<DT>::kPerVec;
   constexpr int V = 32 * VPL;
-  constexpr int TR = ShortTile<VPL>::kRows;
+  constexpr int TR = ShortTile<VPL>::kRows;  // buffer rows; a tile has tile_rows <= TR of them
   constexpr int kPitchVecs = V + 1;  // odd number of 16-byte units: conflict-free lane-per-row walk
   constexpr int kBufVecs = TR * kPitchVecs;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
   uint4* gs = static_cast<uint4*>(a.sum_out);
   uint4* gy = static_cast<uint4*>(a.y);
   const bool has_res = gr != nullptr;
-  const int64_t n_tiles = (a.rows + TR - 1) / TR;
+  const int64_t n_tiles = (a.rows + tile_rows - 1) / tile_rows;
 
   // gamma / beta of this lane's vectors, widened once
   float gam[VPL][PV], bet[VPL][PV];
@@ -276,8 +276,8 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
 #pragma unroll
       for (int k = 0; k < kRowsPerMover; ++k) {
         const int r = mover + kMovers * k;
-        const int64_t row = tile * TR + r;
-        if (r < TR && row < a.rows) {
+        const int64_t row = tile * tile_rows + r;
+        if (r < tile_rows && row < a.rows) {
 #pragma unroll
           for (int j = 0; j < VPL; ++j) cp_async16(buf + r * kPitchVecs + lane + 32 * j, g + row * V + lane + 32 * j);
         }
@@ -288,8 +288,8 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
 
   // pass 2 of one tile
   auto store_tile = [&](int64_t tile, int slot, int parity) {
-    const int64_t row0 = tile * TR;
-    const int live = static_cast<int>(min(static_cast<int64_t>(TR), a.rows - row0));
+    const int64_t row0 = tile * tile_rows;
+    const int live = static_cast<int>(min(static_cast<int64_t>(tile_rows), a.rows - row0));
     const uint4* xb = smem_v + slot * kBufVecs;
 #pragma unroll
     for (int k = 0; k < kRowsPerMover; ++k) {
@@ -334,8 +334,8 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
 
   int slot = 0, it = 0;
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += stride, ++it) {
-    const int64_t row0 = tile * TR;
-    const int live = static_cast<int>(min(static_cast<int64_t>(TR), a.rows - row0));
+    const int64_t row0 = tile * tile_rows;
+    const int live = static_cast<int>(min(static_cast<int64_t>(tile_rows), a.rows - row0));
     uint4* xb = smem_v + slot * kBufVecs;
     const int next_slot = slot == 2 ? 0 : slot + 1;
     const int prev_slot = slot == 0 ? 2 : slot - 1;
@@ -798,6 +798,18 @@ static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// Rows per tile for a persistent one-CTA-per-SM kernel: the smallest tile that still needs no more
+// rounds over the SMs than tiles of `max_rows` would, so that every SM gets the same number of rows
+// (16384 rows: 4 rounds of 28 rows instead of 4 of 32 on some SMs and 3 on the others).
+static int balanced_tile_rows(int64_t rows, int max_rows) {
+  const int64_t per_round = static_cast<int64_t>(max_rows) * kSmCount;
+  const int64_t rounds = (rows + per_round - 1) / per_round;
+  int64_t tr = (rows + rounds * kSmCount - 1) / (rounds * kSmCount);
+  if (tr > max_rows) tr = max_rows;
+  if (tr < 1) tr = 1;
+  return static_cast<int>(tr);
+}
+
 template <int DT, int OP, int VPL>
 static cudaError_t launch_shortrow_t(const LaneRowArgs& a, cudaStream_t stream) {
   constexpr int TR = ShortTile<VPL>::kRows;
@@ -808,9 +820,10 @@ static cudaError_t launch_shortrow_t(const LaneRowArgs& a, cudaStream_t stream) 
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                            static_cast<int>((smem + 1024) * 100 / (228 * 1024) + 1));
   if (e != cudaSuccess) return e;
-  int64_t tiles = (a.rows + TR - 1) / TR;
+  const int tile_rows = balanced_tile_rows(a.rows, TR);
+  int64_t tiles = (a.rows + tile_rows - 1) / tile_rows;
   int64_t grid = tiles < kSmCount ? tiles : kSmCount;
-  kern<<<static_cast<unsigned>(grid), kShortThreads, smem, stream>>>(a);
+  kern<<<static_cast<unsigned>(grid), kShortThreads, smem, stream>>>(a, tile_rows);
   return cudaGetLastError();
 }
 
@@ -839,9 +852,7 @@ static cudaError_t launch_shortrow_dt(const LaneRowArgs& a, cudaStream_t stream)
 // Rows per tile, ring depth and grid of the streaming kernel.  Problems with fewer rows than the
 // device has row slots get smaller tiles, so that every SM has one.
 static void stream_shape(int64_t rows, bool res, int& TR, int& D, int& CV, int64_t& grid) {
-  TR = 32;
-  if (rows < static_cast<int64_t>(32) * kSmCount) TR = static_cast<int>((rows + kSmCount - 1) / kSmCount);
-  if (TR < 1) TR = 1;
+  TR = balanced_tile_rows(rows, 32);
   // 2 KB per copy: the copy engine takes about 35 ns per copy whatever its size, and one warp's
   // copies deliver an SM's share of HBM only from that size on.  The ring is kept to 135 KB: what
   // shared memory does not take stays L1, which bounds the loads pass 2 can have in flight.
