@@ -323,7 +323,20 @@ def gpu_arm(args):
     if rank == 0:
         sampler.start()
     ms = timed(run.step, args.steps, args.warmup)
+    if rank == 0:
+        # the timed region can be shorter than one nvidia-smi sampling period: keep the same launches going
+        # (untimed) for 0.4 s so that the clock record has samples taken under this load
+        t_end, i = time.time() + 0.4, 0
+        while time.time() < t_end:
+            run.step(i)
+            i += 1
+            if i % 32 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "timed region + 0.4 s of the same launches, 100 ms period"
+    barrier()
     raise_for_status(st)
 
     # ---- end to end: host buffers in, host rows out, through the same call ----
