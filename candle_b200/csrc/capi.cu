@@ -285,4 +285,53 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   return cuda_result(cb200::launch_qrms_rowreg(qtype, out_dtype, a, stream), name);
 }
 
+int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* ids, const void* alpha,
+                                    void* const* dsts, int n_dsts, int64_t vocab, int32_t hidden, int64_t n_ids,
+                                    float eps, int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
+                                    int flags, cb200_status* status, cb200_stream_t stream) {
+  const char* name = "cb200_qembedding_rms_norm_owner";
+  if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
+  if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
+  if (dsts == nullptr || n_dsts < 1 || n_dsts > 8)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: between 1 and 8 destinations are supported, got %d", name, n_dsts);
+  int rc = check_lookup(name, qtable, ids, dsts[0], vocab, hidden, n_ids, id_dtype);
+  if (rc != CB200_OK) return rc;
+  if (hidden % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by 32", name, hidden);
+  if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
+                (long long)vocab_end, (long long)vocab);
+  if (n_ids == 0) return CB200_OK;
+  if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  if (!aligned16(alpha) || (reinterpret_cast<uintptr_t>(qtable) & 1u))
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha must be 16-byte aligned, the table 2-byte aligned", name);
+  for (int d = 0; d < n_dsts; ++d)
+    if (dsts[d] == nullptr || !aligned16(dsts[d]))
+      return fail(CB200_E_INVALID_ARGUMENT, "%s: destination %d is null or not 16-byte aligned", name, d);
+  if (out_dtype == CB200_DTYPE_F32 || !cb200::qrms_rowreg_supported(out_dtype, hidden))
+    return fail(CB200_E_INVALID_ARGUMENT,
+                "%s: needs the single-launch kernel (f16 / bf16 output, hidden a multiple of 32 that splits "
+                "over 32, 64 or 128 threads); got dtype %d, hidden %d", name, out_dtype, hidden);
+  cb200::QRmsArgs a{};
+  a.qtable = static_cast<const unsigned char*>(qtable);
+  a.ids = ids;
+  a.alpha = static_cast<const uint4*>(alpha);
+  a.y = static_cast<uint4*>(dsts[0]);
+  a.id_dtype = id_dtype;
+  a.vocab = vocab;
+  a.vocab_begin = vocab_begin;
+  a.vocab_end = vocab_end;
+  a.status = status;
+  a.rows = n_ids;
+  a.V = hidden / 8;
+  a.n = hidden;
+  a.row_bytes = hidden / 32 * cb200::qblock_bytes(qtype);
+  a.bulk = aligned16(qtable) && a.row_bytes % 16 == 0;
+  a.eps = eps;
+  a.flags = flags;
+  a.owned_only = 1;
+  a.n_more = n_dsts - 1;
+  for (int d = 1; d < n_dsts; ++d) a.y_more[d - 1] = static_cast<uint4*>(dsts[d]);
+  return cuda_result(cb200::launch_qrms_rowreg(qtype, out_dtype, a, stream), name);
+}
+
 }  // extern "C"

@@ -233,6 +233,14 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       }
     }
     const int kind = slot.kinds[stage];
+    if (a.owned_only && kind == kRowMasked) {  // another rank owns this row and writes it
+      if (tpr > 32)
+        row_barrier(bar_id, tpr);
+      else
+        __syncwarp();
+      stage = stage + 1 == stages ? 0 : stage + 1;
+      continue;
+    }
     if (kind == kRowDecode) {
       // a wait that runs out is recorded and acted on after the row's synchronisation points,
       // where the whole slot sees the flag and can leave together
@@ -295,19 +303,32 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       uint4* yr = a.y + row * a.V;
       // |h| >= the smallest block scale for every non-zero element: above 2^-40 no product with
       // 1/m (m <= 2^60) can fall under 2^-100, and the guard can go.
+      // one finished 32-byte piece to the local buffer and to every further destination
+      auto put = [&](int p, const uint4& lo, const uint4& hi) {
+        stg_stream(yr + 2 * p, lo);
+        stg_stream(yr + 2 * p + 1, hi);
+#pragma unroll
+        for (int d = 0; d < 7; ++d) {
+          if (d < a.n_more) {
+            uint4* dst = a.y_more[d] + row * a.V + 2 * p;
+            stg_stream(dst, lo);
+            stg_stream(dst + 1, hi);
+          }
+        }
+      };
       if (row_dmin >= 9.0949470e-13f) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          stg_stream(yr + 2 * p, rms_output_vec<DT, false>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div));
-          stg_stream(yr + 2 * p + 1, rms_output_vec<DT, false>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
+          put(p, rms_output_vec<DT, false>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
+              rms_output_vec<DT, false>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
         }
       } else {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          stg_stream(yr + 2 * p, rms_output_vec<DT, true>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div));
-          stg_stream(yr + 2 * p + 1, rms_output_vec<DT, true>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
+          put(p, rms_output_vec<DT, true>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
+              rms_output_vec<DT, true>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
         }
       }
     }

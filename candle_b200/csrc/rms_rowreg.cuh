@@ -61,6 +61,12 @@ struct QRmsArgs {
   int bulk;       // 1: rows are 16-byte multiples and the table is 16-byte aligned
   float eps;
   int flags;
+  // Owner-writes-to-all mode for a vocabulary-sharded table: rows whose id lies outside
+  // [vocab_begin, vocab_end) are skipped instead of written as -0.0, and every finished row also
+  // goes to `n_more` further buffers of the same shape (peers' memory mapped into this process).
+  int owned_only;
+  int n_more;
+  uint4* y_more[7];
 };
 
 // Shared-memory layout of one CTA of the row-register kernels (per row slot `ty`).

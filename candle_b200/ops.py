@@ -210,3 +210,34 @@ def qembedding_rms_norm(qtensor, ids: torch.Tensor, alpha: torch.Tensor, eps: fl
     if check:
         raise_for_status(st)
     return (y, g) if return_gathered else y
+
+
+def qembedding_rms_norm_owner(qtensor, ids: torch.Tensor, alpha: torch.Tensor, eps: float, dst_ptrs, *,
+                              vocab_range: tuple[int, int], vocab: int, flags: int = 0,
+                              status: torch.Tensor | None = None) -> None:
+    """Owner-writes-to-all step of a vocabulary-sharded lookup + RMS norm: the ids inside
+    ``vocab_range`` are decoded from this rank's slice ``qtensor``, normalised, and stored into every
+    buffer of ``dst_ptrs`` (device addresses of ``[ids.numel(), hidden]`` buffers of ``alpha.dtype``:
+    this rank's own first, then the peers' mapped ones).  Ids owned by other ranks are skipped; the
+    caller synchronises the ranks before reading.  Invalid ids are recorded in ``status``."""
+    import ctypes
+
+    from .quantized import QTensor  # local import: quantized imports this module
+
+    if not isinstance(qtensor, QTensor) or len(qtensor.shape) != 2:
+        raise CandleError("qembedding expects a rank-2 QTensor")
+    if alpha.dtype not in _DTYPES:
+        raise CandleError(f"unsupported dtype for rmsnorm {alpha.dtype}")
+    local_vocab, hidden = qtensor.shape
+    if alpha.dim() != 1 or alpha.shape[0] != hidden or not alpha.is_contiguous():
+        raise CandleError(f"shape mismatch in rms-norm {list(ids.shape) + [hidden]} {_dims(alpha)}")
+    flat = _ids_checks(ids.reshape(-1))
+    _same_device(qtensor.data, flat, alpha)
+    begin, end = vocab_range
+    if end - begin != local_vocab:
+        raise CandleError(f"vocab shard [{begin}, {end}) does not match the table's {local_vocab} rows")
+    ptrs = [int(p) for p in dst_ptrs]
+    arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    _cabi.call("cb200_qembedding_rms_norm_owner", _ptr(qtensor.data), qtensor.dtype.value, _ptr(flat), _ptr(alpha),
+               ctypes.cast(arr, ctypes.c_void_p), len(ptrs), vocab, hidden, flat.shape[0], float(eps),
+               _DTYPES[alpha.dtype], _ID_DTYPES[flat.dtype], begin, end, flags, _ptr(status), _stream(alpha))

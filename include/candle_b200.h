@@ -178,6 +178,27 @@ CB200_API int cb200_qembedding_rms_norm(const void* qtable, int qtype, const voi
                               int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
                               int flags, cb200_status* status, cb200_stream_t stream);
 
+/*
+ * The exchange step of a vocabulary-sharded table fused into the lookup: the rank that owns a row
+ * produces it and stores it in every rank's output buffer.  `dsts[0 .. n_dsts)` (a HOST array of
+ * 1..8 device pointers) are buffers of the same shape [n_ids, hidden]: this rank's own and the
+ * peers' buffers mapped into this process (CUDA IPC / virtual-memory mapping over NVLink).  The
+ * call decodes and RMS-normalises only the ids inside [vocab_begin, vocab_end) and writes each
+ * finished row to all destinations with plain stores; rows owned by other ranks are not touched.
+ * When every rank has made the call and the ranks have synchronised (the caller's barrier, after
+ * which the stores are visible), each buffer holds all rows, bit-identical to the unsharded
+ * lookup + norm.  Per GPU this moves (N-1)/N of the output over NVLink once and does 1/N of the
+ * decode and norm work, where the masked lookup + all-reduce of candle's tensor-parallel example
+ * (candle-examples/examples/llama_multiprocess/model.rs:31-90) moves twice that and normalises
+ * every row on every rank.  A buffer may be reused only after its readers are done on every rank.
+ * Needs the single-launch kernel: f16 / bf16 output and a hidden size it has a split for.
+ */
+CB200_API int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* ids, const void* alpha,
+                                    void* const* dsts, int n_dsts, int64_t vocab, int32_t hidden,
+                                    int64_t n_ids, float eps, int out_dtype, int id_dtype,
+                                    int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
+                                    cb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

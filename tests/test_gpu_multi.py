@@ -1,6 +1,7 @@
 """Multi-GPU checks (need >= 2 CUDA devices; skipped otherwise): the vocab-sharded lookup summed by
 NCCL equals the unsharded CPU oracle bit for bit (-0.0 included), with and without the
-reduce-scatter variant, and row sharding reproduces the unsharded rows."""
+reduce-scatter variant and with the owner-writes-to-all variant over peer-mapped buffers, and row
+sharding reproduces the unsharded rows."""
 import os
 import socket
 import sys
@@ -54,6 +55,26 @@ def _worker(rank, world, port, ret):
             ys = emb.forward_rms_norm(ids_tensor(ids, dev), from_oracle(alpha, "bf16", dev), 1e-5, scatter=True)
             rb, re = row_shard(n, rank, world)
             ok = ok and np.array_equal(to_oracle(ys), want[rb:re])
+            # owner-writes-to-all: peers' buffers mapped into this process, rows stored by their owner
+            from candle_b200.ops import new_status as _new_status
+            from candle_b200.parallel import peer_mapped_empty
+
+            try:
+                shared, dsts = peer_mapped_empty((n, hidden), torch.bfloat16, dev)
+            except Exception as exc:  # no peer mapping on this system: the variant cannot run at all
+                print(f"peer-mapped buffers unavailable, owner-writes variant not exercised: {exc}", flush=True)
+                shared = None
+            if shared is not None:
+                shared.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
+                st2 = _new_status(dev)
+                emb.forward_rms_norm_owner(ids_tensor(ids, dev), from_oracle(alpha, "bf16", dev), 1e-5, dsts,
+                                           status=st2)
+                torch.cuda.synchronize()
+                dist.barrier()
+                torch.cuda.synchronize()
+                ok = ok and np.array_equal(to_oracle(shared), want) and st2[0].item() == 0
         # the same through the C entry point with a communicator of its own
         from candle_b200 import _nccl
         from candle_b200.ops import _stream, new_status

@@ -429,6 +429,48 @@ def test_sharded_entry_point_single_rank(cb):
         _nccl.comm_destroy(comm)
 
 
+@pytest.mark.parametrize("qtype,gq", [("q8_0", "Q8_0"), ("q4_0", "Q4_0")])
+def test_owner_writes_variant_emulated_on_one_gpu(cb, qtype, gq):
+    # Two "ranks" run one after the other on this GPU, each over its half of the vocabulary and
+    # both writing into the same two buffers: afterwards either buffer holds every row, equal to
+    # the unsharded oracle, and no row was written by a rank that does not own it.
+    from candle_b200.ops import new_status, qembedding_rms_norm_owner
+
+    rng = np.random.default_rng(53)
+    vocab, hidden, n = 1000, 4096, 777
+    qt = make_qtable(rng, qtype, vocab, hidden)
+    ids = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+    alpha = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+    want = oracle.rms_norm(oracle.qembedding(qt, qtype, ids, "bf16"), alpha, 1e-5, "bf16")
+    ta, tids = from_oracle(alpha, "bf16"), ids_tensor(ids)
+    bufs = [torch.full((n, hidden), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    st = new_status("cuda")
+    halves = [(0, 500), (500, 1000)]
+    for r, (b, e) in enumerate(halves):
+        local = cb.QTensor.from_raw(torch.from_numpy(qt[b:e]), getattr(cb.GgmlDType, gq), (e - b, hidden), device="cuda")
+        qembedding_rms_norm_owner(local, tids, ta, 1e-5, [bufs[r].data_ptr(), bufs[1 - r].data_ptr()],
+                                  vocab_range=(b, e), vocab=vocab, status=st)
+        if r == 0:  # after the first rank only its own rows exist
+            torch.cuda.synchronize()
+            owned = torch.from_numpy(ids.astype(np.int64) < 500).cuda()
+            assert torch.isnan(bufs[0][~owned].float()).all() and torch.isnan(bufs[1][~owned].float()).all()
+            assert np.array_equal(to_oracle(bufs[1][owned]), want[owned.cpu().numpy()])
+    torch.cuda.synchronize()
+    assert st[0].item() == 0
+    for buf in bufs:
+        assert np.array_equal(to_oracle(buf), want)
+    # an id beyond the table is reported by whoever sees it; f32 output and zero destinations are refused
+    bad = torch.tensor([vocab], dtype=torch.int64, device="cuda")
+    qembedding_rms_norm_owner(local, bad, ta, 1e-5, [bufs[0].data_ptr()], vocab_range=(500, 1000), vocab=vocab, status=st)
+    torch.cuda.synchronize()
+    assert (st[0].item() & 0xFFFFFFFF) == 1 and st[2].item() == vocab
+    with pytest.raises(Exception, match="destinations"):
+        qembedding_rms_norm_owner(local, tids, ta, 1e-5, [], vocab_range=(500, 1000), vocab=vocab, status=st)
+    with pytest.raises(Exception, match="single-launch"):
+        qembedding_rms_norm_owner(local, tids, torch.ones(hidden, device="cuda"), 1e-5, [bufs[0].data_ptr()],
+                                  vocab_range=(500, 1000), vocab=vocab, status=st)
+
+
 # ------------------------------------------------------------------------------------------------
 # front-end error behaviour (candle's messages)
 # ------------------------------------------------------------------------------------------------
