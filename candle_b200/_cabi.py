@@ -31,7 +31,7 @@ SIGNATURES = {
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 ID_U8, ID_U32, ID_I64 = 0, 1, 2
-QTYPE_Q4_0, QTYPE_Q8_0 = 2, 8
+QTYPE_Q4_0, QTYPE_Q4_1, QTYPE_Q5_0, QTYPE_Q5_1, QTYPE_Q8_0 = 2, 3, 6, 7, 8
 FLAG_FAST_SUM, FLAG_FORCE_LANEROW, FLAG_FORCE_GENERIC, FLAG_FORCE_REPLAY = 1, 0x100, 0x200, 0x400
 STATUS_OK, STATUS_INVALID_INDEX, STATUS_WAIT_TIMEOUT = 0, 1, 2
 

@@ -27,7 +27,9 @@ int cuda_result(cudaError_t e, const char* what) {
 
 bool valid_dtype(int d) { return d == CB200_DTYPE_F32 || d == CB200_DTYPE_F16 || d == CB200_DTYPE_BF16; }
 bool valid_id_dtype(int d) { return d == CB200_ID_U8 || d == CB200_ID_U32 || d == CB200_ID_I64; }
-bool valid_qtype(int q) { return q == CB200_QTYPE_Q4_0 || q == CB200_QTYPE_Q8_0; }
+bool valid_qtype(int q) { return cb200::qblock_bytes(q) != 0; }
+// the formats the single-launch lookup + norm kernel decodes
+bool fusable_qtype(int q) { return q == CB200_QTYPE_Q4_0 || q == CB200_QTYPE_Q8_0; }
 int elem_bytes(int d) { return d == CB200_DTYPE_F32 ? 4 : 2; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -253,7 +255,8 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
   if (!all_aligned16(alpha, y, gathered) || (reinterpret_cast<uintptr_t>(qtable) & 1u))
     return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha, y and gathered must be 16-byte aligned, the table 2-byte aligned", name);
-  const bool fused = out_dtype != CB200_DTYPE_F32 && cb200::qrms_rowreg_supported(out_dtype, hidden) &&
+  const bool fused = fusable_qtype(qtype) && out_dtype != CB200_DTYPE_F32 &&
+                     cb200::qrms_rowreg_supported(out_dtype, hidden) &&
                      !(flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC));
   if (!fused) {
     // Two launches (f32 output, a row length the fused kernel has no exact split for, or a forced
@@ -307,10 +310,11 @@ int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* i
   for (int d = 0; d < n_dsts; ++d)
     if (dsts[d] == nullptr || !aligned16(dsts[d]))
       return fail(CB200_E_INVALID_ARGUMENT, "%s: destination %d is null or not 16-byte aligned", name, d);
-  if (out_dtype == CB200_DTYPE_F32 || !cb200::qrms_rowreg_supported(out_dtype, hidden))
+  if (!fusable_qtype(qtype) || out_dtype == CB200_DTYPE_F32 || !cb200::qrms_rowreg_supported(out_dtype, hidden))
     return fail(CB200_E_INVALID_ARGUMENT,
-                "%s: needs the single-launch kernel (f16 / bf16 output, hidden a multiple of 32 that splits "
-                "over 32, 64 or 128 threads); got dtype %d, hidden %d", name, out_dtype, hidden);
+                "%s: needs the single-launch kernel (Q4_0 / Q8_0 blocks, f16 / bf16 output, hidden a multiple of 32 "
+                "that splits over 32, 64 or 128 threads); got format %d, dtype %d, hidden %d", name, qtype,
+                out_dtype, hidden);
   cb200::QRmsArgs a{};
   a.qtable = static_cast<const unsigned char*>(qtable);
   a.ids = ids;

@@ -289,6 +289,15 @@ cudaError_t launch_qgather(int qtype, int out_dtype, const QGatherArgs& a, cudaS
   if (qtype == CB200_QTYPE_Q8_0) {
     CB200_QG(CB200_QTYPE_Q8_0)
   }
+  if (qtype == CB200_QTYPE_Q4_1) {
+    CB200_QG(CB200_QTYPE_Q4_1)
+  }
+  if (qtype == CB200_QTYPE_Q5_0) {
+    CB200_QG(CB200_QTYPE_Q5_0)
+  }
+  if (qtype == CB200_QTYPE_Q5_1) {
+    CB200_QG(CB200_QTYPE_Q5_1)
+  }
   CB200_QG(CB200_QTYPE_Q4_0)
 #undef CB200_QG
 }
@@ -332,6 +341,12 @@ cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks,
   }
   if (qtype == CB200_QTYPE_Q8_0) {
     CB200_DQ(CB200_QTYPE_Q8_0)
+  } else if (qtype == CB200_QTYPE_Q4_1) {
+    CB200_DQ(CB200_QTYPE_Q4_1)
+  } else if (qtype == CB200_QTYPE_Q5_0) {
+    CB200_DQ(CB200_QTYPE_Q5_0)
+  } else if (qtype == CB200_QTYPE_Q5_1) {
+    CB200_DQ(CB200_QTYPE_Q5_1)
   } else {
     CB200_DQ(CB200_QTYPE_Q4_0)
   }

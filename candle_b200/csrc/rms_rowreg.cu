@@ -18,34 +18,41 @@ namespace cb200 {
 // SM, each thread with up to eight 16-byte loads outstanding, keep about 100 KB of reads in flight
 // per SM, which measurement shows is what saturates HBM on B200 as long as the loop stays lean:
 // the rare exact replay is kept out of line for that reason.
-// Without a residual a row brings only half the bytes, and the loads of one row at a time no
-// longer cover the memory latency: with kModeAhead set (rows without residual of at most four
-// vectors per thread, where the registers allow it) the next row is loaded into a second set of
-// registers before the current one is worked on.  kModeGather: rows come from a table by id.
-constexpr int kModeGather = 1, kModeAhead = 2;
+// Look-ahead (kModeAhead): the next row is loaded into a second set of registers before the
+// current one is worked on, so that an SM's loads never pause for the per-row reduction and
+// decision.  Without a residual a row brings only half the bytes and this is what keeps enough of
+// them in flight; with a residual (kModeAheadRes) x and the residual of the next row are both held,
+// and the registers for that come from not keeping alpha resident (it is re-read through L1).
+// kModeGather: rows come from a table by id.  The launcher enables look-ahead only for the
+// vectors-per-thread counts whose register need fits.
+constexpr int kModeGather = 1, kModeAhead = 2, kModeAheadRes = 4;
 
 template <int DT, int VPT, int BT, int MODE>
 __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRegArgs a) {
   constexpr bool GATHER = (MODE & kModeGather) != 0;
-  constexpr bool AHEAD = (MODE & kModeAhead) != 0;
+  constexpr bool AHEAD_RES = (MODE & kModeAheadRes) != 0;
+  constexpr bool AHEAD = (MODE & kModeAhead) != 0 || AHEAD_RES;
+  constexpr bool ALPHA_REGS = !AHEAD_RES;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
   RowRegSmem sm(smem_raw, rpc, tpr, a.V, ty);
-  const bool has_res = MODE == 0 && a.res != nullptr;
+  const bool has_res = !GATHER && !AHEAD && a.res != nullptr;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * rpc;
   const int64_t first = static_cast<int64_t>(blockIdx.x) * rpc + ty;
 
-  uint4 al[VPT];
-  float wv[VPT];
+  uint4 al[ALPHA_REGS ? VPT : 1];
+  float wv[ALPHA_REGS ? VPT : 1];
+  if (ALPHA_REGS) {
 #pragma unroll
-  for (int k = 0; k < VPT; ++k) {
-    al[k] = __ldg(a.alpha + k * tpr + tx);
-    wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
+    for (int k = 0; k < VPT; ++k) {
+      al[k] = __ldg(a.alpha + k * tpr + tx);
+      wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
+    }
   }
 
   // The row one step ahead (AHEAD) and, for gathered rows, its id and the id two steps ahead:
   // ids are loaded a whole iteration before the address they make is needed.
-  uint4 nx[AHEAD ? VPT : 1];
+  uint4 nx[AHEAD ? VPT : 1], nr[AHEAD_RES ? VPT : 1];
   uint64_t id_ahead = 0, id_ahead2 = 0;
   if (GATHER && !AHEAD && first < a.rows) id_ahead = read_id(a.ids, a.id_dtype, first);
   if (AHEAD && first < a.rows) {
@@ -56,6 +63,11 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
     const uint4* xr = a.x + (GATHER ? (id_ahead < static_cast<uint64_t>(a.vocab) ? id_ahead : 0) : first) * a.V + tx;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) nx[k] = ldg_stream(xr + k * tpr);
+    if (AHEAD_RES) {
+      const uint4* rr = a.res + first * a.V + tx;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) nr[k] = ldg_stream(rr + k * tpr);
+    }
   }
 
   for (int64_t row = first; row < a.rows; row += stride) {
@@ -68,7 +80,7 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
         if (!live && tx == 0) report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
       }
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) h[k] = nx[k];
+      for (int k = 0; k < VPT; ++k) h[k] = AHEAD_RES ? add_round_vec<DT>(nx[k], nr[k]) : nx[k];
       if (row + stride < a.rows) {
         if (GATHER) {
           id_ahead = id_ahead2;
@@ -78,6 +90,11 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
             a.x + (GATHER ? (id_ahead < static_cast<uint64_t>(a.vocab) ? id_ahead : 0) : row + stride) * a.V + tx;
 #pragma unroll
         for (int k = 0; k < VPT; ++k) nx[k] = ldg_stream(xn + k * tpr);
+        if (AHEAD_RES) {
+          const uint4* rn = a.res + (row + stride) * a.V + tx;
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) nr[k] = ldg_stream(rn + k * tpr);
+        }
       }
     } else {
       const uint4* xr;
@@ -103,20 +120,28 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
     }
     float lsum = 0.0f, lw = 0.0f;
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) accumulate_vec_w<DT>(h[k], wv[k], lsum, lw);
+    for (int k = 0; k < VPT; ++k)
+      accumulate_vec_w<DT>(h[k], ALPHA_REGS ? wv[k] : static_cast<float>(a.n - 8 * (k * tpr + tx)), lsum, lw);
     bool replayed;
     const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm, sm.rows, replayed);
     if (replayed) {  // rare: nothing was kept in registers across the replay
+      if (ALPHA_REGS) {
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        al[k] = __ldg(a.alpha + k * tpr + tx);
-        wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
+        for (int k = 0; k < VPT; ++k) {
+          al[k] = __ldg(a.alpha + k * tpr + tx);
+          wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
+        }
       }
       if (AHEAD && row + stride < a.rows) {
         const uint4* xn =
             a.x + (GATHER ? (id_ahead < static_cast<uint64_t>(a.vocab) ? id_ahead : 0) : row + stride) * a.V + tx;
 #pragma unroll
         for (int k = 0; k < VPT; ++k) nx[k] = ldg_stream(xn + k * tpr);
+        if (AHEAD_RES) {
+          const uint4* rn = a.res + (row + stride) * a.V + tx;
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) nr[k] = ldg_stream(rn + k * tpr);
+        }
       }
     }
     if (live) {
@@ -130,7 +155,9 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
       const float r = fast_div ? __frcp_rn(m) : 0.0f;
       uint4* yr = a.y + row * a.V + tx;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) stg_stream(yr + k * tpr, rms_output_vec<DT>(h[k], al[k], m, r, fast_div));
+      for (int k = 0; k < VPT; ++k)
+        stg_stream(yr + k * tpr,
+                   rms_output_vec<DT>(h[k], ALPHA_REGS ? al[k] : __ldg(a.alpha + k * tpr + tx), m, r, fast_div));
     }
   }
 }
@@ -433,7 +460,14 @@ static cudaError_t launch_dense_bt(const RmsRowRegArgs& a, int tpr, int rpc, cud
   const bool gather = a.ids != nullptr, plain = a.res != nullptr;
   if (tpr * rpc <= 256) {
     if (gather) return launch_dense_t<DT, VPT, 256, kModeGather | kAheadG>(a, tpr, rpc, stream);
-    if (plain) return launch_dense_t<DT, VPT, 256, 0>(a, tpr, rpc, stream);
+    if (plain) {
+      // look-ahead with a residual pays for rows of up to 4096 columns when there are many of them
+      // (measured: 0.77 -> 0.80 of peak at 4096 columns, 0.75 -> 0.81 at 2048; nothing at 8192, and
+      // a loss when each CTA sees only a few rows)
+      if (kAhead != 0 && tpr <= 128 && a.rows >= 16384)
+        return launch_dense_t<DT, VPT, 256, kAhead ? kModeAheadRes : 0>(a, tpr, rpc, stream);
+      return launch_dense_t<DT, VPT, 256, 0>(a, tpr, rpc, stream);
+    }
     return launch_dense_t<DT, VPT, 256, kAhead>(a, tpr, rpc, stream);
   }
   if (gather) return launch_dense_t<DT, VPT, 512, kModeGather | kAheadG>(a, tpr, rpc, stream);

@@ -1,5 +1,5 @@
-"""The slice of ``candle_core::quantized`` the lookup path needs: a ``QTensor`` of Q4_0 / Q8_0
-blocks resident on the GPU (candle-core/src/quantized/mod.rs:35-38, quantized/cuda.rs:9-20) with
+"""The slice of ``candle_core::quantized`` the lookup path needs: a ``QTensor`` of 32-element
+blocks (Q4_0, Q4_1, Q5_0, Q5_1, Q8_0) resident on the GPU (candle-core/src/quantized/mod.rs:35-38, quantized/cuda.rs:9-20) with
 ``dequantize`` / ``dequantize_f16`` (mod.rs:361-382) and a row lookup."""
 from __future__ import annotations
 
@@ -13,9 +13,12 @@ from .ops import _DTYPES, _ID_DTYPES, _ids_checks, _ptr, _same_device, _stream, 
 
 
 class GgmlDType(enum.Enum):
-    """ggml type ids (candle-core/src/quantized/mod.rs:152-171); only the two on this path."""
+    """ggml type ids (candle-core/src/quantized/mod.rs:152-171): the 32-element block formats."""
 
     Q4_0 = _cabi.QTYPE_Q4_0
+    Q4_1 = _cabi.QTYPE_Q4_1
+    Q5_0 = _cabi.QTYPE_Q5_0
+    Q5_1 = _cabi.QTYPE_Q5_1
     Q8_0 = _cabi.QTYPE_Q8_0
 
     @property
@@ -24,7 +27,7 @@ class GgmlDType(enum.Enum):
 
     @property
     def type_size(self) -> int:
-        return 18 if self is GgmlDType.Q4_0 else 34
+        return {2: 18, 3: 20, 6: 22, 7: 24, 8: 34}[self.value]
 
 
 class QTensor:

@@ -52,8 +52,13 @@ extern "C" {
 #define CB200_ID_U32 1
 #define CB200_ID_I64 2
 
-/* Block formats: ggml type ids as in candle-core/src/quantized/mod.rs:152-171. */
+/* Block formats: ggml type ids as in candle-core/src/quantized/mod.rs:152-171.  Q4_0 and Q8_0 are
+ * accepted everywhere; Q4_1, Q5_0 and Q5_1 by cb200_dequantize and cb200_qembedding, and by
+ * cb200_qembedding_rms_norm through its two-launch route. */
 #define CB200_QTYPE_Q4_0 2
+#define CB200_QTYPE_Q4_1 3
+#define CB200_QTYPE_Q5_0 6
+#define CB200_QTYPE_Q5_1 7
 #define CB200_QTYPE_Q8_0 8
 
 /* flags */

@@ -19,8 +19,8 @@ _LIB_PATH = os.path.join(_HERE, "_build", "libcandle_cpu_oracle.so")
 
 DTYPES = {"f32": 0, "f16": 1, "bf16": 2}
 ID_DTYPES = {np.dtype(np.uint8): 0, np.dtype(np.uint32): 1, np.dtype(np.int64): 2}
-QTYPES = {"q4_0": 2, "q8_0": 8}
-BLOCK_BYTES = {"q4_0": 18, "q8_0": 34}
+QTYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8}  # ggml type ids
+BLOCK_BYTES = {"q4_0": 18, "q4_1": 20, "q5_0": 22, "q5_1": 24, "q8_0": 34}
 QK = 32
 
 

@@ -350,11 +350,26 @@ int oracle_index_select(int64_t elem_size, int id_dtype, const void* src, const 
 #define QK 32
 #define Q4_0_BYTES 18
 #define Q8_0_BYTES 34
+/* BlockQ4_1 {d, m: f16, qs: [u8; 16]} = 20 bytes, BlockQ5_0 {d: f16, qh: [u8; 4], qs: [u8; 16]} = 22,
+ * BlockQ5_1 {d, m: f16, qh: [u8; 4], qs: [u8; 16]} = 24 (k_quants.rs:50-76). */
+#define ORACLE_Q4_1 3
+#define ORACLE_Q5_0 6
+#define ORACLE_Q5_1 7
+#define Q4_1_BYTES 20
+#define Q5_0_BYTES 22
+#define Q5_1_BYTES 24
 
 int64_t oracle_block_bytes(int qtype) {
   if (qtype == ORACLE_Q4_0) return Q4_0_BYTES;
   if (qtype == ORACLE_Q8_0) return Q8_0_BYTES;
+  if (qtype == ORACLE_Q4_1) return Q4_1_BYTES;
+  if (qtype == ORACLE_Q5_0) return Q5_0_BYTES;
+  if (qtype == ORACLE_Q5_1) return Q5_1_BYTES;
   return ORACLE_E_DTYPE;
+}
+
+static inline uint32_t read_u32_le(const uint8_t* p) {
+  return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
 }
 
 /* GgmlType::to_float: Q4_0 k_quants.rs:163-183, Q8_0 k_quants.rs:568-584 (sequential in candle). */
@@ -390,6 +405,65 @@ int oracle_dequantize(int qtype, const void* blocks, float* y, int64_t k, int th
       float d = f16_to_f32(dh);
       const int8_t* qs = (const int8_t*)(blk + 2);
       for (int j = 0; j < QK; j++) y[i * QK + j] = (float)qs[j] * d;
+    }
+    return ORACLE_OK;
+  }
+  if (qtype == ORACLE_Q4_1) { /* k_quants.rs:329-349: (x as f32) * d + m, two roundings */
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+    for (int64_t i = 0; i < nb; i++) {
+      const uint8_t* blk = b + i * Q4_1_BYTES;
+      uint16_t dh, mh;
+      memcpy(&dh, blk, 2);
+      memcpy(&mh, blk + 2, 2);
+      float d = f16_to_f32(dh), m = f16_to_f32(mh);
+      const uint8_t* qs = blk + 4;
+      for (int j = 0; j < QK / 2; j++) {
+        uint8_t x0 = qs[j] & 0x0F, x1 = qs[j] >> 4;
+        float p0 = (float)x0 * d, p1 = (float)x1 * d;
+        y[i * QK + j] = p0 + m;
+        y[i * QK + j + QK / 2] = p1 + m;
+      }
+    }
+    return ORACLE_OK;
+  }
+  if (qtype == ORACLE_Q5_0) { /* k_quants.rs:428-452 */
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+    for (int64_t i = 0; i < nb; i++) {
+      const uint8_t* blk = b + i * Q5_0_BYTES;
+      uint16_t dh;
+      memcpy(&dh, blk, 2);
+      float d = f16_to_f32(dh);
+      uint32_t qh = read_u32_le(blk + 2);
+      const uint8_t* qs = blk + 6;
+      for (int j = 0; j < QK / 2; j++) {
+        uint8_t xh0 = (uint8_t)(((qh >> j) << 4) & 0x10);
+        uint8_t xh1 = (uint8_t)((qh >> (j + 12)) & 0x10);
+        int32_t x0 = (int32_t)((qs[j] & 0x0F) | xh0) - 16;
+        int32_t x1 = (int32_t)((qs[j] >> 4) | xh1) - 16;
+        y[i * QK + j] = (float)x0 * d;
+        y[i * QK + j + QK / 2] = (float)x1 * d;
+      }
+    }
+    return ORACLE_OK;
+  }
+  if (qtype == ORACLE_Q5_1) { /* k_quants.rs:535-562 */
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+    for (int64_t i = 0; i < nb; i++) {
+      const uint8_t* blk = b + i * Q5_1_BYTES;
+      uint16_t dh, mh;
+      memcpy(&dh, blk, 2);
+      memcpy(&mh, blk + 2, 2);
+      float d = f16_to_f32(dh), m = f16_to_f32(mh);
+      uint32_t qh = read_u32_le(blk + 4);
+      const uint8_t* qs = blk + 8;
+      for (int j = 0; j < QK / 2; j++) {
+        uint8_t xh0 = (uint8_t)(((qh >> j) << 4) & 0x10);
+        uint8_t xh1 = (uint8_t)((qh >> (j + 12)) & 0x10);
+        uint8_t x0 = (uint8_t)((qs[j] & 0x0F) | xh0), x1 = (uint8_t)((qs[j] >> 4) | xh1);
+        float p0 = (float)x0 * d, p1 = (float)x1 * d;
+        y[i * QK + j] = p0 + m;
+        y[i * QK + j + QK / 2] = p1 + m;
+      }
     }
     return ORACLE_OK;
   }
@@ -453,6 +527,79 @@ int oracle_quantize(int qtype, const float* x, void* blocks, int64_t k) {
       uint8_t* blk = b + i * Q8_0_BYTES;
       memcpy(blk, &dh, 2);
       for (int j = 0; j < QK; j++) blk[2 + j] = (uint8_t)sat_i8(roundf(xs[j] * id));
+    }
+    return ORACLE_OK;
+  }
+  if (qtype == ORACLE_Q4_1 || qtype == ORACLE_Q5_1) { /* k_quants.rs:295-326, 496-532 */
+    const int bits5 = qtype == ORACLE_Q5_1;
+    const int bb = bits5 ? Q5_1_BYTES : Q4_1_BYTES;
+    for (int64_t i = 0; i < nb; i++) {
+      const float* xs = x + i * QK;
+      float min = INFINITY, max = -INFINITY;
+      for (int j = 0; j < QK; j++) { /* f32::min / f32::max ignore a NaN operand, like fminf / fmaxf */
+        min = fminf(xs[j], min);
+        max = fmaxf(xs[j], max);
+      }
+      float d = (max - min) / (float)((bits5 ? 32 : 16) - 1);
+      float id = d != 0.0f ? 1.0f / d : 0.0f;
+      uint16_t dh = f16_from_f32(d), mh = f16_from_f32(min);
+      uint8_t* blk = b + i * bb;
+      memcpy(blk, &dh, 2);
+      memcpy(blk + 2, &mh, 2);
+      uint32_t qh = 0;
+      uint8_t* qs = blk + (bits5 ? 8 : 4);
+      for (int j = 0; j < QK / 2; j++) {
+        float x0 = (xs[j] - min) * id;
+        float x1 = (xs[QK / 2 + j] - min) * id;
+        uint8_t xi0 = sat_u8(x0 + 0.5f), xi1 = sat_u8(x1 + 0.5f);
+        if (!bits5) {
+          if (xi0 > 15) xi0 = 15;
+          if (xi1 > 15) xi1 = 15;
+          qs[j] = (uint8_t)(xi0 | (xi1 << 4));
+        } else {
+          qs[j] = (uint8_t)((xi0 & 0x0F) | ((xi1 & 0x0F) << 4));
+          qh |= (((uint32_t)xi0 & 0x10u) >> 4) << j;
+          qh |= (((uint32_t)xi1 & 0x10u) >> 4) << (j + QK / 2);
+        }
+      }
+      if (bits5) {
+        blk[4] = (uint8_t)qh;
+        blk[5] = (uint8_t)(qh >> 8);
+        blk[6] = (uint8_t)(qh >> 16);
+        blk[7] = (uint8_t)(qh >> 24);
+      }
+    }
+    return ORACLE_OK;
+  }
+  if (qtype == ORACLE_Q5_0) { /* k_quants.rs:392-425 */
+    for (int64_t i = 0; i < nb; i++) {
+      const float* xs = x + i * QK;
+      float amax = 0.0f, max = 0.0f;
+      for (int j = 0; j < QK; j++) {
+        if (amax < fabsf(xs[j])) {
+          amax = fabsf(xs[j]);
+          max = xs[j];
+        }
+      }
+      float d = max / -16.0f;
+      float id = d != 0.0f ? 1.0f / d : 0.0f;
+      uint16_t dh = f16_from_f32(d);
+      uint8_t* blk = b + i * Q5_0_BYTES;
+      memcpy(blk, &dh, 2);
+      uint32_t qh = 0;
+      for (int j = 0; j < QK / 2; j++) {
+        float x0 = xs[j] * id;
+        float x1 = xs[j + QK / 2] * id;
+        int8_t s0 = sat_i8(x0 + 16.5f), s1 = sat_i8(x1 + 16.5f); /* `as i8` saturates */
+        uint8_t xi0 = (uint8_t)(s0 < 31 ? s0 : 31), xi1 = (uint8_t)(s1 < 31 ? s1 : 31);
+        blk[6 + j] = (uint8_t)((xi0 & 0x0F) | ((xi1 & 0x0F) << 4));
+        qh |= (((uint32_t)xi0 & 0x10u) >> 4) << j;
+        qh |= (((uint32_t)xi1 & 0x10u) >> 4) << (j + QK / 2);
+      }
+      blk[2] = (uint8_t)qh;
+      blk[3] = (uint8_t)(qh >> 8);
+      blk[4] = (uint8_t)(qh >> 16);
+      blk[5] = (uint8_t)(qh >> 24);
     }
     return ORACLE_OK;
   }

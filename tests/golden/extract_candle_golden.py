@@ -142,6 +142,17 @@ def main(ref: str, dst: str) -> None:
         "dequantized": [repr(float(v)) for v in vec],  # strings keep the sign of -0.0
     }
 
+    # the other 32-element block formats: same test shape, values compared after rounding to 3 decimals
+    for name in ("quantize_q4_1", "quantize_q5_0", "quantize_q5_1"):
+        body, line = function_body(qt, name)
+        vec = max(array_literals(body), key=len)
+        assert len(vec) == 128
+        kats[name] = {
+            "source": f"candle-core/tests/quantized_tests.rs:{line}", "src": "0..128 as f32",
+            "dequantized_rounded_3": [repr(float(v)) for v in vec],
+            "rounding": "(1000 * x).round() / 1000 in f32, round half away from zero (round_vector)",
+        }
+
     with open(dst, "w") as f:
         json.dump(kats, f, indent=1)
     print(f"wrote {dst}: {sorted(kats)}")

@@ -50,12 +50,19 @@ def randn(rng, shape, dtype: str, mean=0.0, std=1.0) -> np.ndarray:
 def make_qtable(rng, qtype: str, vocab: int, hidden: int) -> np.ndarray:
     """Raw block bytes [vocab, hidden/32*block_bytes] with the value distributions of the
     benchmark configs: f16 scale |N(0,0.01)|, int8 quants uniform[-127,127] (Q8_0) or 4-bit
-    quants uniform[0,15] (Q4_0)."""
+    quants uniform[0,15]; the formats with a minimum get m ~ N(0,0.05) in f16, the 5-bit formats
+    32 uniform high bits."""
     nb = hidden // 32
     d = np.abs(rng.standard_normal((vocab, nb)) * 0.01).astype(np.float16)
+    parts = [d.view(np.uint8).reshape(vocab, nb, 2)]
+    if qtype in ("q4_1", "q5_1"):
+        m = (rng.standard_normal((vocab, nb)) * 0.05).astype(np.float16)
+        parts.append(m.view(np.uint8).reshape(vocab, nb, 2))
+    if qtype in ("q5_0", "q5_1"):
+        parts.append(rng.integers(0, 256, size=(vocab, nb, 4), dtype=np.int16).astype(np.uint8))
     if qtype == "q8_0":
-        qs = rng.integers(-127, 128, size=(vocab, nb, 32), dtype=np.int16).astype(np.int8).view(np.uint8)
+        parts.append(rng.integers(-127, 128, size=(vocab, nb, 32), dtype=np.int16).astype(np.int8).view(np.uint8))
     else:
-        qs = rng.integers(0, 256, size=(vocab, nb, 16), dtype=np.int16).astype(np.uint8)
-    blocks = np.concatenate([d.view(np.uint8).reshape(vocab, nb, 2), qs], axis=2)
+        parts.append(rng.integers(0, 256, size=(vocab, nb, 16), dtype=np.int16).astype(np.uint8))
+    blocks = np.concatenate(parts, axis=2)
     return np.ascontiguousarray(blocks.reshape(vocab, -1))

@@ -117,6 +117,20 @@ def test_kat_quantize_q4_0_dequantize(cb, kats):
     assert np.array_equal(bits(f16), bits(got.to(torch.float16)))  # diff == 0 in candle's test
 
 
+@pytest.mark.parametrize("qtype", ["q4_1", "q5_0", "q5_1"])
+def test_kat_quantize_q4_1_q5_0_q5_1_dequantize(cb, kats, qtype):
+    k = kats[f"quantize_{qtype}"]  # candle-core/tests/quantized_tests.rs:256-351
+    blocks = oracle.quantize(np.arange(128, dtype=np.float32), qtype)  # the CPU writer of the format
+    q = cb.QTensor.from_raw(torch.from_numpy(blocks), getattr(cb.GgmlDType, qtype.upper()), (128,), device="cuda")
+    got = q.dequantize()
+    scaled = got.cpu().numpy() * np.float32(1000.0)  # candle's round_vector
+    rounded = (np.sign(scaled) * np.floor(np.abs(scaled) + np.float32(0.5))).astype(np.float32) / np.float32(1000.0)
+    assert np.array_equal(rounded, np.asarray([float(v) for v in k["dequantized_rounded_3"]], np.float32))
+    assert np.array_equal(bits(got), oracle.dequantize(blocks, qtype).view(np.uint32))
+    f16 = q.dequantize_f16()
+    assert np.array_equal(bits(f16), bits(got.to(torch.float16)))  # diff == 0 in candle's test
+
+
 # ------------------------------------------------------------------------------------------------
 # norms against the oracle
 # ------------------------------------------------------------------------------------------------
@@ -247,6 +261,24 @@ def test_rms_norm_many_rows_exercises_the_replay_path(cb):
     assert rows_diff <= 64
 
 
+@pytest.mark.parametrize("dtype,cols", [("bf16", 2048), ("f16", 4096), ("bf16", 1536)])
+def test_rms_norm_many_narrow_rows_with_residual_take_the_look_ahead_variant(cb, dtype, cols):
+    # >= 16384 rows of at most 4096 columns with a residual: the register kernel holds the next row's
+    # x and residual while it works on the current one.  Ragged row count; sum_out checked too.
+    rng = np.random.default_rng(91)
+    rows = 16384 + 37
+    x, r = randn(rng, (rows, cols), dtype), randn(rng, (rows, cols), dtype)
+    a = randn(rng, (cols,), dtype, 1.0, 0.1)
+    h = oracle.add(x, r, dtype, threads=0)
+    want = oracle.rms_norm(h, a, 1e-5, dtype, threads=0)
+    xt, rt, at = from_oracle(x, dtype), from_oracle(r, dtype), from_oracle(a, dtype)
+    y, hs = cb.rms_norm(xt, at, 1e-5, residual=rt, return_sum=True)
+    assert np.array_equal(to_oracle(hs), h)
+    assert_norm_equal(y, want, dtype)
+    y2 = cb.rms_norm(xt, at, 1e-5, residual=rt, flags=cb.FLAG_FORCE_REPLAY)
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+
+
 def test_norm_special_values_and_aliasing(cb):
     for dtype in ("f32", "bf16", "f16"):
         x = np.zeros((4, 256), np.float32)
@@ -311,10 +343,10 @@ def test_embedding_edge_cases(cb):
 
 
 @pytest.mark.parametrize("out_dtype", ["f32", "f16", "bf16"])
-@pytest.mark.parametrize("qtype", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("qtype", ["q8_0", "q4_0", "q4_1", "q5_0", "q5_1"])
 def test_qembedding_matches_oracle(cb, qtype, out_dtype):
     rng = np.random.default_rng(13)
-    gq = cb.GgmlDType.Q8_0 if qtype == "q8_0" else cb.GgmlDType.Q4_0
+    gq = getattr(cb.GgmlDType, qtype.upper())
     for vocab, hidden, shape in [(300, 4096, (4, 64)), (64, 256, (33,)), (50, 96, (20,)), (40, 8192, (2, 8))]:
         qt = make_qtable(rng, qtype, vocab, hidden)
         qt[3, :2] = np.asarray([0, 0x80], np.uint8)  # d = -0.0 in one block: exercises the sign of zero
@@ -332,12 +364,12 @@ def test_qembedding_matches_oracle(cb, qtype, out_dtype):
         q.embedding(torch.tensor([vocab], dtype=torch.int64, device="cuda"))
 
 
-@pytest.mark.parametrize("qtype", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("qtype", ["q8_0", "q4_0", "q5_1"])
 def test_vocab_sharded_partials_sum_to_the_unsharded_lookup(cb, qtype):
     # Each shard decodes the ids it owns and writes -0.0 elsewhere; summing the partials in bf16
     # (what the all-reduce does) must reproduce the unsharded lookup bit for bit, -0.0 included.
     rng = np.random.default_rng(17)
-    gq = cb.GgmlDType.Q8_0 if qtype == "q8_0" else cb.GgmlDType.Q4_0
+    gq = getattr(cb.GgmlDType, qtype.upper())
     vocab, hidden, n = 512, 1024, 300
     qt = make_qtable(rng, qtype, vocab, hidden)
     qt[:, :2] = 0  # first block of every row has d = +0: a source of +-0.0 values
@@ -375,10 +407,10 @@ def test_embedding_rms_norm_matches_oracle(cb, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
-@pytest.mark.parametrize("qtype", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("qtype", ["q8_0", "q4_0", "q4_1", "q5_0", "q5_1"])
 def test_qembedding_rms_norm_matches_oracle(cb, qtype, dtype):
     rng = np.random.default_rng(23)
-    gq = cb.GgmlDType.Q8_0 if qtype == "q8_0" else cb.GgmlDType.Q4_0
+    gq = getattr(cb.GgmlDType, qtype.upper())
     for vocab, hidden, shape in [(400, 4096, (6, 100)), (64, 256, (50,)), (30, 96, (12,)), (60, 8192, (3, 40))]:
         qt = make_qtable(rng, qtype, vocab, hidden)
         a = randn(rng, (hidden,), dtype, 1.0, 0.1)

@@ -120,6 +120,24 @@ def test_quantize_q4_0_kat(kats):
     assert np.array_equal(as_f16.reshape(-1), oracle.cast_from_f32(dst, "f16"))
 
 
+@pytest.mark.parametrize("qtype,bytes_per_block", [("q4_1", 20), ("q5_0", 22), ("q5_1", 24)])
+def test_quantize_q4_1_q5_0_q5_1_kats(kats, qtype, bytes_per_block):
+    k = kats[f"quantize_{qtype}"]  # candle-core/tests/quantized_tests.rs:256-351
+    src = np.arange(128, dtype=np.float32)
+    blocks = oracle.quantize(src, qtype)
+    assert blocks.shape == (4 * bytes_per_block,)
+    dst = oracle.dequantize(blocks, qtype)
+    want = np.asarray([float(v) for v in k["dequantized_rounded_3"]], dtype=np.float32)
+    # candle's round_vector: (1000. * x).round() / 1000. in f32, half away from zero
+    scaled = dst * np.float32(1000.0)
+    rounded = (np.sign(scaled) * np.floor(np.abs(scaled) + np.float32(0.5))).astype(np.float32) / np.float32(1000.0)
+    assert np.array_equal(rounded, want)
+    if qtype == "q5_0":  # the first element is -0.0 in candle's vector
+        assert np.signbit(dst[0]) and dst[0] == 0.0
+    as_f16 = oracle.qembedding(blocks.reshape(1, -1), qtype, np.zeros(1, np.uint32), "f16")
+    assert np.array_equal(as_f16.reshape(-1), oracle.cast_from_f32(dst, "f16"))  # diff == 0 in candle's test
+
+
 def test_q8_0_roundtrip_error_bound():
     # No golden Q8_0 dequant vector exists in candle; pin the format through quantise->dequantise:
     # |x - dq(q(x))| <= d/2 per element with d = amax/127 rounded to f16.
