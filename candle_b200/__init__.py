@@ -19,11 +19,12 @@ from .ops import (
     qembedding_rms_norm,
     rms_norm,
 )
+from .host_pipeline import PinnedNormPipeline
 from .nn import Embedding, LayerNorm, QEmbedding, RmsNorm
 from .quantized import GgmlDType, QTensor
 
 __all__ = [
     "CandleError", "InvalidIndex", "rms_norm", "layer_norm", "index_select", "embedding_rms_norm",
-    "qembedding_rms_norm", "Embedding", "LayerNorm", "RmsNorm", "QEmbedding", "QTensor", "GgmlDType",
+    "qembedding_rms_norm", "PinnedNormPipeline", "Embedding", "LayerNorm", "RmsNorm", "QEmbedding", "QTensor", "GgmlDType",
     "FLAG_FAST_SUM", "FLAG_FORCE_LANEROW", "FLAG_FORCE_GENERIC", "FLAG_FORCE_REPLAY",
 ]

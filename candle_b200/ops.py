@@ -77,11 +77,19 @@ def _norm_checks(name: str, xs: torch.Tensor, params: list[tuple[str, torch.Tens
     _same_device(xs, *[p for _, p in params], residual)
 
 
+def _out_check(out: torch.Tensor | None, xs: torch.Tensor) -> torch.Tensor:
+    if out is None:
+        return torch.empty_like(xs)
+    if out.shape != xs.shape or out.dtype != xs.dtype or out.device != xs.device or not out.is_contiguous():
+        raise CandleError(f"out must be a contiguous tensor like the input, got {_dims(out)} for {_dims(xs)}")
+    return out
+
+
 def rms_norm(xs: torch.Tensor, alpha: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
-             return_sum: bool = False, flags: int = 0):
+             return_sum: bool = False, flags: int = 0, out: torch.Tensor | None = None):
     """``candle_nn::ops::rms_norm(xs, alpha, eps)``; with ``residual`` the norm of ``xs + residual``.
 
-    Returns ``y``, or ``(y, xs + residual)`` when ``return_sum`` is set.
+    Returns ``y`` (``out`` when given), or ``(y, xs + residual)`` when ``return_sum`` is set.
     """
     if xs.dim() == 0:
         raise CandleError("unexpected rank, expected: at least 1, got: 0")
@@ -92,7 +100,7 @@ def rms_norm(xs: torch.Tensor, alpha: torch.Tensor, eps: float, *, residual: tor
     _norm_checks("rms-norm", xs, [("alpha", alpha)], residual)
     cols = xs.shape[-1]
     rows = xs.numel() // cols if cols else 0
-    y = torch.empty_like(xs)
+    y = _out_check(out, xs)
     h = torch.empty_like(xs) if return_sum else None
     _cabi.call("cb200_rms_norm", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(y), _ptr(h), rows, cols, float(eps),
                _DTYPES[xs.dtype], flags, _stream(xs))
@@ -100,7 +108,8 @@ def rms_norm(xs: torch.Tensor, alpha: torch.Tensor, eps: float, *, residual: tor
 
 
 def layer_norm(xs: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, eps: float, *,
-               residual: torch.Tensor | None = None, return_sum: bool = False, flags: int = 0):
+               residual: torch.Tensor | None = None, return_sum: bool = False, flags: int = 0,
+               out: torch.Tensor | None = None):
     """``candle_nn::ops::layer_norm(xs, alpha, beta, eps)``; with ``residual`` the norm of ``xs + residual``."""
     if xs.dim() == 0:
         raise CandleError("unexpected rank, expected: at least 1, got: 0")
@@ -112,7 +121,7 @@ def layer_norm(xs: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, eps: f
     _norm_checks("layer-norm", xs, [("alpha", alpha), ("beta", beta)], residual)
     cols = xs.shape[-1]
     rows = xs.numel() // cols if cols else 0
-    y = torch.empty_like(xs)
+    y = _out_check(out, xs)
     h = torch.empty_like(xs) if return_sum else None
     _cabi.call("cb200_layer_norm", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(beta), _ptr(y), _ptr(h), rows, cols,
                float(eps), _DTYPES[xs.dtype], flags, _stream(xs))

@@ -522,3 +522,31 @@ def test_front_end_errors(cb):
         cb.rms_norm(x, torch.ones(8, device="cuda", dtype=torch.float16), 1e-5)
     y = cb.rms_norm(torch.zeros(0, 8, device="cuda"), torch.ones(8, device="cuda"), 1e-5)
     assert y.shape == (0, 8)
+
+
+def test_pinned_host_pipeline_equals_the_single_call(cb):
+    # rows in pinned host memory, normalised in chunks on three streams: same bits as one call
+    rng = np.random.default_rng(61)
+    rows, cols = 5000, 1024
+    x, r = randn(rng, (rows, cols), "bf16"), randn(rng, (rows, cols), "bf16")
+    a, b = randn(rng, (cols,), "bf16", 1.0, 0.1), randn(rng, (cols,), "bf16", 0.0, 0.1)
+    xh, rh = from_oracle(x, "bf16", "cpu").pin_memory(), from_oracle(r, "bf16", "cpu").pin_memory()
+    at, bt = from_oracle(a, "bf16"), from_oracle(b, "bf16")
+    yh = torch.empty(rows, cols, dtype=torch.bfloat16).pin_memory()
+    pipe = cb.PinnedNormPipeline(cols, torch.bfloat16, "cuda", chunk_rows=768)
+    for _ in range(2):  # the second pass reuses every buffer set
+        pipe.run(xh, yh, at, 1e-5, residual_host=rh)
+        torch.cuda.synchronize()
+        want = cb.rms_norm(xh.cuda(), at, 1e-5, residual=rh.cuda())
+        assert torch.equal(yh.view(torch.int16), want.cpu().view(torch.int16))
+    pipe.run(xh, yh, at, 1e-12, residual_host=rh, beta=bt)
+    torch.cuda.synchronize()
+    want = cb.layer_norm(xh.cuda(), at, bt, 1e-12, residual=rh.cuda())
+    assert torch.equal(yh.view(torch.int16), want.cpu().view(torch.int16))
+    assert_norm_equal(want, oracle.layer_norm(oracle.add(x, r, "bf16"), a, b, 1e-12, "bf16"), "bf16")
+    plain = cb.PinnedNormPipeline(cols, torch.bfloat16, "cuda", chunk_rows=2048, with_residual=False)
+    plain.run(xh, yh, at, 1e-5)
+    torch.cuda.synchronize()
+    assert torch.equal(yh.view(torch.int16), cb.rms_norm(xh.cuda(), at, 1e-5).cpu().view(torch.int16))
+    with pytest.raises(cb.CandleError, match="pinned"):
+        pipe.run(xh.clone(), yh, at, 1e-5, residual_host=rh)
