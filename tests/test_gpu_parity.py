@@ -550,3 +550,24 @@ def test_pinned_host_pipeline_equals_the_single_call(cb):
     assert torch.equal(yh.view(torch.int16), cb.rms_norm(xh.cuda(), at, 1e-5).cpu().view(torch.int16))
     with pytest.raises(cb.CandleError, match="pinned"):
         pipe.run(xh.clone(), yh, at, 1e-5, residual_host=rh)
+
+
+def test_table_loaded_from_a_gguf_file_looks_up_like_the_oracle(cb, tmp_path):
+    # write -> read -> QTensor on the GPU -> lookup: the container changes no byte of the blocks
+    from candle_b200 import gguf
+
+    rng = np.random.default_rng(67)
+    vocab, hidden = 200, 1024
+    tables = {"q8_0": make_qtable(rng, "q8_0", vocab, hidden), "q5_1": make_qtable(rng, "q5_1", vocab, hidden)}
+    path = tmp_path / "tables.gguf"
+    with open(path, "wb") as f:
+        gguf.write(f, [("general.architecture", gguf.Value("String", "llama"))],
+                   [(f"{k}.weight", oracle.QTYPES[k], (vocab, hidden), v) for k, v in tables.items()])
+    ids = rng.integers(0, vocab, size=(300,)).astype(np.uint32)
+    with open(path, "rb") as f:
+        content = gguf.Content.read(f)
+        for k, raw in tables.items():
+            q = content.tensor(f, f"{k}.weight", "cuda")
+            assert q.shape == (vocab, hidden) and q.dtype.value == oracle.QTYPES[k]
+            got = q.embedding(ids_tensor(ids), torch.bfloat16)
+            assert np.array_equal(to_oracle(got), oracle.qembedding(raw, k, ids, "bf16"))
