@@ -2,7 +2,7 @@
 
 Run in a checkout that has the reference mounted:
 
-    python tests/golden/extract_candle_golden.py /root/reference tests/golden/candle_kats.json
+    python tests/golden/extract_candle_golden.py <candle checkout> tests/golden/candle_kats.json
 
 It READS the reference's test sources as text (no Rust toolchain is needed), pulls the numeric array
 literals out of the named test functions and writes them, with the file:line they came from, to a
