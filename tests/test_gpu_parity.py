@@ -571,3 +571,39 @@ def test_table_loaded_from_a_gguf_file_looks_up_like_the_oracle(cb, tmp_path):
             assert q.shape == (vocab, hidden) and q.dtype.value == oracle.QTYPES[k]
             got = q.embedding(ids_tensor(ids), torch.bfloat16)
             assert np.array_equal(to_oracle(got), oracle.qembedding(raw, k, ids, "bf16"))
+
+
+def test_cpp_host_mirror_on_the_gpu(cb, tmp_path):
+    # include/candle_b200.hpp driven from a C++ program: rms_norm + residual (bf16) and
+    # Embedding::forward (f32, one id out of range) -- outputs compared with the oracle
+    import os
+    import shutil
+    import subprocess
+
+    gxx, cuda = shutil.which("g++"), "/usr/local/cuda"
+    if gxx is None or not os.path.exists(os.path.join(cuda, "include", "cuda_runtime.h")):
+        pytest.skip("no g++ or no CUDA runtime headers")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib_dir = os.path.join(root, "candle_b200", "_lib")
+    exe = str(tmp_path / "host_mirror_gpu")
+    subprocess.run([gxx, "-std=c++17", "-I", os.path.join(root, "include"), "-I", os.path.join(cuda, "include"), "-o", exe,
+                    os.path.join(root, "tests", "cpp", "host_mirror_gpu.cpp"), "-L", lib_dir, "-l:libcandle_b200.so",
+                    f"-Wl,-rpath,{lib_dir}", "-L", os.path.join(cuda, "lib64"), "-lcudart"], check=True)
+    rng = np.random.default_rng(71)
+    rows, cols, vocab, n_ids = 300, 4096, 50, 64
+    x, r, a = randn(rng, (rows, cols), "bf16"), randn(rng, (rows, cols), "bf16"), randn(rng, (cols,), "bf16", 1.0, 0.1)
+    table = randn(rng, (vocab, cols), "f32", 0.0, 0.02)
+    ids = rng.integers(0, vocab, size=(n_ids,)).astype(np.uint32)
+    ids[37] = vocab + 5  # out of range: reported, its row left as it was (zeros)
+    for name, arr in (("x.bf16", x), ("res.bf16", r), ("alpha.bf16", a), ("table.f32", table), ("ids.u32", ids)):
+        arr.tofile(tmp_path / name)
+    out = subprocess.run([exe, str(tmp_path), str(rows), str(cols), str(vocab), str(n_ids)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert out.stdout.strip() == f"index-select invalid index {vocab + 5} with dim size {vocab}"
+    h = oracle.add(x, r, "bf16")
+    assert np.array_equal(np.fromfile(tmp_path / "h.bf16", np.uint16).reshape(rows, cols), h)
+    assert np.array_equal(np.fromfile(tmp_path / "y.bf16", np.uint16).reshape(rows, cols),
+                          oracle.rms_norm(h, a, 1e-5, "bf16"))
+    emb = np.fromfile(tmp_path / "emb.f32", np.float32).reshape(n_ids, cols)
+    good = np.arange(n_ids) != 37
+    assert np.array_equal(emb[good], table[ids[good]]) and not emb[37].any()
