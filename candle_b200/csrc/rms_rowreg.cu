@@ -199,7 +199,7 @@ struct QSlot {
   }
 };
 
-template <int QT, int DT, int HB>
+template <int QT, int DT, int HB, bool OWNER>
 __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, int stages) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       }
     }
     const int kind = slot.kinds[stage];
-    if (a.owned_only && kind == kRowMasked) {  // another rank owns this row and writes it
+    if (OWNER && kind == kRowMasked) {  // another rank owns this row and writes it
       if (tpr > 32)
         row_barrier(bar_id, tpr);
       else
@@ -334,12 +334,14 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       auto put = [&](int p, const uint4& lo, const uint4& hi) {
         stg_stream(yr + 2 * p, lo);
         stg_stream(yr + 2 * p + 1, hi);
+        if (OWNER) {
 #pragma unroll
-        for (int d = 0; d < 7; ++d) {
-          if (d < a.n_more) {
-            uint4* dst = a.y_more[d] + row * a.V + 2 * p;
-            stg_stream(dst, lo);
-            stg_stream(dst + 1, hi);
+          for (int d = 0; d < 7; ++d) {
+            if (d < a.n_more) {
+              uint4* dst = a.y_more[d] + row * a.V + 2 * p;
+              stg_stream(dst, lo);
+              stg_stream(dst + 1, hi);
+            }
           }
         }
       };
@@ -515,7 +517,8 @@ static cudaError_t launch_q_t(const QRmsArgs& a, int tpr, cudaStream_t stream) {
   while (stages < 4 && (QSlot::bytes(stages + 1, stage_bytes, tpr) * rpc + 1024) * ctas <= 196 * 1024) ++stages;
   const size_t smem = QSlot::bytes(stages, stage_bytes, tpr) * rpc;
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
-  auto kern = qrms_rowslot_kernel<QT, DT, HB>;
+  // the owner-writes-to-all mode is a variant of its own: the plain lookup carries none of its code
+  auto kern = a.owned_only ? qrms_rowslot_kernel<QT, DT, HB, true> : qrms_rowslot_kernel<QT, DT, HB, false>;
   unsigned grid = 1;
   cudaError_t e = persistent_grid(kern, 128, smem, ctas, (a.rows + rpc - 1) / rpc, grid);
   if (e != cudaSuccess) return e;
