@@ -173,6 +173,18 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
 // ---------------------------------------------------------------------------------------------
 constexpr int kRowDecode = 0, kRowMasked = 1, kRowBadId = 2;
 
+// decode_half_block out of line, for the rare re-decode after a replay: one copy of the code.
+struct HalfBlockVecs {
+  uint4 lo, hi;
+};
+template <int QT, int DT>
+__device__ __noinline__ HalfBlockVecs decode_half_block_cold(const unsigned char* row, int p) {
+  HalfBlockVecs r;
+  float d;
+  decode_half_block<QT, DT>(row, p, r.lo, r.hi, d);
+  return r;
+}
+
 template <int QT, int DT>
 struct QuantRow {
   const unsigned char* buf;
@@ -302,8 +314,9 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       m = replay_row<DT, QuantRow<QT, DT>>(QuantRow<QT, DT>{buf}, a.V, a.n, a.eps, sm);
 #pragma unroll
       for (int j = 0; j < HB; ++j) {  // nothing was kept in registers across the replay
-        float d;
-        decode_half_block<QT, DT>(buf, j * tpr + tx, h[2 * j], h[2 * j + 1], d);
+        const HalfBlockVecs hb = decode_half_block_cold<QT, DT>(buf, j * tpr + tx);
+        h[2 * j] = hb.lo;
+        h[2 * j + 1] = hb.hi;
       }
     }
     if (tpr == 32) __syncwarp();  // (wider slots passed named barriers inside decide_row)
@@ -345,19 +358,23 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
           }
         }
       };
-      if (row_dmin >= 9.0949470e-13f) {
+      // The common case -- every non-zero |h| is at least the smallest block scale >= 2^-40, so no
+      // quotient can fall under 2^-100, and m allows the reciprocal -- runs unrolled with nothing but
+      // the multiplications; anything else calls the guarded form out of line.
+      const bool plain = (DT != kDtBF16) || (fast_div && row_dmin >= 9.0949470e-13f);
+      if (plain) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_vec<DT, false>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
-              rms_output_vec<DT, false>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
+          put(p, rms_output_plain<DT>(h[2 * j], __ldg(a.alpha + 2 * p), m, r),
+              rms_output_plain<DT>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r));
         }
       } else {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_vec<DT, true>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
-              rms_output_vec<DT, true>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
+          put(p, rms_output_rare<DT>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
+              rms_output_rare<DT>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
         }
       }
     }

@@ -497,6 +497,30 @@ __device__ __forceinline__ uint4 rms_output_vec(const uint4& h, const uint4& alp
                     mul2_rn<DT>(pack2<DT>(q[4], q[5]), aw[2]), mul2_rn<DT>(pack2<DT>(q[6], q[7]), aw[3]));
 }
 
+// The common case of rms_output_vec only, for callers that have established it holds for the whole
+// row: bf16 with 2^-60 <= m <= 2^60 and no tiny non-zero element (quotient = product with r = 1/m),
+// or f16 (always the division).  Kept apart so that hot loops carry nothing else.
+template <int DT>
+__device__ __forceinline__ uint4 rms_output_plain(const uint4& h, const uint4& alpha, float m, float r) {
+  const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+  const uint32_t aw[4] = {alpha.x, alpha.y, alpha.z, alpha.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 hf = unpack2<DT>(hw[i]);
+    const uint32_t q = (DT == kDtBF16) ? pack2<DT>(__fmul_rn(hf.x, r), __fmul_rn(hf.y, r))
+                                       : pack2<DT>(__fdiv_rn(hf.x, m), __fdiv_rn(hf.y, m));
+    o[i] = mul2_rn<DT>(q, aw[i]);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// The guarded form out of line, for rare rows: one copy of the code however often it is called.
+template <int DT>
+__device__ __noinline__ uint4 rms_output_rare(uint4 h, uint4 alpha, float m, float r, bool fast_div) {
+  return rms_output_vec<DT, true>(h, alpha, m, r, fast_div);
+}
+
 // Same as rms_output_vec for a vector whose elements are already widened to f32 (hf).
 template <int DT, bool GUARD>
 __device__ __forceinline__ uint4 rms_output_floats(const float (&hf)[8], const uint4& alpha, float m, float r,
