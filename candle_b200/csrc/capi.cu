@@ -255,7 +255,8 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
   if (!all_aligned16(alpha, y, gathered) || (reinterpret_cast<uintptr_t>(qtable) & 1u))
     return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha, y and gathered must be 16-byte aligned, the table 2-byte aligned", name);
-  const bool fused = fusable_qtype(qtype) && out_dtype != CB200_DTYPE_F32 &&
+  // the single-launch kernel stages rows with bulk copies, which need a 16-byte aligned table
+  const bool fused = fusable_qtype(qtype) && out_dtype != CB200_DTYPE_F32 && aligned16(qtable) &&
                      cb200::qrms_rowreg_supported(out_dtype, hidden) &&
                      !(flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC));
   if (!fused) {
@@ -305,8 +306,8 @@ int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* i
                 (long long)vocab_end, (long long)vocab);
   if (n_ids == 0) return CB200_OK;
   if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
-  if (!aligned16(alpha) || (reinterpret_cast<uintptr_t>(qtable) & 1u))
-    return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha must be 16-byte aligned, the table 2-byte aligned", name);
+  if (!aligned16(alpha) || !aligned16(qtable))
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha and the table must be 16-byte aligned", name);
   for (int d = 0; d < n_dsts; ++d)
     if (dsts[d] == nullptr || !aligned16(dsts[d]))
       return fail(CB200_E_INVALID_ARGUMENT, "%s: destination %d is null or not 16-byte aligned", name, d);

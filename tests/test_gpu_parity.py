@@ -362,6 +362,24 @@ def test_qembedding_matches_oracle(cb, qtype, out_dtype):
         assert np.array_equal(bits(full), want_full.view(np.uint32) if out_dtype == "f32" else want_full)
     with pytest.raises(cb.InvalidIndex):
         q.embedding(torch.tensor([vocab], dtype=torch.int64, device="cuda"))
+    # a table that is only 2-byte aligned (a view 2 bytes into a buffer): no bulk copies, same values
+    if out_dtype != "f32":
+        from candle_b200 import _cabi
+        from candle_b200.ops import _stream, new_status
+        vocab, hidden = 64, 4096
+        qt = make_qtable(rng, qtype, vocab, hidden)
+        ids = rng.integers(0, vocab, size=(40,)).astype(np.uint32)
+        alpha = randn(rng, (hidden,), out_dtype, 1.0, 0.1)
+        want = oracle.rms_norm(oracle.qembedding(qt, qtype, ids, out_dtype), alpha, 1e-5, out_dtype)
+        store = torch.zeros(qt.size + 16, dtype=torch.uint8, device="cuda")
+        store[2:2 + qt.size] = torch.from_numpy(qt.reshape(-1)).cuda()
+        y = torch.empty(40, hidden, dtype=TORCH_DT[out_dtype], device="cuda")
+        st, tids, ta = new_status("cuda"), ids_tensor(ids), from_oracle(alpha, out_dtype)
+        _cabi.call("cb200_qembedding_rms_norm", store.data_ptr() + 2, oracle.QTYPES[qtype], tids.data_ptr(), ta.data_ptr(),
+                   y.data_ptr(), None, vocab, hidden, 40, 1e-5, {"f16": 1, "bf16": 2}[out_dtype], 1, 0, vocab, 0,
+                   st.data_ptr(), _stream(y))
+        torch.cuda.synchronize()
+        assert st[0].item() == 0 and np.array_equal(to_oracle(y), want)
 
 
 @pytest.mark.parametrize("qtype", ["q8_0", "q4_0", "q5_1"])
