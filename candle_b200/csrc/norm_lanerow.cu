@@ -257,13 +257,9 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
   const bool has_res = gr != nullptr;
   const int64_t n_tiles = (a.rows + tile_rows - 1) / tile_rows;
 
-  // gamma / beta of this lane's vectors, widened once
+  // gamma / beta of this lane's vectors, widened once (filled below, after the first copies are on
+  // their way)
   float gam[VPL][PV], bet[VPL][PV];
-#pragma unroll
-  for (int j = 0; j < VPL; ++j) {
-    vec_to_floats<DT>(__ldg(static_cast<const uint4*>(a.alpha) + lane + 32 * j), gam[j]);
-    if (OP == kOpLayerNorm) vec_to_floats<DT>(__ldg(static_cast<const uint4*>(a.beta) + lane + 32 * j), bet[j]);
-  }
 
   // Mover m owns rows m + 12 k of every tile, vectors lane + 32 j, for the copies, the in-place
   // conversion and the stores alike, so a thread converts only what it copied itself.
@@ -331,6 +327,11 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
   issue_rows(gx, smem_v, blockIdx.x);
   issue_rows(gr, rbuf, blockIdx.x);
   issue_rows(gx, smem_v + kBufVecs, blockIdx.x + stride);
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    vec_to_floats<DT>(__ldg(static_cast<const uint4*>(a.alpha) + lane + 32 * j), gam[j]);
+    if (OP == kOpLayerNorm) vec_to_floats<DT>(__ldg(static_cast<const uint4*>(a.beta) + lane + 32 * j), bet[j]);
+  }
 
   int slot = 0, it = 0;
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += stride, ++it) {
