@@ -661,23 +661,40 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
               s2 = (DT == kDtF32) ? __fadd_rn(s2, __fmul_rn(f[e], f[e])) : fmaf(f[e], f[e], s2);
             }
           };
-          const int full = cnt / G * G;
-          uint4 cur[G], nxt[G];
+          // Groups of G vectors, two per trip: while one register set is accumulated the other is
+          // being fetched, and the sets swap roles instead of being copied (the copies cost issue
+          // slots the chain needs).  A fetch past the chunk wraps to vector 0 and is not used.
+          const int groups = cnt / G;
+          auto load_group = [&](uint4 (&dst)[G], int g) {
+            const int v = g * G < kChunkVecs ? g * G : 0;
 #pragma unroll
-          for (int q = 0; q < G; ++q) cur[q] = fetch(q);
+            for (int q = 0; q < G; ++q) dst[q] = fetch(v + q);
+          };
+          uint4 ga[G], gb[G];
+          load_group(ga, 0);
+          int g = 0;
 #pragma unroll 1
-          for (int v = 0; v < full; v += G) {
-            const int vn = v + G < kChunkVecs ? v + G : 0;
+          for (; g + 1 < groups; g += 2) {
+            load_group(gb, g + 1);
 #pragma unroll
-            for (int q = 0; q < G; ++q) nxt[q] = fetch(vn + q);
+            for (int q = 0; q < G; ++q) add_vec(ga[q]);
+            load_group(ga, g + 2);
 #pragma unroll
-            for (int q = 0; q < G; ++q) add_vec(cur[q]);
-#pragma unroll
-            for (int q = 0; q < G; ++q) cur[q] = nxt[q];
+            for (int q = 0; q < G; ++q) add_vec(gb[q]);
           }
+          // ga holds group g here: the last whole group when their number is odd, else the ragged tail
+          if (g < groups) {
+            load_group(gb, g + 1);
 #pragma unroll
-          for (int q = 0; q < G; ++q)
-            if (full + q < cnt) add_vec(cur[q]);
+            for (int q = 0; q < G; ++q) add_vec(ga[q]);
+#pragma unroll
+            for (int q = 0; q < G; ++q)
+              if (groups * G + q < cnt) add_vec(gb[q]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < G; ++q)
+              if (groups * G + q < cnt) add_vec(ga[q]);
+          }
         }
         __syncwarp();
         ++g_c;
