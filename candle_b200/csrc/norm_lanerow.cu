@@ -378,29 +378,33 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
       if (lane < live) {
         const uint4* row = xb + lane * kPitchVecs;
         float s = 0.0f, s2 = 0.0f;
-        // four vectors are fetched while the previous four are accumulated, so the chains of
-        // dependent additions never wait for shared memory
-        uint4 cur[4], nxt[4];
+        // Four vectors are fetched while the previous four are accumulated, so the chains of
+        // dependent additions never wait for shared memory; the two register sets swap roles every
+        // half trip instead of being copied (V is a multiple of 32: an even number of groups).
+        auto add_vec = [&](const uint4& hv) {
+          float f[PV];
+          vec_to_floats<DT>(hv, f);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) cur[q] = row[q];
-#pragma unroll 1
-        for (int v = 0; v < V; v += 4) {
-          const int vn = v + 4 < V ? v + 4 : 0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) nxt[q] = row[vn + q];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float f[PV];
-            vec_to_floats<DT>(cur[q], f);
-#pragma unroll
-            for (int e = 0; e < PV; ++e) {
-              if (OP == kOpLayerNorm) s = __fadd_rn(s, f[e]);
-              // for 16-bit inputs f*f is exact in f32, so the fused form rounds like add(s2, mul(f, f))
-              s2 = (DT == kDtF32) ? __fadd_rn(s2, __fmul_rn(f[e], f[e])) : fmaf(f[e], f[e], s2);
-            }
+          for (int e = 0; e < PV; ++e) {
+            if (OP == kOpLayerNorm) s = __fadd_rn(s, f[e]);
+            // for 16-bit inputs f*f is exact in f32, so the fused form rounds like add(s2, mul(f, f))
+            s2 = (DT == kDtF32) ? __fadd_rn(s2, __fmul_rn(f[e], f[e])) : fmaf(f[e], f[e], s2);
           }
+        };
+        uint4 ga[4], gb[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) cur[q] = nxt[q];
+        for (int q = 0; q < 4; ++q) ga[q] = row[q];
+#pragma unroll 1
+        for (int v = 0; v < V; v += 8) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) gb[q] = row[v + 4 + q];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) add_vec(ga[q]);
+          const int vn = v + 8 < V ? v + 8 : 0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) ga[q] = row[vn + q];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) add_vec(gb[q]);
         }
         stats[(it & 1) * TR + lane] = make_float2(s, s2);
       }
