@@ -2,14 +2,20 @@
 //
 // candle's CPU path accumulates each row's sum (and sum of squares) strictly left to right in
 // f32 (candle-nn/src/ops.rs:484-490, 709-715).  For these ops nothing coarser than f32 absorbs
-// the rounding of that sum, so bit-equal results need the same order.  A CTA stages R whole rows
-// in shared memory (h = T(x + residual) when a residual is given, or rows gathered from a dense
-// table by the bulk-copy engine), then one LANE per row walks its row sequentially -- R
-// independent dependency chains advance per instruction, and several CTAs per SM overlap their
-// load / chain / store phases -- and finally all threads normalise and store the rows with
-// 16-byte coalesced accesses.  Each row is read from HBM once.
-// The row pitch in shared memory is an odd number of 16-byte units so the 16-byte loads of the
-// lane-per-row walk are bank-conflict free.
+// the rounding of that sum, so bit-equal results need the same order: one LANE per row walks its
+// row sequentially, 32 independent dependency chains per warp.  Three kernels share that walk and
+// differ in how rows reach it:
+//   norm_shortrow_kernel  rows of 512..2048 bytes, many of them: tiles of whole rows in a ring of
+//                         shared-memory buffers, copies two tiles ahead, the walk hidden behind
+//                         the previous tile's stores (each row read from HBM once);
+//   norm_stream_kernel    rows of 512 bytes and more otherwise (long rows, few rows, gathered
+//                         rows): rows streamed through a ring of 2 KB chunks, read a second time
+//                         (L2) for the normalise-and-store pass;
+//   norm_lanerow_kernel   rows under 512 bytes, and the cross-check of the two above: R whole rows
+//                         staged per CTA (h = T(x + residual), or rows gathered by the bulk-copy
+//                         engine), walk, then all threads normalise and store.
+// Row pitches in shared memory are an odd number of 16-byte units so that the 16-byte loads of the
+// lane-per-row walk are bank-conflict free.  norm_generic_kernel takes what is not 16-byte shaped.
 #include "launch.h"
 #include "rms_rowreg.cuh"
 
