@@ -201,6 +201,31 @@ int cb200_embedding_rms_norm(const void* table, const void* ids, const void* alp
   const bool vec_ok = all_aligned16(table, alpha, y, gathered) && (static_cast<int64_t>(hidden) * elem_bytes(dtype)) % 16 == 0;
   const bool force_lane = flags & CB200_FLAG_FORCE_LANEROW;
   const bool force_generic = flags & CB200_FLAG_FORCE_GENERIC;
+  if (vec_ok && !force_lane && !force_generic && dtype != CB200_DTYPE_F32 &&
+      cb200::qrms_rowreg_supported(dtype, hidden)) {
+    // 16-bit tables whose rows split over the row-slot kernel: rows staged by bulk copies, several
+    // rows ahead, instead of loaded into registers one row ahead (measured 0.59 -> 0.79 of the HBM
+    // peak at 4096 columns, 0.69 -> 0.73 at 8192)
+    cb200::QRmsArgs a{};
+    a.qtable = static_cast<const unsigned char*>(table);
+    a.ids = ids;
+    a.alpha = static_cast<const uint4*>(alpha);
+    a.y = static_cast<uint4*>(y);
+    a.gathered = static_cast<uint4*>(gathered);
+    a.id_dtype = id_dtype;
+    a.vocab = vocab;
+    a.vocab_begin = 0;
+    a.vocab_end = vocab;
+    a.status = status;
+    a.rows = n_ids;
+    a.V = hidden / 8;
+    a.n = hidden;
+    a.row_bytes = hidden * 2;
+    a.bulk = 1;
+    a.eps = eps;
+    a.flags = flags;
+    return cuda_result(cb200::launch_qrms_rowreg(cb200::kQTypeDense16, dtype, a, stream), name);
+  }
   if (vec_ok && !force_lane && !force_generic && cb200::rms_rowreg_supported(dtype, hidden)) {
     cb200::RmsRowRegArgs a{};
     a.x = static_cast<const uint4*>(table);

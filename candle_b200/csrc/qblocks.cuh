@@ -46,6 +46,15 @@ struct QBlock<CB200_QTYPE_Q5_1> {
   static constexpr int kBytes = 24;
 };
 
+// Internal pseudo-format: rows that already hold 16-bit elements of the output type (a dense f16 /
+// bf16 table).  It lets the row-slot kernel, with its ring of bulk-copied rows, serve dense tables:
+// a "block" is 32 elements = 64 bytes and decoding is a plain 16-byte load.  Never part of the ABI.
+constexpr int kQTypeDense16 = 1000;
+template <>
+struct QBlock<kQTypeDense16> {
+  static constexpr int kBytes = 64;
+};
+
 __host__ __device__ inline int qblock_bytes(int qtype) {
   switch (qtype) {
     case CB200_QTYPE_Q4_0:
@@ -127,9 +136,14 @@ __device__ __forceinline__ void decode8(const unsigned char* row, int v, float (
 // Same, rounded to a 16-bit type and packed into one 16-byte vector.
 template <int QT, int DT>
 __device__ __forceinline__ uint4 decode_vec8(const unsigned char* row, int v, float* scale = nullptr) {
-  float f[8];
-  decode8<QT>(row, v, f, scale);
-  return make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
+  if constexpr (QT == kQTypeDense16) {
+    if (scale != nullptr) *scale = 1.0f;
+    return reinterpret_cast<const uint4*>(row)[v];
+  } else {
+    float f[8];
+    decode8<QT>(row, v, f, scale);
+    return make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
+  }
 }
 
 // Decodes the sixteen elements [16p, 16p+16) (half a block) of a row of blocks: two vectors that
@@ -137,34 +151,41 @@ __device__ __forceinline__ uint4 decode_vec8(const unsigned char* row, int v, fl
 // nibbles of all sixteen bytes.
 template <int QT, int DT>
 __device__ __forceinline__ void decode_half_block(const unsigned char* row, int p, uint4& lo8, uint4& hi8, float& scale) {
-  const unsigned char* b = row + (p >> 1) * QBlock<QT>::kBytes;
-  const float d = __half2float(*reinterpret_cast<const __half*>(b));
-  scale = d;
-  const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + (QT == CB200_QTYPE_Q8_0 ? (p & 1) * 16 : 0));
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) w[i] = static_cast<uint32_t>(q[2 * i]) | (static_cast<uint32_t>(q[2 * i + 1]) << 16);
-  float bias;
-  if (QT == CB200_QTYPE_Q8_0) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] ^= 0x80808080u;
-    bias = 8388608.0f + 128.0f;
+  if constexpr (QT == kQTypeDense16) {
+    lo8 = reinterpret_cast<const uint4*>(row)[2 * p];
+    hi8 = reinterpret_cast<const uint4*>(row)[2 * p + 1];
+    scale = 1.0f;
+    return;
   } else {
-    const int shift = (p & 1) * 4;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] = (w[i] >> shift) & 0x0F0F0F0Fu;
-    bias = 8388608.0f + 8.0f;
+    const unsigned char* b = row + (p >> 1) * QBlock<QT>::kBytes;
+    const float d = __half2float(*reinterpret_cast<const __half*>(b));
+    scale = d;
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + (QT == CB200_QTYPE_Q8_0 ? (p & 1) * 16 : 0));
+    uint32_t w[4];
+  #pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = static_cast<uint32_t>(q[2 * i]) | (static_cast<uint32_t>(q[2 * i + 1]) << 16);
+    float bias;
+    if (QT == CB200_QTYPE_Q8_0) {
+  #pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] ^= 0x80808080u;
+      bias = 8388608.0f + 128.0f;
+    } else {
+      const int shift = (p & 1) * 4;
+  #pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = (w[i] >> shift) & 0x0F0F0F0Fu;
+      bias = 8388608.0f + 8.0f;
+    }
+    float f[16];
+  #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[4 * i] = __fmul_rn(byte_to_float<0>(w[i], bias), d);
+      f[4 * i + 1] = __fmul_rn(byte_to_float<1>(w[i], bias), d);
+      f[4 * i + 2] = __fmul_rn(byte_to_float<2>(w[i], bias), d);
+      f[4 * i + 3] = __fmul_rn(byte_to_float<3>(w[i], bias), d);
+    }
+    lo8 = make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
+    hi8 = make_uint4(pack2<DT>(f[8], f[9]), pack2<DT>(f[10], f[11]), pack2<DT>(f[12], f[13]), pack2<DT>(f[14], f[15]));
   }
-  float f[16];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[4 * i] = __fmul_rn(byte_to_float<0>(w[i], bias), d);
-    f[4 * i + 1] = __fmul_rn(byte_to_float<1>(w[i], bias), d);
-    f[4 * i + 2] = __fmul_rn(byte_to_float<2>(w[i], bias), d);
-    f[4 * i + 3] = __fmul_rn(byte_to_float<3>(w[i], bias), d);
-  }
-  lo8 = make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
-  hi8 = make_uint4(pack2<DT>(f[8], f[9]), pack2<DT>(f[10], f[11]), pack2<DT>(f[12], f[13]), pack2<DT>(f[14], f[15]));
 }
 
 }  // namespace cb200

@@ -361,8 +361,17 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       // The common case -- every non-zero |h| is at least the smallest block scale >= 2^-40, so no
       // quotient can fall under 2^-100, and m allows the reciprocal -- runs unrolled with nothing but
       // the multiplications; anything else calls the guarded form out of line.
-      const bool plain = (DT != kDtBF16) || (fast_div && row_dmin >= 9.0949470e-13f);
-      if (plain) {
+      // (rows of a dense table carry no scales to bound their elements by: bf16 keeps the guard)
+      const bool plain =
+          (DT != kDtBF16) || (QT != kQTypeDense16 && fast_div && row_dmin >= 9.0949470e-13f);
+      if (QT == kQTypeDense16 && !plain) {
+#pragma unroll
+        for (int j = 0; j < HB; ++j) {
+          const int p = j * tpr + tx;
+          put(p, rms_output_vec<DT, true>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
+              rms_output_vec<DT, true>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
+        }
+      } else if (plain) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
@@ -535,7 +544,10 @@ static cudaError_t launch_q_t(const QRmsArgs& a, int tpr, cudaStream_t stream) {
   const size_t smem = QSlot::bytes(stages, stage_bytes, tpr) * rpc;
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   // the owner-writes-to-all mode is a variant of its own: the plain lookup carries none of its code
-  auto kern = a.owned_only ? qrms_rowslot_kernel<QT, DT, HB, true> : qrms_rowslot_kernel<QT, DT, HB, false>;
+  auto kern = qrms_rowslot_kernel<QT, DT, HB, false>;
+  if constexpr (QT != kQTypeDense16) {
+    if (a.owned_only) kern = qrms_rowslot_kernel<QT, DT, HB, true>;
+  }
   unsigned grid = 1;
   cudaError_t e = persistent_grid(kern, 128, smem, ctas, (a.rows + rpc - 1) / rpc, grid);
   if (e != cudaSuccess) return e;
@@ -561,6 +573,9 @@ static cudaError_t launch_q_dt(const QRmsArgs& a, cudaStream_t stream) {
 
 cudaError_t launch_qrms_rowreg(int qtype, int dtype, const QRmsArgs& a, cudaStream_t stream) {
   if (a.rows == 0) return cudaSuccess;
+  if (qtype == kQTypeDense16)
+    return dtype == kDtBF16 ? launch_q_dt<kQTypeDense16, kDtBF16>(a, stream)
+                            : launch_q_dt<kQTypeDense16, kDtF16>(a, stream);
   if (qtype == CB200_QTYPE_Q8_0)
     return dtype == kDtBF16 ? launch_q_dt<CB200_QTYPE_Q8_0, kDtBF16>(a, stream)
                             : launch_q_dt<CB200_QTYPE_Q8_0, kDtF16>(a, stream);
