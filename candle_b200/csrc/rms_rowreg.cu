@@ -224,6 +224,10 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
   const int64_t step = static_cast<int64_t>(gridDim.x) * rpc;
   uint64_t id_ahead = 0;  // issuing lane: id of the next row to be issued, already loaded
 
+  // without an id list the rows are taken in order (a dense source)
+  auto row_id = [&](int64_t r) -> uint64_t {
+    return a.ids != nullptr ? read_id(a.ids, a.id_dtype, r) : static_cast<uint64_t>(r);
+  };
   // issuing lane: classify row (whose id is `id`), publish its kind, start its copy into `stage`
   auto issue = [&](int64_t row, uint64_t id, int stage) {
     int kind = kRowDecode;
@@ -247,10 +251,10 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
     *slot.abort_flag = 0;
     for (int j = 0; j < stages - 1; ++j) {
       const int64_t r = first + j * step;
-      if (r < a.rows) issue(r, read_id(a.ids, a.id_dtype, r), j);
+      if (r < a.rows) issue(r, row_id(r), j);
     }
     const int64_t r = first + static_cast<int64_t>(stages - 1) * step;
-    if (r < a.rows) id_ahead = read_id(a.ids, a.id_dtype, r);
+    if (r < a.rows) id_ahead = row_id(r);
   }
   if (tpr > 32)
     row_barrier(bar_id, tpr);
@@ -268,7 +272,7 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       const int64_t ahead = row + static_cast<int64_t>(stages - 1) * step;
       if (ahead < a.rows) {
         issue(ahead, id_ahead, stage == 0 ? stages - 1 : stage - 1);
-        if (ahead + step < a.rows) id_ahead = read_id(a.ids, a.id_dtype, ahead + step);
+        if (ahead + step < a.rows) id_ahead = row_id(ahead + step);
       }
     }
     const int kind = slot.kinds[stage];

@@ -279,6 +279,25 @@ def test_rms_norm_many_narrow_rows_with_residual_take_the_look_ahead_variant(cb,
     assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
 
 
+def test_rms_norm_many_narrow_rows_without_residual_take_the_row_slot_kernel(cb):
+    # >= 32768 rows of at most 4096 columns, no residual: rows are staged by bulk copies in the
+    # row-slot kernel (ids implied).  Checked against the oracle, the forced replay, and in place.
+    rng = np.random.default_rng(93)
+    rows, cols = 32768 + 5, 1024
+    x, a = randn(rng, (rows, cols), "bf16"), randn(rng, (cols,), "bf16", 1.0, 0.1)
+    want = oracle.rms_norm(x, a, 1e-5, "bf16", threads=0)
+    xt, at = from_oracle(x, "bf16"), from_oracle(a, "bf16")
+    y = cb.rms_norm(xt, at, 1e-5)
+    assert_norm_equal(y, want, "bf16")
+    y2 = cb.rms_norm(xt, at, 1e-5, flags=cb.FLAG_FORCE_REPLAY)
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+    y3 = cb.rms_norm(xt, at, 1e-5, flags=cb.FLAG_FORCE_LANEROW)
+    assert torch.equal(y.view(torch.int16), y3.view(torch.int16))
+    xc = xt.clone()
+    cb.rms_norm(xc, at, 1e-5, out=xc)
+    assert torch.equal(xc.view(torch.int16), y.view(torch.int16))
+
+
 def test_norm_special_values_and_aliasing(cb):
     for dtype in ("f32", "bf16", "f16"):
         x = np.zeros((4, 256), np.float32)
