@@ -16,15 +16,17 @@ from .ops import (
     embedding_rms_norm,
     index_select,
     layer_norm,
+    layer_norm_slow,
     qembedding_rms_norm,
     rms_norm,
+    rms_norm_slow,
 )
 from .host_pipeline import PinnedNormPipeline
 from .nn import Embedding, LayerNorm, QEmbedding, RmsNorm
 from .quantized import GgmlDType, QTensor
 
 __all__ = [
-    "CandleError", "InvalidIndex", "rms_norm", "layer_norm", "index_select", "embedding_rms_norm",
+    "CandleError", "InvalidIndex", "rms_norm", "layer_norm", "rms_norm_slow", "layer_norm_slow", "index_select", "embedding_rms_norm",
     "qembedding_rms_norm", "PinnedNormPipeline", "Embedding", "LayerNorm", "RmsNorm", "QEmbedding", "QTensor", "GgmlDType",
     "FLAG_FAST_SUM", "FLAG_FORCE_LANEROW", "FLAG_FORCE_GENERIC", "FLAG_FORCE_REPLAY",
 ]

@@ -16,6 +16,10 @@ SIGNATURES = {
     "cb200_last_error": [],
     "cb200_rms_norm": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp],
     "cb200_layer_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp],
+    "cb200_rms_norm_checked": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp, _vp],
+    "cb200_layer_norm_checked": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp, _vp],
+    "cb200_layer_norm_slow": [_vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp],
+    "cb200_selftest_wait_expiry": [_int],
     "cb200_index_select": [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _int, _vp, _vp],
     "cb200_embedding": [_vp, _vp, _vp, _i64, _i32, _i64, _int, _int, _vp, _vp],
     "cb200_dequantize": [_vp, _int, _vp, _i64, _int, _vp],

@@ -11,7 +11,7 @@ LIB_DIR = os.path.join(_HERE, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libcandle_b200.so")
 NCCL_LIB_PATH = os.path.join(LIB_DIR, "libcandle_b200_nccl.so")
 
-CORE_SOURCES = ["capi.cu", "rms_rowreg.cu", "norm_lanerow.cu", "embedding.cu"]
+CORE_SOURCES = ["capi.cu", "launch_cache.cu", "rms_rowreg.cu", "norm_lanerow.cu", "norm_slow.cu", "embedding.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--use_fast_math=false",
@@ -35,15 +35,33 @@ def _stale(target: str, sources: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _source_stale(obj: str, src: str) -> bool:
+    return _stale(obj, [src])
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(LIB_DIR, exist_ok=True)
+    """Compiles every source into its own object (in parallel, only the stale ones) and links."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    obj_dir = os.path.join(LIB_DIR, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
     srcs = [os.path.join(CSRC, s) for s in CORE_SOURCES]
-    if force or _stale(LIB_PATH, srcs):
-        flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
-        cmd = [_nvcc(), *flags, "-ccbin", "/usr/bin/g++", "-shared", "-o", LIB_PATH, *srcs]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-        subprocess.run(cmd, check=True)
+    objs = [os.path.join(obj_dir, os.path.splitext(s)[0] + ".o") for s in CORE_SOURCES]
+    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    if verbose:
+        flags = ["-Xptxas=-v", *flags]
+
+    def compile_one(pair):
+        src, obj = pair
+        if force or _source_stale(obj, src):
+            subprocess.run([_nvcc(), *flags, "-ccbin", "/usr/bin/g++", "-c", "-o", obj, src], check=True)
+            return True
+        return False
+
+    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
+        rebuilt = list(pool.map(compile_one, zip(srcs, objs)))
+    if any(rebuilt) or not os.path.exists(LIB_PATH):
+        subprocess.run([_nvcc(), *flags, "-ccbin", "/usr/bin/g++", "-shared", "-o", LIB_PATH, *objs], check=True)
     return LIB_PATH
 
 

@@ -40,7 +40,8 @@ bool all_aligned16(P... ptrs) {
 }
 
 int norm_impl(int op, const void* x, const void* residual, const void* alpha, const void* beta, void* y,
-              void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags, cudaStream_t stream) {
+              void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags, cb200_status* status,
+              cudaStream_t stream) {
   const char* name = op == cb200::kOpLayerNorm ? "cb200_layer_norm" : "cb200_rms_norm";
   if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
   if (rows < 0 || cols < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape [%lld, %d]", name, (long long)rows, cols);
@@ -68,6 +69,7 @@ int norm_impl(int op, const void* x, const void* residual, const void* alpha, co
     a.gathered = static_cast<uint4*>(sum_out);
     a.vocab = rows;
     a.vocab_end = rows;
+    a.status = status;
     a.rows = rows;
     a.V = cols / 8;
     a.n = cols;
@@ -84,6 +86,7 @@ int norm_impl(int op, const void* x, const void* residual, const void* alpha, co
     a.alpha = static_cast<const uint4*>(alpha);
     a.y = static_cast<uint4*>(y);
     a.sum_out = static_cast<uint4*>(sum_out);
+    a.status = status;
     a.rows = rows;
     a.V = cols / 8;
     a.n = cols;
@@ -93,6 +96,7 @@ int norm_impl(int op, const void* x, const void* residual, const void* alpha, co
   }
   cb200::LaneRowArgs a{};
   a.x = x;
+  a.status = status;
   a.res = residual;
   a.alpha = alpha;
   a.beta = beta;
@@ -126,13 +130,47 @@ const char* cb200_last_error(void) { return g_last_error; }
 
 int cb200_rms_norm(const void* x, const void* residual, const void* alpha, void* y, void* sum_out, int64_t rows,
                    int32_t cols, float eps, int dtype, int flags, cb200_stream_t stream) {
-  return norm_impl(cb200::kOpRmsNorm, x, residual, alpha, nullptr, y, sum_out, rows, cols, eps, dtype, flags, stream);
+  return norm_impl(cb200::kOpRmsNorm, x, residual, alpha, nullptr, y, sum_out, rows, cols, eps, dtype, flags, nullptr,
+                   stream);
+}
+
+int cb200_rms_norm_checked(const void* x, const void* residual, const void* alpha, void* y, void* sum_out,
+                           int64_t rows, int32_t cols, float eps, int dtype, int flags, cb200_status* status,
+                           cb200_stream_t stream) {
+  return norm_impl(cb200::kOpRmsNorm, x, residual, alpha, nullptr, y, sum_out, rows, cols, eps, dtype, flags, status,
+                   stream);
 }
 
 int cb200_layer_norm(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
                      void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags,
                      cb200_stream_t stream) {
-  return norm_impl(cb200::kOpLayerNorm, x, residual, gamma, beta, y, sum_out, rows, cols, eps, dtype, flags, stream);
+  return norm_impl(cb200::kOpLayerNorm, x, residual, gamma, beta, y, sum_out, rows, cols, eps, dtype, flags, nullptr,
+                   stream);
+}
+
+int cb200_layer_norm_checked(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
+                             void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags,
+                             cb200_status* status, cb200_stream_t stream) {
+  return norm_impl(cb200::kOpLayerNorm, x, residual, gamma, beta, y, sum_out, rows, cols, eps, dtype, flags, status,
+                   stream);
+}
+
+int cb200_layer_norm_slow(const void* x, const void* weight, const void* bias, void* y, int64_t rows, int32_t cols,
+                          float eps, int dtype, int remove_mean, cb200_stream_t stream) {
+  const char* name = "cb200_layer_norm_slow";
+  if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
+  if (rows < 0 || cols < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape [%lld, %d]", name, (long long)rows, cols);
+  if (rows == 0) return CB200_OK;
+  if (cols == 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: rows of zero columns cannot be normalised", name);
+  if (x == nullptr || weight == nullptr || y == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  if (rows > (int64_t(1) << 40)) return fail(CB200_E_INVALID_ARGUMENT, "%s: too many rows", name);
+  return cuda_result(cb200::launch_norm_slow(dtype, x, weight, bias, y, rows, cols, eps, remove_mean != 0, stream), name);
+}
+
+int cb200_selftest_wait_expiry(int enable) {
+  // 64 polls and 16 bytes that never arrive: every bounded wait of the bulk-copy kernels runs out
+  cb200::set_wait_tuning(enable ? cb200::WaitTuning{64u, 16u} : cb200::WaitTuning{cb200::kWaitSpins, 0u});
+  return CB200_OK;
 }
 
 int cb200_index_select(const void* src, const void* ids, void* out, int64_t left, int64_t src_dim, int64_t right,

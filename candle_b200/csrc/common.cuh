@@ -15,8 +15,6 @@ constexpr int kDtF32 = CB200_DTYPE_F32;
 constexpr int kDtF16 = CB200_DTYPE_F16;
 constexpr int kDtBF16 = CB200_DTYPE_BF16;
 
-constexpr int kSmCount = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
-
 // ---------------------------------------------------------------------------------------------
 // Element traits.  Every conversion is IEEE round-to-nearest-even, which is what crate `half`
 // does on candle's CPU path; products and sums that candle rounds separately are written with
@@ -165,10 +163,20 @@ __device__ __forceinline__ uint64_t read_id(const void* ids, int id_dtype, int64
 
 // ---------------------------------------------------------------------------------------------
 // mbarrier + bulk async copy (the TMA engine's untiled form).  Addresses and sizes must be
-// multiples of 16 bytes.  Every wait is bounded: after kWaitSpins polls it gives up and the
-// caller reports CB200_STATUS_WAIT_TIMEOUT instead of spinning forever.
+// multiples of 16 bytes.  Every wait is bounded: after `spins` polls (kWaitSpins unless the host's
+// self-test hook lowered it) it gives up and the caller reports CB200_STATUS_WAIT_TIMEOUT instead
+// of spinning forever.
 // ---------------------------------------------------------------------------------------------
 constexpr uint32_t kWaitSpins = 1u << 22;
+
+// How the kernels wait, as the launchers pass it to them.  Normally {kWaitSpins, 0}.  The library's
+// self-test hook (cb200_selftest_wait_expiry) sets a small poll budget and makes every mbarrier
+// expect `extra_tx` more bytes than its copies deliver, so that the waits run out and the give-up
+// paths execute -- without any copy actually failing.
+struct WaitTuning {
+  uint32_t spins;
+  uint32_t extra_tx;
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -194,20 +202,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-#ifdef CB200_PROBE_SPINS
-__device__ unsigned long long g_probe_spins = 0;  // test-bench instrumentation only
-#endif
 // Returns false if the phase did not complete within the spin budget.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitSpins; ++i) {
-    if (mbar_try_wait(bar, parity)) {
-#ifdef CB200_PROBE_SPINS
-      if (i > 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_probe_spins, static_cast<unsigned long long>(i));
-#endif
-      return true;
-    }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t spins = kWaitSpins) {
+  for (uint32_t i = 0; i < spins; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
   }
   return false;
+}
+// A CTA that gives up on a wait must not retire while bulk copies may still be writing its shared
+// memory.  After the bounded second-chance waits it also pauses for about 0.1 ms (bounded), far longer
+// than any copy that was issued takes to land.
+__device__ __forceinline__ void drain_pause() {
+  for (int i = 0; i < 64; ++i) __nanosleep(2000);
 }
 // global -> shared, completion counted in bytes on `bar`.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(32) gather_rows_bulk_kernel(const GatherArgs a
     const unsigned char* src = a.src + (l * a.src_dim + static_cast<int64_t>(id)) * a.row_bytes + off;
     size[s] = bytes;
     dst[s] = a.out + row * a.row_bytes + off;
-    mbar_expect_tx(&bars[s], bytes);
+    mbar_expect_tx(&bars[s], bytes + a.wt.extra_tx);
     bulk_g2s(ring + static_cast<size_t>(s) * kGatherChunk, src, bytes, &bars[s]);
     pending |= 1u << s;
   };
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(32) gather_rows_bulk_kernel(const GatherArgs a
   for (int64_t j = 0; j < n_my; ++j) {
     const int s = static_cast<int>(j % kGatherStages);
     if (size[s] != 0) {
-      if (!mbar_wait(&bars[s], (phase >> s) & 1u)) {
+      if (!mbar_wait(&bars[s], (phase >> s) & 1u, a.wt.spins)) {
         report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, first + j * step, 0, a.src_dim);
         timed_out = true;
         break;
@@ -84,7 +84,8 @@ __global__ void __launch_bounds__(32) gather_rows_bulk_kernel(const GatherArgs a
   if (timed_out) {
     // bounded second chance for loads still in flight, so none lands after the CTA retires
     for (int s = 0; s < kGatherStages; ++s)
-      if (pending & (1u << s)) mbar_wait(&bars[s], (phase >> s) & 1u);
+      if (pending & (1u << s)) mbar_wait(&bars[s], (phase >> s) & 1u, a.wt.spins);
+    drain_pause();
   }
 }
 
@@ -119,23 +120,24 @@ static int64_t common_alignment(const GatherArgs& a) {
   return 1;
 }
 
-cudaError_t launch_gather_rows(const GatherArgs& a, cudaStream_t stream) {
+cudaError_t launch_gather_rows(const GatherArgs& a_in, cudaStream_t stream) {
+  GatherArgs a = a_in;
+  a.wt = wait_tuning();
   const int64_t rows = a.left * a.n_ids;
   if (rows == 0 || a.row_bytes == 0) return cudaSuccess;
   const int64_t align = common_alignment(a);
   if (align == 16 && a.row_bytes >= 1024) {
     const int64_t chunks = (a.row_bytes + kGatherChunk - 1) / kGatherChunk;
     const size_t smem = 128 + static_cast<size_t>(kGatherStages) * kGatherChunk;
-    cudaError_t e = cudaFuncSetAttribute(gather_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+    cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(gather_rows_bulk_kernel), 32, smem, -1, nullptr);
     if (e != cudaSuccess) return e;
-    int64_t grid = static_cast<int64_t>(kSmCount) * 3;  // 3 x 64 KB rings per SM
+    int64_t grid = static_cast<int64_t>(sm_count()) * 3;  // 3 x 64 KB rings per SM
     if (grid > rows * chunks) grid = rows * chunks;
     gather_rows_bulk_kernel<<<static_cast<unsigned>(grid), 32, smem, stream>>>(a, static_cast<int>(chunks));
     return cudaGetLastError();
   }
   int64_t warps = rows;
-  const int64_t max_warps = static_cast<int64_t>(kSmCount) * 8 * 8;
+  const int64_t max_warps = static_cast<int64_t>(sm_count()) * 8 * 8;
   if (warps > max_warps) warps = max_warps;
   const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
   switch (align) {
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
     uint64_t id;
     if (classify(row, id) != 0) return;
     const unsigned char* src = a.qtable + (id - a.vocab_begin) * static_cast<uint64_t>(a.row_bytes);
-    mbar_expect_tx(&bars[stage], static_cast<uint32_t>(a.row_bytes));
+    mbar_expect_tx(&bars[stage], static_cast<uint32_t>(a.row_bytes) + a.wt.extra_tx);
     bulk_g2s(smem_raw + stage * stage_bytes, src, static_cast<uint32_t>(a.row_bytes), &bars[stage]);
   };
 
@@ -219,18 +221,19 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
     if (a.bulk && tx == 0 && has_next) issue(row + step, (it + 1) % kQGatherStages);
     if (kind == 0) {
       if (a.bulk) {
-        const bool ok = mbar_wait(&bars[stage], (phase >> stage) & 1u);
+        const bool ok = mbar_wait(&bars[stage], (phase >> stage) & 1u, a.wt.spins);
         phase ^= 1u << stage;
         if (!__syncthreads_and(ok ? 1 : 0)) {
           if (tx == 0) {
             report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row, static_cast<int64_t>(id), a.vocab);
             // bounded second chance for this row's copy and for the prefetch of the next one
-            mbar_wait(&bars[stage], ((phase >> stage) & 1u) ^ 1u);
+            mbar_wait(&bars[stage], ((phase >> stage) & 1u) ^ 1u, a.wt.spins);
             uint64_t nid;
             if (has_next && classify(row + step, nid) == 0) {
               const int ns = (it + 1) % kQGatherStages;
-              mbar_wait(&bars[ns], (phase >> ns) & 1u);
+              mbar_wait(&bars[ns], (phase >> ns) & 1u, a.wt.spins);
             }
+            drain_pause();
           }
           return;
         }
@@ -261,15 +264,15 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
 }
 
 template <int QT, int DT>
-static cudaError_t launch_qgather_t(const QGatherArgs& a, cudaStream_t stream) {
+static cudaError_t launch_qgather_t(const QGatherArgs& a_in, cudaStream_t stream) {
+  QGatherArgs a = a_in;
+  a.wt = wait_tuning();
   const int stage_bytes = (a.row_bytes + 15) & ~15;
   const size_t smem = static_cast<size_t>(kQGatherStages) * stage_bytes + kQGatherStages * 8;
   auto kern = qgather_kernel<QT, DT>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-  }
-  int64_t grid = static_cast<int64_t>(kSmCount) * 8;
+  cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), kQGatherThreads, smem, -1, nullptr);
+  if (e != cudaSuccess) return e;
+  int64_t grid = static_cast<int64_t>(sm_count()) * 8;
   if (grid > a.rows) grid = a.rows;
   kern<<<static_cast<unsigned>(grid), kQGatherThreads, smem, stream>>>(a);
   return cudaGetLastError();
@@ -324,7 +327,7 @@ cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks,
   const int64_t n_vec = n_blocks * 4;
   if (n_vec == 0) return cudaSuccess;
   int64_t grid = (n_vec + 255) / 256;
-  const int64_t cap = static_cast<int64_t>(kSmCount) * 32;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
   if (grid > cap) grid = cap;
   const unsigned char* b = static_cast<const unsigned char*>(blocks);
 #define CB200_DQ(QT)                                                                            \

@@ -5,6 +5,26 @@
 
 namespace cb200 {
 
+// launch_cache.cu: per-device values and per-kernel attributes, set up once and cached.
+// device_sm_count: SMs of the current device.  kernel_launch_config: raises `func`'s dynamic
+// shared-memory limit to the architectural maximum (once), applies the shared-memory carve-out
+// preference when it changes (pass -1 to leave it alone) and returns how many CTAs of `threads`
+// threads and `smem` dynamic bytes fit on an SM (pass NULL to skip the query).
+cudaError_t device_sm_count(int* out);
+cudaError_t kernel_launch_config(const void* func, int threads, size_t smem, int carveout_percent,
+                                 int* ctas_per_sm);
+
+// The wait parameters every launcher copies into its kernel's arguments (launch_cache.cu).
+WaitTuning wait_tuning();
+void set_wait_tuning(WaitTuning t);
+
+// SMs of the current device for grid sizing; if the query fails the launch that follows reports
+// the error, and 148 (B200) stands in meanwhile.
+inline int sm_count() {
+  int n = 148;
+  return device_sm_count(&n) == cudaSuccess ? n : 148;
+}
+
 constexpr int kOpRmsNorm = 0;
 constexpr int kOpLayerNorm = 1;
 
@@ -28,6 +48,7 @@ struct LaneRowArgs {
   int pitch;  // filled by the launcher: shared-memory row pitch in bytes
   int R;      // filled by the launcher: rows per CTA
   int classic;  // keep to the whole-row kernel where the streaming one would apply (cross-checks)
+  WaitTuning wt;  // filled by the launcher
 };
 
 struct RmsRowRegArgs;
@@ -42,6 +63,10 @@ bool norm_lanerow_supported(int dtype, int cols);
 cudaError_t launch_norm_lanerow(int dtype, int op, const LaneRowArgs& a, cudaStream_t stream);
 cudaError_t launch_norm_generic(int dtype, int op, const LaneRowArgs& a, cudaStream_t stream);
 
+// candle's composite norm (norm_slow.cu); bias may be NULL
+cudaError_t launch_norm_slow(int dtype, const void* x, const void* weight, const void* bias, void* y, int64_t rows,
+                             int n, float eps, int remove_mean, cudaStream_t stream);
+
 // Row gathers (embedding.cu)
 struct GatherArgs {
   const unsigned char* src;  // [left, src_dim, row_bytes]
@@ -51,6 +76,7 @@ struct GatherArgs {
   int64_t row_bytes;
   int id_dtype;
   cb200_status* status;
+  WaitTuning wt;  // filled by the launcher
 };
 cudaError_t launch_gather_rows(const GatherArgs& a, cudaStream_t stream);
 
@@ -65,6 +91,7 @@ struct QGatherArgs {
   int n;          // elements per row (multiple of 32)
   int row_bytes;  // bytes per quantised row
   int bulk;
+  WaitTuning wt;  // filled by the launcher
 };
 cudaError_t launch_qgather(int qtype, int out_dtype, const QGatherArgs& a, cudaStream_t stream);
 cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks, void* out, int64_t n_blocks,

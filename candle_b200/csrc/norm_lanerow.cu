@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const Lan
           else
             report_status(a.status, CB200_STATUS_INVALID_INDEX, row0 + r, static_cast<int64_t>(id), a.vocab);
         }
-        mbar_expect_tx(bar, bytes);
+        mbar_expect_tx(bar, bytes + a.wt.extra_tx);
         for (int r = 0; r < live; ++r) {
           if (!valid[r]) continue;
           uint64_t id = read_id(a.ids, a.id_dtype, row0 + r);
@@ -89,11 +89,12 @@ __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const Lan
         }
       }
       __syncthreads();
-      const bool ok = mbar_wait(bar, 0);
+      const bool ok = mbar_wait(bar, 0, a.wt.spins);
       if (!__syncthreads_and(ok ? 1 : 0)) {
         // give the copies in flight one more bounded chance to land before the CTA retires
         if (tid == 0) {
-          mbar_wait(bar, 0);
+          mbar_wait(bar, 0, a.wt.spins);
+          drain_pause();
           report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row0, 0, a.vocab);
         }
         return;
@@ -607,7 +608,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
     const int stage = static_cast<int>(g_i % static_cast<uint32_t>(D));
     const int vecs = min(kChunkVecs, V - kChunkVecs * chunk_i);
     const uint32_t bytes = static_cast<uint32_t>(vecs) * 16u;
-    if (lane == 0) mbar_expect_tx(&sm.bars[stage], static_cast<uint32_t>(nlive_i) * bytes * (RES ? 2u : 1u));
+    if (lane == 0) mbar_expect_tx(&sm.bars[stage], static_cast<uint32_t>(nlive_i) * bytes * (RES ? 2u : 1u) + a.wt.extra_tx);
     if (live_i) {
       const size_t slot = (static_cast<size_t>(stage) * TR + lane) * kChunkPitch;
       const size_t off = static_cast<size_t>(chunk_i) * kChunkVecs * 16;
@@ -638,7 +639,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
       bool ok = true;
       for (int c = 0; c < nc && ok; ++c) {
         const int stage = static_cast<int>(g_c % static_cast<uint32_t>(D));
-        ok = __all_sync(0xffffffffu, mbar_wait(&sm.bars[stage], (g_c / static_cast<uint32_t>(D)) & 1u));
+        ok = __all_sync(0xffffffffu, mbar_wait(&sm.bars[stage], (g_c / static_cast<uint32_t>(D)) & 1u, a.wt.spins));
         if (!ok) break;
         const int cnt = min(kChunkVecs, V - kChunkVecs * c);
         if (live) {
@@ -725,9 +726,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
     __syncthreads();
     if (*sm.abort_flag) {
       // bounded second chance for the copies still in flight before the CTA retires
-      if (warp == 0)
+      if (warp == 0) {
         for (uint32_t g = g_c; g != g_i; ++g)
-          mbar_wait(&sm.bars[g % static_cast<uint32_t>(D)], (g / static_cast<uint32_t>(D)) & 1u);
+          mbar_wait(&sm.bars[g % static_cast<uint32_t>(D)], (g / static_cast<uint32_t>(D)) & 1u, a.wt.spins);
+        drain_pause();
+      }
       return;
     }
   }
@@ -803,6 +806,7 @@ bool norm_lanerow_supported(int dtype, int cols) {
 template <int DT, int OP>
 static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
   const int row_bytes = a.n * Elem<DT>::kBytes;
+  a.wt = wait_tuning();
   a.V = row_bytes / 16;
   a.pitch = row_bytes + ((a.V & 1) ? 0 : 16);
   // rows per CTA: up to a warp's worth, sized so that several CTAs fit in an SM's shared memory
@@ -812,15 +816,14 @@ static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
   if (R < 4) R = static_cast<int>((72 * 1024) / a.pitch);  // long rows: about three
   if (R > 32) R = 32;
   if (R < 1) R = 1;
-  int64_t spread = (a.rows + 2 * kSmCount - 1) / (2 * kSmCount);
+  const int sms = sm_count();
+  int64_t spread = (a.rows + 2 * sms - 1) / (2 * sms);
   if (R > spread) R = static_cast<int>(spread);
   a.R = R;
   size_t smem = lanerow_smem(R, a.pitch);
   auto kern = norm_lanerow_kernel<DT, OP>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-  }
+  cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), kLaneRowThreads, smem, -1, nullptr);
+  if (e != cudaSuccess) return e;
   int64_t grid = (a.rows + R - 1) / R;
   kern<<<static_cast<unsigned>(grid), kLaneRowThreads, smem, stream>>>(a);
   return cudaGetLastError();
@@ -830,9 +833,10 @@ static cudaError_t launch_lanerow_t(LaneRowArgs a, cudaStream_t stream) {
 // rounds over the SMs than tiles of `max_rows` would, so that every SM gets the same number of rows
 // (16384 rows: 4 rounds of 28 rows instead of 4 of 32 on some SMs and 3 on the others).
 static int balanced_tile_rows(int64_t rows, int max_rows) {
-  const int64_t per_round = static_cast<int64_t>(max_rows) * kSmCount;
+  const int sms = sm_count();
+  const int64_t per_round = static_cast<int64_t>(max_rows) * sms;
   const int64_t rounds = (rows + per_round - 1) / per_round;
-  int64_t tr = (rows + rounds * kSmCount - 1) / (rounds * kSmCount);
+  int64_t tr = (rows + rounds * sms - 1) / (rounds * sms);
   if (tr > max_rows) tr = max_rows;
   if (tr < 1) tr = 1;
   return static_cast<int>(tr);
@@ -843,14 +847,13 @@ static cudaError_t launch_shortrow_t(const LaneRowArgs& a, cudaStream_t stream) 
   constexpr int TR = ShortTile<VPL>::kRows;
   const size_t smem = static_cast<size_t>(4) * TR * (32 * VPL + 1) * 16 + 2 * TR * sizeof(float2);
   auto kern = norm_shortrow_kernel<DT, OP, VPL>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                           static_cast<int>((smem + 1024) * 100 / (228 * 1024) + 1));
+  cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), kShortThreads, smem,
+                                       static_cast<int>((smem + 1024) * 100 / (228 * 1024) + 1), nullptr);
   if (e != cudaSuccess) return e;
   const int tile_rows = balanced_tile_rows(a.rows, TR);
   int64_t tiles = (a.rows + tile_rows - 1) / tile_rows;
-  int64_t grid = tiles < kSmCount ? tiles : kSmCount;
+  const int sms = sm_count();
+  int64_t grid = tiles < sms ? tiles : sms;
   kern<<<static_cast<unsigned>(grid), kShortThreads, smem, stream>>>(a, tile_rows);
   return cudaGetLastError();
 }
@@ -860,7 +863,7 @@ static bool shortrow_applies(int dtype, const LaneRowArgs& a) {
   const int esz = dtype == kDtF32 ? 4 : 2;
   const int64_t row_bytes = static_cast<int64_t>(a.n) * esz;
   return a.ids == nullptr && row_bytes % 512 == 0 && row_bytes / 512 >= 1 && row_bytes / 512 <= 4 &&
-         a.rows >= 2 * 32 * kSmCount;
+         a.rows >= 2 * 32 * sm_count();
 }
 
 template <int DT, int OP>
@@ -891,7 +894,8 @@ static void stream_shape(int64_t rows, bool res, int& TR, int& D, int& CV, int64
   if (D < 1) D = 1;
   if (D > kStreamMaxStages) D = kStreamMaxStages;
   const int64_t tiles = (rows + TR - 1) / TR;
-  grid = tiles < kSmCount ? tiles : kSmCount;
+  const int sms = sm_count();
+  grid = tiles < sms ? tiles : sms;
 }
 
 static bool stream_applies(int dtype, const LaneRowArgs& a) {
@@ -904,16 +908,15 @@ static bool stream_applies(int dtype, const LaneRowArgs& a) {
 template <int DT, int OP, bool RES>
 static cudaError_t launch_stream_r(LaneRowArgs a, cudaStream_t stream) {
   a.V = a.n * Elem<DT>::kBytes / 16;
+  a.wt = wait_tuning();
   int TR, D, CV;
   int64_t grid;
   stream_shape(a.rows, RES, TR, D, CV, grid);
   const size_t smem = StreamSmem::bytes(TR, D, CV, RES);
   auto kern = norm_stream_kernel<DT, OP, RES>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
   int percent = static_cast<int>((smem + 1024) * 100 / (228 * 1024) + 1);
   if (percent > 100) percent = 100;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+  cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), kStreamThreads, smem, percent, nullptr);
   if (e != cudaSuccess) return e;
   kern<<<static_cast<unsigned>(grid), kStreamThreads, smem, stream>>>(a, TR, D, CV);
   return cudaGetLastError();

@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
     slot.kinds[stage] = kind;
     if (kind == kRowDecode) {
       const unsigned char* src = a.qtable + (id - a.vocab_begin) * static_cast<uint64_t>(a.row_bytes);
-      mbar_expect_tx(&slot.bars[stage], static_cast<uint32_t>(a.row_bytes));
+      mbar_expect_tx(&slot.bars[stage], static_cast<uint32_t>(a.row_bytes) + a.wt.extra_tx);
       bulk_g2s(slot.ring + stage * stage_bytes, src, static_cast<uint32_t>(a.row_bytes), &slot.bars[stage]);
     }
   };
@@ -284,11 +284,16 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       stage = stage + 1 == stages ? 0 : stage + 1;
       continue;
     }
+    bool wait_ok = true;
     if (kind == kRowDecode) {
       // a wait that runs out is recorded and acted on after the row's synchronisation points,
-      // where the whole slot sees the flag and can leave together
-      if (!mbar_wait(&slot.bars[stage], (phase >> stage) & 1u)) *slot.abort_flag = 1;
-      phase ^= 1u << stage;
+      // where the whole slot sees the flag and can leave together; the stage's parity bit moves on
+      // only when its phase really completed
+      wait_ok = mbar_wait(&slot.bars[stage], (phase >> stage) & 1u, a.wt.spins);
+      if (wait_ok)
+        phase ^= 1u << stage;
+      else
+        *slot.abort_flag = 1;
     }
 
     // Each thread owns HB half blocks: vectors 2p and 2p+1 for p = j*tpr + tx share one scale
@@ -327,8 +332,12 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
     if (*slot.abort_flag) {
       if (tx == 0) {
         report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row, 0, a.vocab);
-        for (int j = 0; j < stages; ++j)  // bounded second chance for the copies still in flight
-          if (slot.kinds[j] == kRowDecode) mbar_wait(&slot.bars[j], (phase >> j) & 1u);
+        // Bounded second chance for the copies still in flight: every stage that holds a row to be
+        // decoded has one, except this row's own stage if this thread saw it complete.
+        for (int j = 0; j < stages; ++j)
+          if (slot.kinds[j] == kRowDecode && !(j == stage && wait_ok && kind == kRowDecode))
+            mbar_wait(&slot.bars[j], (phase >> j) & 1u, a.wt.spins);
+        drain_pause();
       }
       return;
     }
@@ -456,17 +465,12 @@ static cudaError_t persistent_grid(K kern, int threads, size_t smem, int ctas_wa
   const size_t per_cta = smem + 1024;  // the driver reserves 1 KB per CTA
   int percent = static_cast<int>((per_cta * ctas_wanted * 100 + 228 * 1024 - 1) / (228 * 1024));
   if (percent > 100) percent = 100;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+  int per_sm = 1, sms = 1;
+  cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), threads, smem, percent, &per_sm);
   if (e != cudaSuccess) return e;
-  if (smem > 48 * 1024) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-  }
-  int per_sm = 1;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem);
+  e = device_sm_count(&sms);
   if (e != cudaSuccess) return e;
-  if (per_sm < 1) per_sm = 1;
-  int64_t g = static_cast<int64_t>(kSmCount) * per_sm;
+  int64_t g = static_cast<int64_t>(sms) * per_sm;
   if (g > work_items) g = work_items;
   grid = static_cast<unsigned>(g);
   return cudaSuccess;
@@ -537,7 +541,9 @@ cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t st
 }
 
 template <int QT, int DT, int HB>
-static cudaError_t launch_q_t(const QRmsArgs& a, int tpr, cudaStream_t stream) {
+static cudaError_t launch_q_t(const QRmsArgs& a_in, int tpr, cudaStream_t stream) {
+  QRmsArgs a = a_in;
+  a.wt = wait_tuning();
   const int rpc = 128 / tpr;  // row slots per 128-thread CTA
   const int ctas = 5;         // CTAs per SM the register cap admits (640 threads); more ran slower
   const int stage_bytes = (a.row_bytes + 15) & ~15;

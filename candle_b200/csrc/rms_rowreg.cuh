@@ -67,6 +67,7 @@ struct QRmsArgs {
   int owned_only;
   int n_more;
   uint4* y_more[7];
+  WaitTuning wt;  // filled by the launcher
 };
 
 // Shared-memory layout of one CTA of the row-register kernels (per row slot `ty`).

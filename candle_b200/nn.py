@@ -54,17 +54,14 @@ class LayerNorm:
         return self._bias
 
     def forward(self, x: torch.Tensor, *, residual: torch.Tensor | None = None) -> torch.Tensor:
-        # candle-nn/src/layer_norm.rs:108-136: the fused op needs a contiguous input, remove_mean
-        # and a bias.  candle's other branch is a chain of generic tensor ops (to_dtype, sum_keepdim,
-        # broadcast_sub/div/mul/add) that are not part of this library.
+        # candle-nn/src/layer_norm.rs:108-136: the fused op iff the input is contiguous, the mean is
+        # removed and there is a bias; otherwise the composite chain (f32 inside, one rounding, weight
+        # and bias applied in the tensor's dtype), which rounds differently for f16 / bf16.
         if x.is_contiguous() and self.remove_mean and self._bias is not None:
             return ops.layer_norm(x, self._weight, self._bias, self.eps, residual=residual)
-        if not self.remove_mean and x.is_contiguous():
-            return ops.rms_norm(x, self._weight, self.eps, residual=residual)
-        raise CandleError(
-            "LayerNorm: only the fused paths are provided (contiguous input and either remove_mean with a bias, "
-            "or the rms-norm form); candle's composite slow path is built from generic tensor ops outside this library"
-        )
+        if residual is not None:
+            raise CandleError("a fused residual is only available on the fused norm paths")
+        return ops._norm_slow(x, self._weight, self._bias, self.eps, self.remove_mean)
 
     __call__ = forward
 
@@ -78,7 +75,12 @@ class RmsNorm:
     def into_inner(self) -> LayerNorm:
         return self._inner
 
+    def forward_diff(self, xs: torch.Tensor) -> torch.Tensor:
+        # layer_norm.rs:176-178: always the inner LayerNorm, i.e. the composite chain
+        return self._inner.forward(xs)
+
     def forward(self, xs: torch.Tensor, *, residual: torch.Tensor | None = None) -> torch.Tensor:
+        # layer_norm.rs:186-194: only this entry point uses the fused rms-norm op
         if xs.is_contiguous():
             return ops.rms_norm(xs, self._inner.weight(), self._inner.eps, residual=residual)
         return self._inner.forward(xs, residual=residual)

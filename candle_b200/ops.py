@@ -86,10 +86,12 @@ def _out_check(out: torch.Tensor | None, xs: torch.Tensor) -> torch.Tensor:
 
 
 def rms_norm(xs: torch.Tensor, alpha: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
-             return_sum: bool = False, flags: int = 0, out: torch.Tensor | None = None):
+             return_sum: bool = False, flags: int = 0, out: torch.Tensor | None = None,
+             status: torch.Tensor | None = None):
     """``candle_nn::ops::rms_norm(xs, alpha, eps)``; with ``residual`` the norm of ``xs + residual``.
 
-    Returns ``y`` (``out`` when given), or ``(y, xs + residual)`` when ``return_sum`` is set.
+    Returns ``y`` (``out`` when given), or ``(y, xs + residual)`` when ``return_sum`` is set.  A
+    ``status`` record (``new_status``) receives device-side problems (a bounded wait that ran out).
     """
     if xs.dim() == 0:
         raise CandleError("unexpected rank, expected: at least 1, got: 0")
@@ -102,14 +104,14 @@ def rms_norm(xs: torch.Tensor, alpha: torch.Tensor, eps: float, *, residual: tor
     rows = xs.numel() // cols if cols else 0
     y = _out_check(out, xs)
     h = torch.empty_like(xs) if return_sum else None
-    _cabi.call("cb200_rms_norm", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(y), _ptr(h), rows, cols, float(eps),
-               _DTYPES[xs.dtype], flags, _stream(xs))
+    _cabi.call("cb200_rms_norm_checked", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(y), _ptr(h), rows, cols,
+               float(eps), _DTYPES[xs.dtype], flags, _ptr(status), _stream(xs))
     return (y, h) if return_sum else y
 
 
 def layer_norm(xs: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, eps: float, *,
                residual: torch.Tensor | None = None, return_sum: bool = False, flags: int = 0,
-               out: torch.Tensor | None = None):
+               out: torch.Tensor | None = None, status: torch.Tensor | None = None):
     """``candle_nn::ops::layer_norm(xs, alpha, beta, eps)``; with ``residual`` the norm of ``xs + residual``."""
     if xs.dim() == 0:
         raise CandleError("unexpected rank, expected: at least 1, got: 0")
@@ -123,9 +125,46 @@ def layer_norm(xs: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, eps: f
     rows = xs.numel() // cols if cols else 0
     y = _out_check(out, xs)
     h = torch.empty_like(xs) if return_sum else None
-    _cabi.call("cb200_layer_norm", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(beta), _ptr(y), _ptr(h), rows, cols,
-               float(eps), _DTYPES[xs.dtype], flags, _stream(xs))
+    _cabi.call("cb200_layer_norm_checked", _ptr(xs), _ptr(residual), _ptr(alpha), _ptr(beta), _ptr(y), _ptr(h), rows,
+               cols, float(eps), _DTYPES[xs.dtype], flags, _ptr(status), _stream(xs))
     return (y, h) if return_sum else y
+
+
+def _norm_slow(xs: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, eps: float, remove_mean: bool):
+    """candle's composite norm chain (candle-nn/src/layer_norm.rs:115-135) in one launch."""
+    if xs.dim() == 0:
+        raise CandleError("unexpected rank, expected: at least 1, got: 0")
+    if xs.dtype not in _DTYPES:
+        raise CandleError(f"unsupported dtype for rmsnorm {_DTYPE_NAMES.get(xs.dtype, xs.dtype)}")
+    cols = xs.shape[-1]
+    for p in (weight, bias):
+        if p is None:
+            continue
+        if p.dtype != xs.dtype:
+            raise CandleError(f"dtype mismatch in mul, lhs: {_DTYPE_NAMES[xs.dtype]}, rhs: {_DTYPE_NAMES.get(p.dtype, p.dtype)}")
+        if p.dim() != 1 or p.shape[0] != cols:
+            raise CandleError(f"shape mismatch in broadcast_mul, lhs: {_dims(xs)}, rhs: {_dims(p)}")
+    _same_device(xs, weight, bias)
+    # the chain starts with to_dtype, which reads a strided input into a contiguous tensor
+    xs = xs if xs.is_contiguous() else xs.contiguous()
+    weight = weight if weight.is_contiguous() else weight.contiguous()
+    if bias is not None and not bias.is_contiguous():
+        bias = bias.contiguous()
+    rows = xs.numel() // cols if cols else 0
+    y = torch.empty_like(xs)
+    _cabi.call("cb200_layer_norm_slow", _ptr(xs), _ptr(weight), _ptr(bias), _ptr(y), rows, cols, float(eps),
+               _DTYPES[xs.dtype], 1 if remove_mean else 0, _stream(xs))
+    return y
+
+
+def rms_norm_slow(x: torch.Tensor, alpha: torch.Tensor, eps: float) -> torch.Tensor:
+    """``candle_nn::ops::rms_norm_slow`` (candle-nn/src/ops.rs:628-639)."""
+    return _norm_slow(x, alpha, None, eps, False)
+
+
+def layer_norm_slow(x: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, eps: float) -> torch.Tensor:
+    """``candle_nn::ops::layer_norm_slow`` (candle-nn/src/ops.rs:876-894)."""
+    return _norm_slow(x, alpha, beta, eps, True)
 
 
 def _ids_checks(ids: torch.Tensor) -> torch.Tensor:

@@ -121,6 +121,48 @@ CB200_API int cb200_layer_norm(const void* x, const void* residual, const void* 
                      cb200_stream_t stream);
 
 /*
+ * cb200_rms_norm / cb200_layer_norm with a status record.  Some of the norm kernels stage rows with
+ * the bulk-copy engine and wait for them with a bounded wait; should such a wait ever run out the
+ * rows concerned are left unwritten.  These variants record that as CB200_STATUS_WAIT_TIMEOUT in
+ * `status` (NULL is allowed and makes them identical to the plain entry points, which have no way
+ * to tell).  The reference has no counterpart: its kernels wait for nothing.
+ */
+CB200_API int cb200_rms_norm_checked(const void* x, const void* residual, const void* alpha, void* y, void* sum_out,
+                           int64_t rows, int32_t cols, float eps, int dtype, int flags, cb200_status* status,
+                           cb200_stream_t stream);
+CB200_API int cb200_layer_norm_checked(const void* x, const void* residual, const void* gamma, const void* beta,
+                             void* y, void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags,
+                             cb200_status* status, cb200_stream_t stream);
+
+/*
+ * candle's composite ("slow") norm in one launch: what LayerNorm::forward computes whenever the
+ * fused op does not apply -- no bias (LayerNorm::new_no_bias, layer_norm_no_bias), remove_mean ==
+ * false (LayerNorm::rms_norm, RmsNorm::forward_diff / into_inner), or an input that had to be made
+ * contiguous first (candle-nn/src/layer_norm.rs:108-136) -- and what ops::rms_norm_slow /
+ * layer_norm_slow compute (candle-nn/src/ops.rs:628-639, 876-894):
+ *   x = f32(x); if remove_mean: x -= sum(x) / n;  d = sqrt(sum(x*x) / n + eps);
+ *   y = T(x / d) * weight (+ bias), the product and the sum evaluated in T
+ * Replaces the chain of to_dtype / sum_keepdim / affine / broadcast_{sub,div,mul,add} / sqr / sqrt
+ * launches (kernels of candle-kernels/src/{cast,reduce,affine,binary,unary}.cu).  Differs from
+ * cb200_rms_norm / cb200_layer_norm in where it rounds, as candle's two paths do.  The row sums
+ * follow the order of candle's CPU `vec_sum` in an AVX build (candle-core/src/cpu/mod.rs:113-135,
+ * cpu/avx.rs:54-66), which makes the result bit-equal to that build; other builds of candle sum
+ * in another order and agree to rounding error.  `bias` may be NULL.
+ */
+CB200_API int cb200_layer_norm_slow(const void* x, const void* weight, const void* bias, void* y, int64_t rows,
+                          int32_t cols, float eps, int dtype, int remove_mean, cb200_stream_t stream);
+
+/*
+ * Self-test hook, not for production use: with `enable` != 0 every later launch of a kernel that
+ * waits for bulk copies polls only a few dozen times and expects 16 bytes more than its copies
+ * deliver, so every such wait runs out, the kernel records CB200_STATUS_WAIT_TIMEOUT, lets the
+ * copies it issued land and returns -- the give-up path executes although nothing is wrong with the
+ * device.  Results of calls made in this mode are undefined.  enable == 0 restores normal waiting.
+ * Process-wide.  No counterpart in the reference.
+ */
+CB200_API int cb200_selftest_wait_expiry(int enable);
+
+/*
  * index_select along one dimension of a contiguous tensor viewed as [left, src_dim, right]:
  *   out[l, i, :] = src[l, ids[i], :]   for i < n_ids
  * Replaces IndexSelect::f + BackendStorage::index_select of the CUDA backend

@@ -6,6 +6,8 @@
  *
  *   ops::rms_norm(xs, alpha, eps)            candle_nn::ops::rms_norm        ops.rs:641-652, 536-543
  *   ops::layer_norm(xs, alpha, beta, eps)    candle_nn::ops::layer_norm      ops.rs:896-909, 770-781
+ *   ops::rms_norm_slow / layer_norm_slow     candle_nn::ops::*_slow          ops.rs:628-639, 876-894
+ *   LayerNorm / RmsNorm {..}.forward(xs)     candle_nn::{LayerNorm,RmsNorm}  layer_norm.rs:63-194
  *   index_select(t, ids, dim)                Tensor::index_select            tensor.rs:1568-1589
  *   Embedding{table, hidden}.forward(ids)    candle_nn::Embedding::forward   embedding.rs:28-37
  *   QTensor::embedding / embedding_rms_norm  (new: lookups out of GGML blocks)
@@ -160,7 +162,85 @@ inline void layer_norm(const Tensor& xs, const Tensor& alpha, const Tensor& beta
                                     static_cast<int>(xs.dtype), flags, stream));
 }
 
+/* the composite norm behind rms_norm_slow, layer_norm_slow and the modules' slow branch */
+inline void norm_slow_chain(const Tensor& xs, const Tensor& weight, const Tensor* bias, float eps, bool remove_mean,
+                      Tensor& out, cb200_stream_t stream) {
+  if (xs.rank() == 0) throw Error("unexpected rank, expected: at least 1, got: 0");
+  if (!is_float(xs.dtype)) throw Error(std::string("unsupported dtype for rmsnorm ") + dtype_name(xs.dtype));
+  /* candle's chain starts with to_dtype, which copies a strided input; a view here has no strides,
+   * so the caller makes that copy */
+  if (!xs.contiguous) throw Error("input has to be contiguous");
+  const int64_t cols = xs.dims.back();
+  const Tensor* params[] = {&weight, bias};
+  for (const Tensor* p : params) {
+    if (p == nullptr) continue;
+    if (p->dtype != xs.dtype)
+      throw Error(std::string("dtype mismatch in mul, lhs: ") + dtype_name(xs.dtype) + ", rhs: " + dtype_name(p->dtype));
+    if (p->rank() != 1 || p->dims[0] != cols || !p->contiguous)
+      throw Error("shape mismatch in broadcast_mul, lhs: " + dims_string(xs.dims) + ", rhs: " + dims_string(p->dims));
+  }
+  detail::check_out(out, xs.dims, xs.dtype, "layer-norm");
+  const int64_t rows = cols ? xs.elem_count() / cols : 0;
+  detail::check_rc(cb200_layer_norm_slow(xs.data, weight.data, bias ? bias->data : nullptr, out.data, rows,
+                                         static_cast<int32_t>(cols), eps, static_cast<int>(xs.dtype),
+                                         remove_mean ? 1 : 0, stream));
+}
+
+/* candle_nn::ops::rms_norm_slow (ops.rs:628-639): f32 inside, one rounding, weight applied in T. */
+inline void rms_norm_slow(const Tensor& xs, const Tensor& alpha, float eps, Tensor& out, cb200_stream_t stream) {
+  norm_slow_chain(xs, alpha, nullptr, eps, false, out, stream);
+}
+/* candle_nn::ops::layer_norm_slow (ops.rs:876-894). */
+inline void layer_norm_slow(const Tensor& xs, const Tensor& alpha, const Tensor& beta, float eps, Tensor& out,
+                            cb200_stream_t stream) {
+  norm_slow_chain(xs, alpha, &beta, eps, true, out, stream);
+}
+
 }  // namespace ops
+
+/* candle_nn::LayerNorm (layer_norm.rs:63-136): the fused op iff the input is contiguous, the mean is
+ * removed and there is a bias; the composite chain otherwise. */
+class LayerNorm {
+ public:
+  static LayerNorm create(Tensor weight, Tensor bias, double eps) { return LayerNorm(std::move(weight), std::move(bias), true, true, eps); }
+  static LayerNorm new_no_bias(Tensor weight, double eps) { return LayerNorm(std::move(weight), Tensor{}, false, true, eps); }
+  static LayerNorm rms_norm(Tensor weight, double eps) { return LayerNorm(std::move(weight), Tensor{}, false, false, eps); }
+  const Tensor& weight() const { return weight_; }
+  const Tensor* bias() const { return has_bias_ ? &bias_ : nullptr; }
+  double eps() const { return eps_; }
+  void forward(const Tensor& x, Tensor& out, cb200_stream_t stream) const {
+    if (x.contiguous && remove_mean_ && has_bias_) {
+      ops::layer_norm(x, weight_, bias_, static_cast<float>(eps_), out, stream);
+      return;
+    }
+    ops::norm_slow_chain(x, weight_, bias(), static_cast<float>(eps_), remove_mean_, out, stream);
+  }
+
+ private:
+  LayerNorm(Tensor w, Tensor b, bool has_bias, bool remove_mean, double eps)
+      : weight_(std::move(w)), bias_(std::move(b)), has_bias_(has_bias), remove_mean_(remove_mean), eps_(eps) {}
+  Tensor weight_, bias_;
+  bool has_bias_, remove_mean_;
+  double eps_;
+};
+
+/* candle_nn::RmsNorm (layer_norm.rs:167-194): the fused op on contiguous input, else the inner
+ * LayerNorm's composite chain; forward_diff always takes the latter. */
+class RmsNorm {
+ public:
+  RmsNorm(Tensor weight, double eps) : inner_(LayerNorm::rms_norm(std::move(weight), eps)) {}
+  const LayerNorm& into_inner() const { return inner_; }
+  void forward_diff(const Tensor& xs, Tensor& out, cb200_stream_t stream) const { inner_.forward(xs, out, stream); }
+  void forward(const Tensor& xs, Tensor& out, cb200_stream_t stream) const {
+    if (xs.contiguous)
+      ops::rms_norm(xs, inner_.weight(), static_cast<float>(inner_.eps()), out, stream);
+    else
+      inner_.forward(xs, out, stream);
+  }
+
+ private:
+  LayerNorm inner_;
+};
 
 /* Shape of t.index_select(ids, dim); throws what Tensor::index_select would for bad arguments. */
 inline Shape index_select_shape(const Tensor& t, const Tensor& ids, int64_t dim) {

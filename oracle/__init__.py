@@ -58,6 +58,9 @@ def lib() -> ctypes.CDLL:
         L.oracle_dequantize.argtypes = [ci, vp, vp, i64, ci]
         L.oracle_quantize.argtypes = [ci, vp, vp, i64]
         L.oracle_qembedding.argtypes = [ci, ci, ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(i64), ci]
+        L.oracle_norm_slow.argtypes = [ci, vp, vp, vp, vp, i64, i64, ctypes.c_double, ci, ci]
+        L.oracle_avx_vec_sum.argtypes = [vp, i64]
+        L.oracle_avx_vec_sum.restype = f32
         L.oracle_max_threads.restype = ci
         L.oracle_bf16_from_f32.argtypes = [f32]
         L.oracle_bf16_from_f32.restype = ctypes.c_uint16
@@ -142,6 +145,30 @@ def layer_norm(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: float, d
         "layer_norm",
     )
     return y
+
+
+def norm_slow(x: np.ndarray, weight: np.ndarray, bias: np.ndarray | None, eps: float, dtype: str,
+              remove_mean: bool = True, threads: int = 0) -> np.ndarray:
+    """candle's composite norm (``LayerNorm::forward`` off the fused path, ``ops::rms_norm_slow`` /
+    ``layer_norm_slow``): f32 internally, AVX-ordered row sums, one rounding to ``dtype``, then the
+    weight (and bias) applied in ``dtype``."""
+    x, weight = _check(x, dtype, "x"), _check(weight, dtype, "weight")
+    cols = x.shape[-1]
+    if bias is not None:
+        bias = _check(bias, dtype, "bias")
+    if weight.shape != (cols,) or (bias is not None and bias.shape != (cols,)):
+        raise ValueError("shape mismatch in the composite norm")
+    rows = x.size // cols if cols else 0
+    y = np.empty_like(x)
+    _rc(lib().oracle_norm_slow(DTYPES[dtype], _ptr(x), _ptr(weight), _ptr(bias) if bias is not None else None,
+                               _ptr(y), rows, cols, float(eps), 1 if remove_mean else 0, threads), "norm_slow")
+    return y
+
+
+def avx_vec_sum(row: np.ndarray) -> float:
+    """candle's ``vec_sum`` in its AVX order over one f32 row."""
+    row = np.ascontiguousarray(row, dtype=np.float32)
+    return float(lib().oracle_avx_vec_sum(_ptr(row), row.size))
 
 
 def index_select(src: np.ndarray, ids: np.ndarray, dim: int = 0) -> np.ndarray:

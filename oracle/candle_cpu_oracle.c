@@ -20,6 +20,7 @@
  */
 #include <math.h>
 #include <stddef.h>
+#include <stdlib.h>
 #include <stdint.h>
 #include <string.h>
 #ifdef _OPENMP
@@ -649,6 +650,106 @@ int oracle_qembedding(int qtype, int out_dtype, int id_dtype, const void* qtable
           oracle_cast_from_f32(out_dtype, tmp, (uint16_t*)out + o, QK, 1);
       }
     }
+  }
+  return rc;
+}
+
+/* ------------------------------------------------------------------------------------------------
+ * The composite ("slow") norm: LayerNorm::forward when the fused op does not apply
+ * (candle-nn/src/layer_norm.rs:108-136; the same chain as ops::rms_norm_slow / layer_norm_slow,
+ * candle-nn/src/ops.rs:628-639, 876-894).  Each line is one candle tensor op on f32 data:
+ *   x      = to_dtype(F32)
+ *   mean   = sum_keepdim(x) / n       -> `Tensor / f64` is affine(1/n, 0): fl(fl(s * f32(1/n)) + 0)
+ *                                        (candle-core/src/tensor.rs:2656, cpu_backend/mod.rs:291-299)
+ *   x      = x - mean                 (only when remove_mean)
+ *   norm   = sum_keepdim(x*x) / n     (same affine)
+ *   d      = sqrt(norm + eps)         -> `Tensor + f64` is affine(1, eps): fl(fl(v * 1) + f32(eps))
+ *   y      = T(x / d) * weight [+ bias]   (the product and the sum are T operations, each rounding)
+ * sum_keepdim over the last dimension of a contiguous f32 tensor is ReduceSum -> vec_reduce_sum ->
+ * vec_sum (candle-core/src/cpu_backend/mod.rs:213-260, candle-core/src/cpu/kernels.rs:79-81).  With
+ * AVX (candle builds with target-cpu=native, .cargo/config.toml) vec_sum keeps four 8-lane
+ * accumulators -- accumulator j lane l takes elements 32 i + 8 j + l in increasing i -- and folds
+ * them as (a0 + a1) + (a2 + a3), then low half + high half, then two horizontal adds; the k % 32
+ * leftovers are added one by one (candle-core/src/cpu/mod.rs:113-135, cpu/avx.rs:54-66).  That AVX
+ * order is what is restated here; a build without SIMD would add left to right instead.
+ */
+static float avx_vec_sum(const float* row, int64_t k) {
+  float acc[32];
+  for (int i = 0; i < 32; i++) acc[i] = 0.0f;
+  int64_t np = k & ~(int64_t)31;
+  for (int64_t i = 0; i < np; i += 32)
+    for (int l = 0; l < 32; l++) acc[l] = acc[l] + row[i + l];
+  float r8[8], t0[4];
+  for (int l = 0; l < 8; l++) {
+    float a01 = acc[l] + acc[8 + l];
+    float a23 = acc[16 + l] + acc[24 + l];
+    r8[l] = a01 + a23;
+  }
+  for (int l = 0; l < 4; l++) t0[l] = r8[l] + r8[l + 4];
+  float h0 = t0[0] + t0[1], h1 = t0[2] + t0[3];
+  float b = h0 + h1;
+  for (int64_t i = np; i < k; i++) b = b + row[i];
+  return b;
+}
+
+float oracle_avx_vec_sum(const float* row, int64_t k) { return avx_vec_sum(row, k); }
+
+int oracle_norm_slow(int dtype, const void* x, const void* weight, const void* bias, void* y, int64_t rows,
+                     int64_t cols, double eps, int remove_mean, int threads) {
+  int nt = resolve_threads(threads);
+  (void)nt;
+  if (dtype != ORACLE_F32 && dtype != ORACLE_F16 && dtype != ORACLE_BF16) return ORACLE_E_DTYPE;
+  const float inv_n = (float)(1.0 / (double)cols); /* T::from_f64(1. / rhs) */
+  const float eps32 = (float)eps;
+  int rc = ORACLE_OK;
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+  for (int64_t r = 0; r < rows; r++) {
+    float stack_buf[2048];
+    float* xf = cols <= 1024 ? stack_buf : (float*)malloc((size_t)cols * 2 * sizeof(float));
+    if (xf == NULL) {
+      rc = ORACLE_E_SHAPE;
+      continue;
+    }
+    float* sq = xf + cols;
+    for (int64_t c = 0; c < cols; c++) {
+      if (dtype == ORACLE_F32)
+        xf[c] = ((const float*)x)[r * cols + c];
+      else if (dtype == ORACLE_BF16)
+        xf[c] = bf16_to_f32(((const uint16_t*)x)[r * cols + c]);
+      else
+        xf[c] = f16_to_f32(((const uint16_t*)x)[r * cols + c]);
+    }
+    if (remove_mean) {
+      float s = avx_vec_sum(xf, cols);
+      float sm = s * inv_n;
+      float mean = sm + 0.0f;
+      for (int64_t c = 0; c < cols; c++) xf[c] = xf[c] - mean;
+    }
+    for (int64_t c = 0; c < cols; c++) sq[c] = xf[c] * xf[c];
+    float q = avx_vec_sum(sq, cols);
+    float qm = q * inv_n;
+    float norm = qm + 0.0f;
+    float n1 = norm * 1.0f;
+    float d = sqrtf(n1 + eps32);
+    for (int64_t c = 0; c < cols; c++) {
+      float xn = xf[c] / d;
+      if (dtype == ORACLE_F32) {
+        float t = xn * ((const float*)weight)[c];
+        if (bias != NULL) t = t + ((const float*)bias)[c];
+        ((float*)y)[r * cols + c] = t;
+      } else if (dtype == ORACLE_BF16) {
+        uint16_t t = bf16_from_f32(xn);
+        t = bf16_from_f32(bf16_to_f32(t) * bf16_to_f32(((const uint16_t*)weight)[c]));
+        if (bias != NULL) t = bf16_from_f32(bf16_to_f32(t) + bf16_to_f32(((const uint16_t*)bias)[c]));
+        ((uint16_t*)y)[r * cols + c] = t;
+      } else {
+        uint16_t t = f16_from_f32(xn);
+        t = f16_from_f32(f16_to_f32(t) * f16_to_f32(((const uint16_t*)weight)[c]));
+        if (bias != NULL) t = f16_from_f32(f16_to_f32(t) + f16_to_f32(((const uint16_t*)bias)[c]));
+        ((uint16_t*)y)[r * cols + c] = t;
+      }
+    }
+    if (xf != stack_buf) free(xf);
   }
   return rc;
 }

@@ -81,6 +81,27 @@ int main() {
   Tensor x0{fake, {0, 8}, DType::F32, true}, y0{fake, {0, 8}, DType::F32, true};
   ops::rms_norm(x0, a, 1e-5f, y0, nullptr);
   std::printf("ok zero rows\n");
+  // modules: candle's dispatch (layer_norm.rs:108-136, 186-194) decided on the host
+  LayerNorm ln = LayerNorm::create(a, a, 1e-5), ln_nb = LayerNorm::new_no_bias(a, 1e-5);
+  RmsNorm rn(a, 1e-5);
+  ln.forward(x0, y0, nullptr);      // fused op, zero rows: nothing launched
+  ln_nb.forward(x0, y0, nullptr);   // composite chain, zero rows
+  rn.forward(x0, y0, nullptr);
+  rn.forward_diff(x0, y0, nullptr);
+  std::printf("ok module zero rows\n");
+  expect_error("LayerNorm fused weight shape", "shape mismatch in layer-norm src: [4, 8] alpha: [7] beta: [7]",
+               [&] { LayerNorm::create(a7, a7, 1e-5).forward(x, y, nullptr); });
+  expect_error("LayerNorm slow weight shape", "shape mismatch in broadcast_mul, lhs: [4, 8], rhs: [7]",
+               [&] { LayerNorm::new_no_bias(a7, 1e-5).forward(x, y, nullptr); });
+  expect_error("LayerNorm slow weight dtype", "dtype mismatch in mul, lhs: F32, rhs: F16",
+               [&] { LayerNorm::rms_norm(ah, 1e-5).forward(x, y, nullptr); });
+  expect_error("RmsNorm strided input", "input has to be contiguous", [&] { rn.forward(xs, y, nullptr); });
+  if (ln.bias() == nullptr || ln_nb.bias() != nullptr || rn.into_inner().bias() != nullptr) {
+    std::printf("FAIL module accessors\n");
+    ++failures;
+  } else {
+    std::printf("ok module accessors\n");
+  }
   cb200_status st{};
   st.code = 1;
   st.index = 12;
