@@ -31,6 +31,9 @@ SIGNATURES = {
     "cb200_qembedding_rms_norm_owner": [
         _vp, _int, _vp, _vp, _vp, _int, _i64, _i32, _i64, _f32, _int, _int, _i64, _i64, _int, _vp, _vp,
     ],
+    "cb200_qembedding_rms_norm_row_owner": [
+        _vp, _int, _vp, _vp, _vp, _int, _vp, _i64, _i32, _i64, _f32, _int, _int, _i64, _i64, _int, _vp, _vp,
+    ],
 }
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2

@@ -374,11 +374,10 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   return cuda_result(cb200::launch_qrms_rowreg(qtype, out_dtype, a, stream), name);
 }
 
-int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* ids, const void* alpha,
-                                    void* const* dsts, int n_dsts, int64_t vocab, int32_t hidden, int64_t n_ids,
-                                    float eps, int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
-                                    int flags, cb200_status* status, cb200_stream_t stream) {
-  const char* name = "cb200_qembedding_rms_norm_owner";
+static int owner_impl(const char* name, const void* qtable, int qtype, const void* ids, const void* alpha,
+                      void* const* dsts, int n_dsts, const int64_t* row_bounds, int64_t vocab, int32_t hidden,
+                      int64_t n_ids, float eps, int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
+                      int flags, cb200_status* status, cb200_stream_t stream) {
   if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
   if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
   if (dsts == nullptr || n_dsts < 1 || n_dsts > 8)
@@ -389,13 +388,23 @@ int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* i
   if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
     return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
                 (long long)vocab_end, (long long)vocab);
+  if (row_bounds != nullptr) {
+    if (row_bounds[0] != 0 || row_bounds[n_dsts] != n_ids)
+      return fail(CB200_E_INVALID_ARGUMENT, "%s: row bounds must run from 0 to n_ids (%lld), got %lld .. %lld", name,
+                  (long long)n_ids, (long long)row_bounds[0], (long long)row_bounds[n_dsts]);
+    for (int d = 0; d < n_dsts; ++d)
+      if (row_bounds[d + 1] < row_bounds[d])
+        return fail(CB200_E_INVALID_ARGUMENT, "%s: row bounds must not decrease (entry %d)", name, d + 1);
+  }
   if (n_ids == 0) return CB200_OK;
   if (alpha == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
   if (!aligned16(alpha) || !aligned16(qtable))
     return fail(CB200_E_INVALID_ARGUMENT, "%s: alpha and the table must be 16-byte aligned", name);
-  for (int d = 0; d < n_dsts; ++d)
-    if (dsts[d] == nullptr || !aligned16(dsts[d]))
+  for (int d = 0; d < n_dsts; ++d) {
+    const bool empty = row_bounds != nullptr && row_bounds[d + 1] == row_bounds[d];
+    if ((dsts[d] == nullptr && !empty) || !aligned16(dsts[d]))
       return fail(CB200_E_INVALID_ARGUMENT, "%s: destination %d is null or not 16-byte aligned", name, d);
+  }
   if (!fusable_qtype(qtype) || out_dtype == CB200_DTYPE_F32 || !cb200::qrms_rowreg_supported(out_dtype, hidden))
     return fail(CB200_E_INVALID_ARGUMENT,
                 "%s: needs the single-launch kernel (Q4_0 / Q8_0 blocks, f16 / bf16 output, hidden a multiple of 32 "
@@ -418,10 +427,31 @@ int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* i
   a.bulk = aligned16(qtable) && a.row_bytes % 16 == 0;
   a.eps = eps;
   a.flags = flags;
-  a.owned_only = 1;
+  a.owned_only = row_bounds != nullptr ? 2 : 1;
   a.n_more = n_dsts - 1;
   for (int d = 1; d < n_dsts; ++d) a.y_more[d - 1] = static_cast<uint4*>(dsts[d]);
+  if (row_bounds != nullptr)
+    for (int d = 0; d <= n_dsts; ++d) a.row_bounds[d] = row_bounds[d];
   return cuda_result(cb200::launch_qrms_rowreg(qtype, out_dtype, a, stream), name);
+}
+
+int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* ids, const void* alpha,
+                                    void* const* dsts, int n_dsts, int64_t vocab, int32_t hidden, int64_t n_ids,
+                                    float eps, int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
+                                    int flags, cb200_status* status, cb200_stream_t stream) {
+  return owner_impl("cb200_qembedding_rms_norm_owner", qtable, qtype, ids, alpha, dsts, n_dsts, nullptr, vocab, hidden,
+                    n_ids, eps, out_dtype, id_dtype, vocab_begin, vocab_end, flags, status, stream);
+}
+
+int cb200_qembedding_rms_norm_row_owner(const void* qtable, int qtype, const void* ids, const void* alpha,
+                                        void* const* dsts, int n_dsts, const int64_t* row_bounds, int64_t vocab,
+                                        int32_t hidden, int64_t n_ids, float eps, int out_dtype, int id_dtype,
+                                        int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
+                                        cb200_stream_t stream) {
+  const char* name = "cb200_qembedding_rms_norm_row_owner";
+  if (row_bounds == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null row bounds", name);
+  return owner_impl(name, qtable, qtype, ids, alpha, dsts, n_dsts, row_bounds, vocab, hidden, n_ids, eps, out_dtype,
+                    id_dtype, vocab_begin, vocab_end, flags, status, stream);
 }
 
 }  // extern "C"

@@ -211,7 +211,9 @@ struct QSlot {
   }
 };
 
-template <int QT, int DT, int HB, bool OWNER>
+constexpr int kOwnerNone = 0, kOwnerToAll = 1, kOwnerToRowOwner = 2;
+
+template <int QT, int DT, int HB, int OWNER>
 __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, int stages) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
@@ -276,7 +278,7 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       }
     }
     const int kind = slot.kinds[stage];
-    if (OWNER && kind == kRowMasked) {  // another rank owns this row and writes it
+    if (OWNER != kOwnerNone && kind == kRowMasked) {  // another rank owns this row and writes it
       if (tpr > 32)
         row_barrier(bar_id, tpr);
       else
@@ -354,13 +356,21 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
       const bool fast_div = (DT == kDtBF16) && (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
       const float r = fast_div ? __frcp_rn(m) : 0.0f;
       uint4* yr = a.y + row * a.V;
+      if (OWNER == kOwnerToRowOwner) {
+        // the one destination of this row: the buffer of the rank whose row block contains it
+        int r = 0;
+#pragma unroll
+        for (int d = 1; d < 8; ++d)
+          if (d <= a.n_more && row >= a.row_bounds[d]) r = d;
+        yr = (r == 0 ? a.y : a.y_more[r - 1]) + (row - a.row_bounds[r]) * a.V;
+      }
       // |h| >= the smallest block scale for every non-zero element: above 2^-40 no product with
       // 1/m (m <= 2^60) can fall under 2^-100, and the guard can go.
       // one finished 32-byte piece to the local buffer and to every further destination
       auto put = [&](int p, const uint4& lo, const uint4& hi) {
         stg_stream(yr + 2 * p, lo);
         stg_stream(yr + 2 * p + 1, hi);
-        if (OWNER) {
+        if (OWNER == kOwnerToAll) {
 #pragma unroll
           for (int d = 0; d < 7; ++d) {
             if (d < a.n_more) {
@@ -554,9 +564,10 @@ static cudaError_t launch_q_t(const QRmsArgs& a_in, int tpr, cudaStream_t stream
   const size_t smem = QSlot::bytes(stages, stage_bytes, tpr) * rpc;
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   // the owner-writes-to-all mode is a variant of its own: the plain lookup carries none of its code
-  auto kern = qrms_rowslot_kernel<QT, DT, HB, false>;
+  auto kern = qrms_rowslot_kernel<QT, DT, HB, kOwnerNone>;
   if constexpr (QT != kQTypeDense16) {
-    if (a.owned_only) kern = qrms_rowslot_kernel<QT, DT, HB, true>;
+    if (a.owned_only == 1) kern = qrms_rowslot_kernel<QT, DT, HB, kOwnerToAll>;
+    if (a.owned_only == 2) kern = qrms_rowslot_kernel<QT, DT, HB, kOwnerToRowOwner>;
   }
   unsigned grid = 1;
   cudaError_t e = persistent_grid(kern, 128, smem, ctas, (a.rows + rpc - 1) / rpc, grid);

@@ -64,9 +64,13 @@ struct QRmsArgs {
   // Owner-writes-to-all mode for a vocabulary-sharded table: rows whose id lies outside
   // [vocab_begin, vocab_end) are skipped instead of written as -0.0, and every finished row also
   // goes to `n_more` further buffers of the same shape (peers' memory mapped into this process).
+  // owned_only == 2 (row-owner mode): a finished row goes to exactly one buffer, that of the rank
+  // whose block of token rows contains it: destination r (y for r == 0, y_more[r - 1] otherwise)
+  // holds rows [row_bounds[r], row_bounds[r + 1]) as a [rows_r, V] tensor of its own.
   int owned_only;
   int n_more;
   uint4* y_more[7];
+  int64_t row_bounds[9];
   WaitTuning wt;  // filled by the launcher
 };
 

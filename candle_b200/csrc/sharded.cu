@@ -49,9 +49,11 @@ int sharded_steps(void* comm, const void* qtable, int qtype, const void* ids, co
 }
 
 // Scratch for the allocation-free entry point.  It lives in the library image: every GPU that loads
-// the library carries these bytes until the process exits.  In host code the array's name is only
-// a host-side handle, not a device address, so the address is looked up once per device (below)
-// and that pointer is what the kernels get.
+// the library's device code carries these bytes until the process exits.  In host code the array's
+// name is only a host-side handle, not a device address, so the address is looked up once per device
+// (below) and that pointer is what the kernels get.  With CUDA's default lazy module loading the
+// device image -- and with it the array's memory -- is brought onto a device by that first lookup,
+// not when the host library is loaded; CUDA_MODULE_LOADING=EAGER moves it to context creation.
 __device__ __align__(256) unsigned char g_static_scratch[CB200_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
@@ -135,7 +137,9 @@ int cb200_sharded_qembedding_rms_norm_static(void* comm, const void* qtable, int
   void* scratch = nullptr;
   int rc = static_scratch_address(&scratch);
   if (rc != CB200_OK) return rc;
-  // nothing in the scratch has to start at zero: the lookup writes every byte the later steps read
+  // Nothing in the scratch has to start at zero: for valid ids the lookup writes every byte the later
+  // steps read.  A row whose id is out of range is left unwritten (and recorded in `status`), so the
+  // array's old contents are what gets summed and normalised for it: that row of y is undefined.
   return sharded_steps(comm, qtable, qtype, ids, alpha, y, scratch, vocab, hidden, n_ids, eps, out_dtype, id_dtype,
                        vocab_begin, vocab_end, flags, status, stream);
 }

@@ -289,3 +289,40 @@ def qembedding_rms_norm_owner(qtensor, ids: torch.Tensor, alpha: torch.Tensor, e
     _cabi.call("cb200_qembedding_rms_norm_owner", _ptr(qtensor.data), qtensor.dtype.value, _ptr(flat), _ptr(alpha),
                ctypes.cast(arr, ctypes.c_void_p), len(ptrs), vocab, hidden, flat.shape[0], float(eps),
                _DTYPES[alpha.dtype], _ID_DTYPES[flat.dtype], begin, end, flags, _ptr(status), _stream(alpha))
+
+
+def qembedding_rms_norm_row_owner(qtensor, ids: torch.Tensor, alpha: torch.Tensor, eps: float, dst_ptrs, row_bounds, *,
+                                  vocab_range: tuple[int, int], vocab: int, flags: int = 0,
+                                  status: torch.Tensor | None = None) -> None:
+    """Row-owner step of a vocabulary-sharded lookup + RMS norm: the ids inside ``vocab_range`` are
+    decoded from this rank's slice ``qtensor`` and normalised, and each finished row is stored into
+    the one buffer whose block of token rows contains it.  ``dst_ptrs[r]`` is the device address of
+    rank r's ``[row_bounds[r + 1] - row_bounds[r], hidden]`` buffer (rank order; peers' buffers mapped
+    into this process), ``row_bounds`` the ``len(dst_ptrs) + 1`` block limits from 0 to ``ids.numel()``.
+    Ids owned by other ranks are skipped; the caller synchronises the ranks before reading."""
+    import ctypes
+
+    from .quantized import QTensor  # local import: quantized imports this module
+
+    if not isinstance(qtensor, QTensor) or len(qtensor.shape) != 2:
+        raise CandleError("qembedding expects a rank-2 QTensor")
+    if alpha.dtype not in _DTYPES:
+        raise CandleError(f"unsupported dtype for rmsnorm {alpha.dtype}")
+    local_vocab, hidden = qtensor.shape
+    if alpha.dim() != 1 or alpha.shape[0] != hidden or not alpha.is_contiguous():
+        raise CandleError(f"shape mismatch in rms-norm {list(ids.shape) + [hidden]} {_dims(alpha)}")
+    flat = _ids_checks(ids.reshape(-1))
+    _same_device(qtensor.data, flat, alpha)
+    begin, end = vocab_range
+    if end - begin != local_vocab:
+        raise CandleError(f"vocab shard [{begin}, {end}) does not match the table's {local_vocab} rows")
+    ptrs = [int(p) for p in dst_ptrs]
+    bounds = [int(b) for b in row_bounds]
+    if len(bounds) != len(ptrs) + 1:
+        raise CandleError(f"{len(ptrs)} destinations need {len(ptrs) + 1} row bounds, got {len(bounds)}")
+    arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    barr = (ctypes.c_int64 * len(bounds))(*bounds)
+    _cabi.call("cb200_qembedding_rms_norm_row_owner", _ptr(qtensor.data), qtensor.dtype.value, _ptr(flat), _ptr(alpha),
+               ctypes.cast(arr, ctypes.c_void_p), len(ptrs), ctypes.cast(barr, ctypes.c_void_p), vocab, hidden,
+               flat.shape[0], float(eps), _DTYPES[alpha.dtype], _ID_DTYPES[flat.dtype], begin, end, flags, _ptr(status),
+               _stream(alpha))

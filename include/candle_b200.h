@@ -246,6 +246,24 @@ CB200_API int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, con
                                     int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
                                     cb200_stream_t stream);
 
+/*
+ * The same exchange for callers that continue ROW-SHARDED after the lookup (each rank works on its
+ * own block of token rows): a finished row is stored into ONE buffer only, that of the rank whose
+ * block contains it.  `dsts[r]` (HOST array, in rank order, 1..8 entries) is rank r's buffer -- this
+ * rank's own memory for its own entry, peers' buffers mapped into this process for the others -- of
+ * shape [row_bounds[r + 1] - row_bounds[r], hidden]; `row_bounds` (HOST array of n_dsts + 1 entries,
+ * from 0 to n_ids, non-decreasing) gives the blocks, e.g. contiguous blocks whose sizes differ by at
+ * most one.  Per GPU only about (N-1)/N^2 of the output crosses NVLink, against (N-1)/N for
+ * cb200_qembedding_rms_norm_owner and 2(N-1)/N for candle's all-reduce
+ * (candle-examples/examples/llama_multiprocess/model.rs:31-90); after the ranks' barrier each buffer
+ * holds exactly its block, bit-identical to those rows of the unsharded lookup + norm.
+ */
+CB200_API int cb200_qembedding_rms_norm_row_owner(const void* qtable, int qtype, const void* ids, const void* alpha,
+                                        void* const* dsts, int n_dsts, const int64_t* row_bounds, int64_t vocab,
+                                        int32_t hidden, int64_t n_ids, float eps, int out_dtype, int id_dtype,
+                                        int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
+                                        cb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

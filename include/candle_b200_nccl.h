@@ -59,10 +59,16 @@ CB200_API int cb200_sharded_qembedding_rms_norm(void* comm, const void* qtable, 
  * created earlier (pass NULL for a single rank: no NCCL call is made).
  *
  * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
- * that device current) and keeps it; make that first call outside any stream capture.  All calls
- * share the one array, which keeps the previous call's rows: nothing in it needs clearing, because
- * the lookup rewrites every byte the later steps read, but two calls whose work overlaps on the GPU
- * (different streams, or threads) race on it -- serialise them.
+ * that device current) and keeps it.  Under CUDA's default lazy module loading that lookup is also
+ * what brings the library's device image, array included, onto the device: the 32 MiB are reserved
+ * THEN, not when the host library is loaded.  So make the first call on each device early -- before
+ * a memory pool claims the rest of the device (afterwards it can fail with an out-of-memory error),
+ * and outside any stream capture -- or run the process with CUDA_MODULE_LOADING=EAGER.  Every later
+ * call allocates nothing.  All calls share the one array, which keeps the previous call's rows:
+ * nothing in it needs clearing, because for valid ids the lookup rewrites every byte the later steps
+ * read (the row of y that belongs to an out-of-range id, which `status` records, is undefined), but
+ * two calls whose work overlaps on the GPU (different streams, or threads) race on it -- serialise
+ * them.
  */
 #define CB200_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 

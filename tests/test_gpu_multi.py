@@ -1,7 +1,7 @@
 """Multi-GPU checks (need >= 2 CUDA devices; skipped otherwise): the vocab-sharded lookup summed by
 NCCL equals the unsharded CPU oracle bit for bit (-0.0 included), with and without the
-reduce-scatter variant and with the owner-writes-to-all variant over peer-mapped buffers, and row
-sharding reproduces the unsharded rows."""
+reduce-scatter variant, with the owner-writes-to-all and the row-owner variants over peer-mapped
+buffers, and through the C entry points (caller scratch and built-in scratch) with a communicator."""
 import os
 import socket
 import sys
@@ -75,6 +75,19 @@ def _worker(rank, world, port, ret):
                 dist.barrier()
                 torch.cuda.synchronize()
                 ok = ok and np.array_equal(to_oracle(shared), want) and st2[0].item() == 0
+                # row-owner mode: each finished row goes only to the rank whose row block holds it
+                block, by_rank = peer_mapped_empty((-(-n // world), hidden), torch.bfloat16, dev, rank_order=True)
+                block.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
+                st3 = _new_status(dev)
+                mb, me = emb.forward_rms_norm_row_owner(ids_tensor(ids, dev), from_oracle(alpha, "bf16", dev), 1e-5,
+                                                        by_rank, status=st3)
+                torch.cuda.synchronize()
+                dist.barrier()
+                torch.cuda.synchronize()
+                ok = ok and (mb, me) == row_shard(n, rank, world)
+                ok = ok and np.array_equal(to_oracle(block[: me - mb]), want[mb:me]) and st3[0].item() == 0
         # the same through the C entry point with a communicator of its own
         from candle_b200 import _nccl
         from candle_b200.ops import _stream, new_status
@@ -91,6 +104,13 @@ def _worker(rank, world, port, ret):
                    st.data_ptr(), _stream(y))
         torch.cuda.synchronize()
         ok = ok and np.array_equal(to_oracle(y), want) and st[0].item() == 0
+        # the allocation-free entry with the same communicator: its NCCL sum runs on the built-in array
+        y2 = torch.full_like(y, 3.0)
+        for _ in range(2):
+            _nccl.call("cb200_sharded_qembedding_rms_norm_static", comm, tq.data_ptr(), 8, tids.data_ptr(),
+                       ta.data_ptr(), y2.data_ptr(), vocab, hidden, n, 1e-5, 2, 1, b, e, 0, st.data_ptr(), _stream(y))
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(y2.view(torch.int16), y.view(torch.int16)) and st[0].item() == 0
         _nccl.comm_destroy(comm)
         ret[rank] = bool(ok)
     finally:
