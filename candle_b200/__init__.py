@@ -19,14 +19,19 @@ from .ops import (
     layer_norm_slow,
     qembedding_rms_norm,
     rms_norm,
+    rms_norm_rows,
     rms_norm_slow,
+    rope,
+    rope_i,
+    rope_thd,
+    softmax_last_dim,
 )
 from .host_pipeline import PinnedNormPipeline
 from .nn import Embedding, LayerNorm, QEmbedding, RmsNorm
 from .quantized import GgmlDType, QTensor
 
 __all__ = [
-    "CandleError", "InvalidIndex", "rms_norm", "layer_norm", "rms_norm_slow", "layer_norm_slow", "index_select", "embedding_rms_norm",
+    "CandleError", "InvalidIndex", "rms_norm", "layer_norm", "rms_norm_slow", "layer_norm_slow", "rms_norm_rows", "softmax_last_dim", "rope", "rope_i", "rope_thd", "index_select", "embedding_rms_norm",
     "qembedding_rms_norm", "PinnedNormPipeline", "Embedding", "LayerNorm", "RmsNorm", "QEmbedding", "QTensor", "GgmlDType",
     "FLAG_FAST_SUM", "FLAG_FORCE_LANEROW", "FLAG_FORCE_GENERIC", "FLAG_FORCE_REPLAY",
 ]

@@ -19,6 +19,8 @@ SIGNATURES = {
     "cb200_rms_norm_checked": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp, _vp],
     "cb200_layer_norm_checked": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp, _vp],
     "cb200_layer_norm_slow": [_vp, _vp, _vp, _vp, _i64, _i32, _f32, _int, _int, _vp],
+    "cb200_softmax_last_dim": [_vp, _vp, _i64, _i32, _int, _vp],
+    "cb200_rope": [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _int, _int, _vp],
     "cb200_selftest_wait_expiry": [_int],
     "cb200_index_select": [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _int, _vp, _vp],
     "cb200_embedding": [_vp, _vp, _vp, _i64, _i32, _i64, _int, _int, _vp, _vp],
@@ -39,8 +41,10 @@ SIGNATURES = {
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 ID_U8, ID_U32, ID_I64 = 0, 1, 2
 QTYPE_Q4_0, QTYPE_Q4_1, QTYPE_Q5_0, QTYPE_Q5_1, QTYPE_Q8_0 = 2, 3, 6, 7, 8
+QTYPE_Q2K, QTYPE_Q3K, QTYPE_Q4K, QTYPE_Q5K, QTYPE_Q6K, QTYPE_Q8K = 10, 11, 12, 13, 14, 15
 FLAG_FAST_SUM, FLAG_FORCE_LANEROW, FLAG_FORCE_GENERIC, FLAG_FORCE_REPLAY = 1, 0x100, 0x200, 0x400
 STATUS_OK, STATUS_INVALID_INDEX, STATUS_WAIT_TIMEOUT = 0, 1, 2
+ROPE_INTERLEAVED, ROPE_HALF, ROPE_THD = 0, 1, 2
 
 
 class CandleB200Error(RuntimeError):

@@ -167,6 +167,31 @@ int cb200_layer_norm_slow(const void* x, const void* weight, const void* bias, v
   return cuda_result(cb200::launch_norm_slow(dtype, x, weight, bias, y, rows, cols, eps, remove_mean != 0, stream), name);
 }
 
+int cb200_softmax_last_dim(const void* x, void* y, int64_t rows, int32_t cols, int dtype, cb200_stream_t stream) {
+  const char* name = "cb200_softmax_last_dim";
+  if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
+  if (rows < 0 || cols < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape [%lld, %d]", name, (long long)rows, cols);
+  if (rows == 0 || cols == 0) return CB200_OK;
+  if (x == nullptr || y == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  if (x == y) return fail(CB200_E_INVALID_ARGUMENT, "%s: the output must not alias the input", name);
+  return cuda_result(cb200::launch_softmax_last_dim(dtype, x, y, rows, cols, stream), name);
+}
+
+int cb200_rope(const void* src, const void* cos, const void* sin, void* dst, int64_t b, int32_t h, int32_t t, int32_t d,
+               int dtype, int variant, cb200_stream_t stream) {
+  const char* name = "cb200_rope";
+  if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
+  if (variant < CB200_ROPE_INTERLEAVED || variant > CB200_ROPE_THD)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: unknown variant %d", name, variant);
+  if (b < 0 || h < 0 || t < 0 || d < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape", name);
+  if (d % 2 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: the last dimension (%d) must be even", name, d);
+  if (b == 0 || h == 0 || t == 0 || d == 0) return CB200_OK;
+  if (src == nullptr || cos == nullptr || sin == nullptr || dst == nullptr)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  if (src == dst) return fail(CB200_E_INVALID_ARGUMENT, "%s: the output must not alias the input", name);
+  return cuda_result(cb200::launch_rope(variant, dtype, src, cos, sin, dst, b, h, t, d, stream), name);
+}
+
 int cb200_selftest_wait_expiry(int enable) {
   // 64 polls and 16 bytes that never arrive: every bounded wait of the bulk-copy kernels runs out
   cb200::set_wait_tuning(enable ? cb200::WaitTuning{64u, 16u} : cb200::WaitTuning{cb200::kWaitSpins, 0u});
@@ -207,12 +232,14 @@ int cb200_dequantize(const void* blocks, int qtype, void* out, int64_t k, int ou
   const char* name = "cb200_dequantize";
   if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
   if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
-  if (k < 0 || k % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: %lld is not divisible by 32", name, (long long)k);
+  const int be = cb200::qblock_elems(qtype);
+  if (k < 0 || k % be != 0)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: %lld is not divisible by %d", name, (long long)k, be);
   if (k == 0) return CB200_OK;
   if (blocks == nullptr || out == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null tensor pointer", name);
   if (!aligned16(out) || (reinterpret_cast<uintptr_t>(blocks) & 1u))
     return fail(CB200_E_INVALID_ARGUMENT, "%s: output must be 16-byte aligned and blocks 2-byte aligned", name);
-  return cuda_result(cb200::launch_dequantize_flat(qtype, out_dtype, blocks, out, k / 32, stream), name);
+  return cuda_result(cb200::launch_dequantize_flat(qtype, out_dtype, blocks, out, k / 8, stream), name);
 }
 
 int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, int64_t vocab, int32_t hidden,
@@ -223,7 +250,9 @@ int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, 
   if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
   int rc = check_lookup(name, qtable, ids, out, vocab, hidden, n_ids, id_dtype);
   if (rc != CB200_OK) return rc;
-  if (hidden % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by 32", name, hidden);
+  if (hidden % cb200::qblock_elems(qtype) != 0)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by %d", name, hidden,
+                cb200::qblock_elems(qtype));
   if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
     return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
                 (long long)vocab_end, (long long)vocab);
@@ -241,7 +270,7 @@ int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, 
   a.status = status;
   a.rows = n_ids;
   a.n = hidden;
-  a.row_bytes = hidden / 32 * cb200::qblock_bytes(qtype);
+  a.row_bytes = hidden / cb200::qblock_elems(qtype) * cb200::qblock_bytes(qtype);
   a.bulk = aligned16(qtable) && a.row_bytes % 16 == 0;
   if (2 * ((a.row_bytes + 15) & ~15) + 64 > 227 * 1024)
     return fail(CB200_E_UNSUPPORTED_SHAPE, "%s: hidden size %d exceeds the staged-row limit", name, hidden);
@@ -331,7 +360,9 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
   int rc = check_lookup(name, qtable, ids, y, vocab, hidden, n_ids, id_dtype);
   if (rc != CB200_OK) return rc;
-  if (hidden % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by 32", name, hidden);
+  if (hidden % cb200::qblock_elems(qtype) != 0)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by %d", name, hidden,
+                cb200::qblock_elems(qtype));
   if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
     return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
                 (long long)vocab_end, (long long)vocab);
@@ -367,7 +398,7 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   a.rows = n_ids;
   a.V = hidden / 8;
   a.n = hidden;
-  a.row_bytes = hidden / 32 * cb200::qblock_bytes(qtype);
+  a.row_bytes = hidden / cb200::qblock_elems(qtype) * cb200::qblock_bytes(qtype);
   a.bulk = aligned16(qtable) && a.row_bytes % 16 == 0;
   a.eps = eps;
   a.flags = flags;
@@ -384,7 +415,9 @@ static int owner_impl(const char* name, const void* qtable, int qtype, const voi
     return fail(CB200_E_INVALID_ARGUMENT, "%s: between 1 and 8 destinations are supported, got %d", name, n_dsts);
   int rc = check_lookup(name, qtable, ids, dsts[0], vocab, hidden, n_ids, id_dtype);
   if (rc != CB200_OK) return rc;
-  if (hidden % 32 != 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by 32", name, hidden);
+  if (hidden % cb200::qblock_elems(qtype) != 0)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by %d", name, hidden,
+                cb200::qblock_elems(qtype));
   if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
     return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
                 (long long)vocab_end, (long long)vocab);
@@ -423,7 +456,7 @@ static int owner_impl(const char* name, const void* qtable, int qtype, const voi
   a.rows = n_ids;
   a.V = hidden / 8;
   a.n = hidden;
-  a.row_bytes = hidden / 32 * cb200::qblock_bytes(qtype);
+  a.row_bytes = hidden / cb200::qblock_elems(qtype) * cb200::qblock_bytes(qtype);
   a.bulk = aligned16(qtable) && a.row_bytes % 16 == 0;
   a.eps = eps;
   a.flags = flags;

@@ -301,6 +301,24 @@ cudaError_t launch_qgather(int qtype, int out_dtype, const QGatherArgs& a, cudaS
   if (qtype == CB200_QTYPE_Q5_1) {
     CB200_QG(CB200_QTYPE_Q5_1)
   }
+  if (qtype == CB200_QTYPE_Q2K) {
+    CB200_QG(CB200_QTYPE_Q2K)
+  }
+  if (qtype == CB200_QTYPE_Q3K) {
+    CB200_QG(CB200_QTYPE_Q3K)
+  }
+  if (qtype == CB200_QTYPE_Q4K) {
+    CB200_QG(CB200_QTYPE_Q4K)
+  }
+  if (qtype == CB200_QTYPE_Q5K) {
+    CB200_QG(CB200_QTYPE_Q5K)
+  }
+  if (qtype == CB200_QTYPE_Q6K) {
+    CB200_QG(CB200_QTYPE_Q6K)
+  }
+  if (qtype == CB200_QTYPE_Q8K) {
+    CB200_QG(CB200_QTYPE_Q8K)
+  }
   CB200_QG(CB200_QTYPE_Q4_0)
 #undef CB200_QG
 }
@@ -313,18 +331,18 @@ __global__ void __launch_bounds__(256) dequantize_flat_kernel(const unsigned cha
                                                               void* __restrict__ out, int64_t n_vec) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec; v += stride) {
-    const unsigned char* blk = blocks + (v >> 2) * QBlock<QT>::kBytes;
+    constexpr int kVecs = qblock_elems(QT) / 8;  // 8-element groups per block
+    const unsigned char* blk = blocks + (v / kVecs) * QBlock<QT>::kBytes;
     float f[8];
-    decode8<QT>(blk, static_cast<int>(v & 3), f);
+    decode8<QT>(blk, static_cast<int>(v % kVecs), f);
     // element offset 8v: express as a row of one vector
     unsigned char* o = static_cast<unsigned char*>(out) + static_cast<size_t>(v) * 8 * Elem<DT>::kBytes;
     store_decoded<DT>(o, 0, f);
   }
 }
 
-cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks, void* out, int64_t n_blocks,
+cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks, void* out, int64_t n_vec,
                                    cudaStream_t stream) {
-  const int64_t n_vec = n_blocks * 4;
   if (n_vec == 0) return cudaSuccess;
   int64_t grid = (n_vec + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
@@ -350,6 +368,18 @@ cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks,
     CB200_DQ(CB200_QTYPE_Q5_0)
   } else if (qtype == CB200_QTYPE_Q5_1) {
     CB200_DQ(CB200_QTYPE_Q5_1)
+  } else if (qtype == CB200_QTYPE_Q2K) {
+    CB200_DQ(CB200_QTYPE_Q2K)
+  } else if (qtype == CB200_QTYPE_Q3K) {
+    CB200_DQ(CB200_QTYPE_Q3K)
+  } else if (qtype == CB200_QTYPE_Q4K) {
+    CB200_DQ(CB200_QTYPE_Q4K)
+  } else if (qtype == CB200_QTYPE_Q5K) {
+    CB200_DQ(CB200_QTYPE_Q5K)
+  } else if (qtype == CB200_QTYPE_Q6K) {
+    CB200_DQ(CB200_QTYPE_Q6K)
+  } else if (qtype == CB200_QTYPE_Q8K) {
+    CB200_DQ(CB200_QTYPE_Q8K)
   } else {
     CB200_DQ(CB200_QTYPE_Q4_0)
   }

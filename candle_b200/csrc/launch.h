@@ -67,6 +67,12 @@ cudaError_t launch_norm_generic(int dtype, int op, const LaneRowArgs& a, cudaStr
 cudaError_t launch_norm_slow(int dtype, const void* x, const void* weight, const void* bias, void* y, int64_t rows,
                              int n, float eps, int remove_mean, cudaStream_t stream);
 
+// softmax over the last dimension and rotary embeddings (neighbours.cu).  rope variants: 0 rope_i
+// (interleaved pairs, src [b, h, t, d]), 1 rope (half-split pairs, [b, h, t, d]), 2 rope_thd ([b, t, h, d]).
+cudaError_t launch_softmax_last_dim(int dtype, const void* x, void* y, int64_t rows, int n, cudaStream_t stream);
+cudaError_t launch_rope(int variant, int dtype, const void* src, const void* cos_, const void* sin_, void* dst, int64_t b,
+                        int h, int t, int d, cudaStream_t stream);
+
 // Row gathers (embedding.cu)
 struct GatherArgs {
   const unsigned char* src;  // [left, src_dim, row_bytes]
@@ -94,7 +100,7 @@ struct QGatherArgs {
   WaitTuning wt;  // filled by the launcher
 };
 cudaError_t launch_qgather(int qtype, int out_dtype, const QGatherArgs& a, cudaStream_t stream);
-cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks, void* out, int64_t n_blocks,
-                                   cudaStream_t stream);
+cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks, void* out, int64_t n_vec,
+                                   cudaStream_t stream);  // n_vec: groups of 8 elements
 
 }  // namespace cb200

@@ -17,6 +17,18 @@
 // sign of zero: the integer is converted to float first and multiplied by d, exactly as the CPU
 // does, instead of the d*q + (-8d) form of the reference's CUDA kernel.
 // Blocks are only 2-byte aligned inside a row, hence the 16-bit loads.
+//
+// K-quant super-blocks of 256 elements (k_quants.rs:96-154; decoders :834-871, 1095-1149, 1313-1342,
+// 1528-1563, 1716-1746, 1827-1839):
+//   BlockQ2K { scales: [u8; 16], qs: [u8; 64], d, dmin: f16 }                     84 bytes
+//   BlockQ3K { hmask: [u8; 32], qs: [u8; 64], scales: [u8; 12], d: f16 }         110 bytes
+//   BlockQ4K { d, dmin: f16, scales: [u8; 12], qs: [u8; 128] }                   144 bytes
+//   BlockQ5K { d, dmin: f16, scales: [u8; 12], qh: [u8; 32], qs: [u8; 128] }     176 bytes
+//   BlockQ6K { ql: [u8; 128], qh: [u8; 64], scales: [i8; 16], d: f16 }           210 bytes
+//   BlockQ8K { d: f32, qs: [i8; 256], bsums: [i16; 16] }                         292 bytes
+// Their values are NOT exact products: y = (d * sc) * q - (dmin * m) and the like round two or three
+// times in f32, so the decoders below perform the same operations in the same order with
+// __fmul_rn / __fsub_rn (no fused multiply-add).
 #pragma once
 
 #include "common.cuh"
@@ -46,6 +58,31 @@ struct QBlock<CB200_QTYPE_Q5_1> {
   static constexpr int kBytes = 24;
 };
 
+template <>
+struct QBlock<CB200_QTYPE_Q2K> {
+  static constexpr int kBytes = 84;
+};
+template <>
+struct QBlock<CB200_QTYPE_Q3K> {
+  static constexpr int kBytes = 110;
+};
+template <>
+struct QBlock<CB200_QTYPE_Q4K> {
+  static constexpr int kBytes = 144;
+};
+template <>
+struct QBlock<CB200_QTYPE_Q5K> {
+  static constexpr int kBytes = 176;
+};
+template <>
+struct QBlock<CB200_QTYPE_Q6K> {
+  static constexpr int kBytes = 210;
+};
+template <>
+struct QBlock<CB200_QTYPE_Q8K> {
+  static constexpr int kBytes = 292;
+};
+
 // Internal pseudo-format: rows that already hold 16-bit elements of the output type (a dense f16 /
 // bf16 table).  It lets the row-slot kernel, with its ring of bulk-copied rows, serve dense tables:
 // a "block" is 32 elements = 64 bytes and decoding is a plain 16-byte load.  Never part of the ABI.
@@ -67,8 +104,108 @@ __host__ __device__ inline int qblock_bytes(int qtype) {
       return 24;
     case CB200_QTYPE_Q8_0:
       return 34;
+    case CB200_QTYPE_Q2K:
+      return 84;
+    case CB200_QTYPE_Q3K:
+      return 110;
+    case CB200_QTYPE_Q4K:
+      return 144;
+    case CB200_QTYPE_Q5K:
+      return 176;
+    case CB200_QTYPE_Q6K:
+      return 210;
+    case CB200_QTYPE_Q8K:
+      return 292;
     default:
       return 0;
+  }
+}
+
+// Elements per block: 256 for the K-quant super-blocks, 32 for the others.
+__host__ __device__ constexpr bool is_kquant(int qtype) { return qtype >= CB200_QTYPE_Q2K && qtype <= CB200_QTYPE_Q8K; }
+__host__ __device__ constexpr int qblock_elems(int qtype) { return is_kquant(qtype) ? 256 : 32; }
+
+__device__ __forceinline__ float half_at(const unsigned char* p) {
+  return __half2float(*reinterpret_cast<const __half*>(p));
+}
+
+// The 6-bit (scale, min) pair j of a Q4K / Q5K block (get_scale_min_k4, quantized/utils.rs:49-59).
+__device__ __forceinline__ void scale_min_k4(int j, const unsigned char* q, float& sc, float& mn) {
+  int d, m;
+  if (j < 4) {
+    d = q[j] & 63;
+    m = q[j + 4] & 63;
+  } else {
+    d = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+    m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+  }
+  sc = static_cast<float>(d);
+  mn = static_cast<float>(m);
+}
+
+// Elements [8s, 8s+8) of ONE super-block `b` (s = 0..31), with candle's operation order.
+template <int QT>
+__device__ __forceinline__ void decode8_kquant(const unsigned char* b, int s, float (&out)[8]) {
+  const int e0 = 8 * s;
+  if constexpr (QT == CB200_QTYPE_Q4K || QT == CB200_QTYPE_Q5K) {
+    constexpr bool kFive = QT == CB200_QTYPE_Q5K;
+    const float d = half_at(b), dmin = half_at(b + 2);
+    const int g = e0 >> 6, idx = e0 & 63, hi = idx >> 5, l0 = idx & 31;
+    float sc, mn;
+    scale_min_k4(2 * g + hi, b + 4, sc, mn);
+    const float dl = __fmul_rn(d, sc), ml = __fmul_rn(dmin, mn);
+    const unsigned char* q = b + (kFive ? 48 : 16) + 32 * g + l0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int v = hi ? (q[i] >> 4) : (q[i] & 0xF);
+      if (kFive) v += ((b[16 + l0 + i] >> (2 * g + hi)) & 1) << 4;
+      out[i] = __fsub_rn(__fmul_rn(dl, static_cast<float>(v)), ml);
+    }
+  } else if constexpr (QT == CB200_QTYPE_Q6K) {
+    const float d = half_at(b + 208);
+    const int n = e0 >> 7, r = e0 & 127, j = r >> 5, l0 = r & 31, is = l0 >> 4;
+    const unsigned char* ql = b + 64 * n + ((j & 1) ? 32 : 0) + l0;
+    const unsigned char* qh = b + 128 + 32 * n + l0;
+    const float sc = static_cast<float>(static_cast<signed char>(b[192 + 8 * n + is + 2 * j]));
+    const float ds = __fmul_rn(d, sc);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int lo = (j & 2) ? (ql[i] >> 4) : (ql[i] & 0xF);
+      const int v = (lo | (((qh[i] >> (2 * j)) & 3) << 4)) - 32;
+      out[i] = __fmul_rn(ds, static_cast<float>(v));
+    }
+  } else if constexpr (QT == CB200_QTYPE_Q8K) {
+    // d is an f32 at a 2-byte aligned address: read it as two halves
+    const uint16_t* d16 = reinterpret_cast<const uint16_t*>(b);
+    const float d = __uint_as_float(static_cast<uint32_t>(d16[0]) | (static_cast<uint32_t>(d16[1]) << 16));
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      out[i] = __fmul_rn(d, static_cast<float>(static_cast<signed char>(b[4 + e0 + i])));
+  } else if constexpr (QT == CB200_QTYPE_Q2K) {
+    const float d = half_at(b + 80), dmin = half_at(b + 82);
+    const int n = e0 >> 7, r = e0 & 127, j = r >> 5, half = (r & 31) >> 4, l0 = r & 15;
+    const int sc = b[8 * n + 2 * j + half];
+    const float dl = __fmul_rn(d, static_cast<float>(sc & 0xF)), ml = __fmul_rn(dmin, static_cast<float>(sc >> 4));
+    const unsigned char* q = b + 16 + 32 * n + 16 * half + l0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      out[i] = __fsub_rn(__fmul_rn(dl, static_cast<float>((q[i] >> (2 * j)) & 3)), ml);
+  } else {  // Q3K
+    const float d_all = half_at(b + 108);
+    const int n = e0 >> 7, r = e0 & 127, j = r >> 5, half = (r & 31) >> 4, l0 = r & 15;
+    const int js = 8 * n + 2 * j + half;  // which of the sixteen 6-bit scales
+    const unsigned char* s12 = b + 96;
+    const int lo = js < 8 ? (s12[js] & 0xF) : (s12[js - 8] >> 4);
+    const int sc = (lo | (((s12[8 + (js & 3)] >> (2 * (js >> 2))) & 3) << 4)) - 32;
+    const float dl = __fmul_rn(d_all, static_cast<float>(sc));
+    const unsigned char* q = b + 32 + 32 * n + 16 * half + l0;
+    const unsigned char* hm = b + 16 * half + l0;
+    const int mbit = 4 * n + j;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int v = ((q[i] >> (2 * j)) & 3) - (((hm[i] >> mbit) & 1) ? 0 : 4);
+      out[i] = __fmul_rn(dl, static_cast<float>(v));
+    }
   }
 }
 
@@ -84,6 +221,11 @@ __device__ __forceinline__ float byte_to_float(uint32_t w, float magic_plus_bias
 // `scale`, when given, receives the block's scale d.
 template <int QT>
 __device__ __forceinline__ void decode8(const unsigned char* row, int v, float (&out)[8], float* scale = nullptr) {
+  if constexpr (is_kquant(QT)) {
+    if (scale != nullptr) *scale = 1.0f;
+    decode8_kquant<QT>(row + (v >> 5) * QBlock<QT>::kBytes, v & 31, out);
+    return;
+  }
   constexpr bool kHasMin = QT == CB200_QTYPE_Q4_1 || QT == CB200_QTYPE_Q5_1;
   constexpr bool kFiveBits = QT == CB200_QTYPE_Q5_0 || QT == CB200_QTYPE_Q5_1;
   constexpr int kQsOffset = 2 + (kHasMin ? 2 : 0) + (kFiveBits ? 4 : 0);

@@ -326,3 +326,75 @@ def qembedding_rms_norm_row_owner(qtensor, ids: torch.Tensor, alpha: torch.Tenso
                ctypes.cast(arr, ctypes.c_void_p), len(ptrs), ctypes.cast(barr, ctypes.c_void_p), vocab, hidden,
                flat.shape[0], float(eps), _DTYPES[alpha.dtype], _ID_DTYPES[flat.dtype], begin, end, flags, _ptr(status),
                _stream(alpha))
+
+
+def softmax_last_dim(xs: torch.Tensor) -> torch.Tensor:
+    """``candle_nn::ops::softmax_last_dim`` (candle-nn/src/ops.rs:289-435)."""
+    if xs.dtype not in _DTYPES:
+        raise CandleError(f"unsupported dtype for softmax {_DTYPE_NAMES.get(xs.dtype, xs.dtype)}")
+    if not xs.is_contiguous():
+        raise CandleError("input has to be contiguous")
+    _same_device(xs)
+    if xs.dim() == 0:
+        raise CandleError("unexpected rank, expected: at least 1, got: 0")
+    cols = xs.shape[-1]
+    rows = xs.numel() // cols if cols else 0
+    y = torch.empty_like(xs)
+    _cabi.call("cb200_softmax_last_dim", _ptr(xs), _ptr(y), rows, cols, _DTYPES[xs.dtype], _stream(xs))
+    return y
+
+
+def _rope(variant: int, name: str, xs: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    # the checks of rotary_emb.rs:203-228 (rope_i), 457-482 (rope), 706-731 (rope_thd)
+    if xs.dim() != 4:
+        raise CandleError(f"unexpected rank, expected: 4, got: {xs.dim()} ({_dims(xs)})")
+    if cos.dim() != 2 or sin.dim() != 2:
+        bad = cos if cos.dim() != 2 else sin
+        raise CandleError(f"unexpected rank, expected: 2, got: {bad.dim()} ({_dims(bad)})")
+    if variant == _cabi.ROPE_THD:
+        b, seq_len, h, n_embd = xs.shape
+    else:
+        b, h, seq_len, n_embd = xs.shape
+    if cos.shape[1] * 2 != n_embd or sin.shape[1] * 2 != n_embd or seq_len > cos.shape[0] or seq_len > sin.shape[0]:
+        raise CandleError(f"inconsistent last dim size in rope {_dims(xs)} {_dims(cos)} {_dims(sin)}")
+    if not xs.is_contiguous():
+        raise CandleError("xs has to be contiguous in rope")
+    if not cos.is_contiguous():
+        raise CandleError("cos has to be contiguous in rope")
+    if not sin.is_contiguous():
+        raise CandleError("sin has to be contiguous in rope")
+    if xs.dtype not in _DTYPES or cos.dtype != xs.dtype or sin.dtype != xs.dtype:
+        raise CandleError(f"unsupported dtype for rope {xs.dtype} {cos.dtype} {sin.dtype}")
+    _same_device(xs, cos, sin)
+    dst = torch.empty_like(xs)
+    _cabi.call("cb200_rope", _ptr(xs), _ptr(cos), _ptr(sin), _ptr(dst), b, h, seq_len, n_embd, _DTYPES[xs.dtype], variant,
+               _stream(xs))
+    return dst
+
+
+def rope_i(xs: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``candle_nn::rotary_emb::rope_i``: interleaved pairs, ``xs`` is ``[b, h, t, d]``."""
+    return _rope(_cabi.ROPE_INTERLEAVED, "rope-i", xs, cos, sin)
+
+
+def rope(xs: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``candle_nn::rotary_emb::rope``: pairs ``(x[k], x[k + d/2])``, ``xs`` is ``[b, h, t, d]``."""
+    return _rope(_cabi.ROPE_HALF, "rope", xs, cos, sin)
+
+
+def rope_thd(xs: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``candle_nn::rotary_emb::rope_thd``: as ``rope`` for ``xs`` laid out ``[b, t, h, d]``."""
+    return _rope(_cabi.ROPE_THD, "rope-thd", xs, cos, sin)
+
+
+def rms_norm_rows(xs: torch.Tensor, rows: torch.Tensor, alpha: torch.Tensor, eps: float, *, check: bool = True,
+                  status: torch.Tensor | None = None) -> torch.Tensor:
+    """RMS norm of the selected rows only: ``rms_norm(xs, alpha, eps).index_select(rows, 0)`` without
+    normalising the rows nobody reads.  The final norm of a decoder is followed by a slice that keeps
+    the last token of each sequence (candle-transformers/src/models/quantized_llama.rs:507-508: norm of
+    all rows, then ``x.i((.., seq_len - 1, ..))``); with ``rows`` = those positions in the flattened
+    ``[b * t, hidden]`` activations this reads and writes ``b`` rows instead of ``b * t``.  Rows are
+    independent, so the values are the same."""
+    if xs.dim() != 2:
+        raise CandleError(f"unexpected rank, expected: 2, got: {xs.dim()} ({_dims(xs)})")
+    return embedding_rms_norm(xs, rows, alpha, eps, check=check, status=status)

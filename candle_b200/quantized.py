@@ -1,5 +1,5 @@
 """The slice of ``candle_core::quantized`` the lookup path needs: a ``QTensor`` of 32-element
-blocks (Q4_0, Q4_1, Q5_0, Q5_1, Q8_0) resident on the GPU (candle-core/src/quantized/mod.rs:35-38, quantized/cuda.rs:9-20) with
+blocks (Q4_0, Q4_1, Q5_0, Q5_1, Q8_0) or 256-element K-quant super-blocks (Q2K .. Q8K) resident on the GPU (candle-core/src/quantized/mod.rs:35-38, quantized/cuda.rs:9-20) with
 ``dequantize`` / ``dequantize_f16`` (mod.rs:361-382) and a row lookup."""
 from __future__ import annotations
 
@@ -13,21 +13,28 @@ from .ops import _DTYPES, _ID_DTYPES, _ids_checks, _ptr, _same_device, _stream, 
 
 
 class GgmlDType(enum.Enum):
-    """ggml type ids (candle-core/src/quantized/mod.rs:152-171): the 32-element block formats."""
+    """ggml type ids (candle-core/src/quantized/mod.rs:152-171) with ``block_size`` / ``type_size`` as in
+    ``GgmlDType::block_size`` / ``type_size`` (mod.rs:210-252)."""
 
     Q4_0 = _cabi.QTYPE_Q4_0
     Q4_1 = _cabi.QTYPE_Q4_1
     Q5_0 = _cabi.QTYPE_Q5_0
     Q5_1 = _cabi.QTYPE_Q5_1
     Q8_0 = _cabi.QTYPE_Q8_0
+    Q2K = _cabi.QTYPE_Q2K
+    Q3K = _cabi.QTYPE_Q3K
+    Q4K = _cabi.QTYPE_Q4K
+    Q5K = _cabi.QTYPE_Q5K
+    Q6K = _cabi.QTYPE_Q6K
+    Q8K = _cabi.QTYPE_Q8K
 
     @property
     def block_size(self) -> int:
-        return 32
+        return 256 if self.value >= 10 else 32
 
     @property
     def type_size(self) -> int:
-        return {2: 18, 3: 20, 6: 22, 7: 24, 8: 34}[self.value]
+        return {2: 18, 3: 20, 6: 22, 7: 24, 8: 34, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210, 15: 292}[self.value]
 
 
 class QTensor:

@@ -53,13 +53,21 @@ extern "C" {
 #define CB200_ID_I64 2
 
 /* Block formats: ggml type ids as in candle-core/src/quantized/mod.rs:152-171.  Q4_0 and Q8_0 are
- * accepted everywhere; Q4_1, Q5_0 and Q5_1 by cb200_dequantize and cb200_qembedding, and by
- * cb200_qembedding_rms_norm through its two-launch route. */
+ * accepted everywhere; Q4_1, Q5_0, Q5_1 and the K-quant super-blocks of 256 elements (Q2K .. Q8K,
+ * candle-core/src/quantized/k_quants.rs:96-154) by cb200_dequantize and cb200_qembedding, and by
+ * cb200_qembedding_rms_norm through its two-launch route.  A row must be a whole number of blocks:
+ * hidden % 32 == 0, hidden % 256 == 0 for the K-quants. */
 #define CB200_QTYPE_Q4_0 2
 #define CB200_QTYPE_Q4_1 3
 #define CB200_QTYPE_Q5_0 6
 #define CB200_QTYPE_Q5_1 7
 #define CB200_QTYPE_Q8_0 8
+#define CB200_QTYPE_Q2K 10
+#define CB200_QTYPE_Q3K 11
+#define CB200_QTYPE_Q4K 12
+#define CB200_QTYPE_Q5K 13
+#define CB200_QTYPE_Q6K 14
+#define CB200_QTYPE_Q8K 15
 
 /* flags */
 #define CB200_FLAG_FAST_SUM 1 /* tree-order row sums: faster for some shapes, NOT bit-faithful */
@@ -153,6 +161,36 @@ CB200_API int cb200_layer_norm_slow(const void* x, const void* weight, const voi
                           int32_t cols, float eps, int dtype, int remove_mean, cb200_stream_t stream);
 
 /*
+ * softmax over the last dimension: y[r, :] = exp(x[r, :] - max(x[r, :])) / sum(...), x and y
+ * [rows, cols] contiguous, y not aliasing x.  Replaces SoftmaxLastDim::cuda_fwd
+ * (candle-nn/src/ops.rs:335-386, kernel `softmax_*` of candle-kernels/src/reduce.cu:177-219) with the
+ * arithmetic of its cpu_fwd (:296-333): everything in T, the row sum in candle's CPU order -- the
+ * AVX-ordered vec_sum for f32, one T-rounded addition per element for f16 / bf16.  exp follows the
+ * correctly rounded value where candle calls the platform's expf; the two agree except in the rare
+ * cases where that libm does not round correctly.
+ */
+CB200_API int cb200_softmax_last_dim(const void* x, void* y, int64_t rows, int32_t cols, int dtype,
+                                     cb200_stream_t stream);
+
+/*
+ * Rotary embeddings (candle-nn/src/rotary_emb.rs), all three fused forms, computed in T with every
+ * product and the final sum / difference rounded separately as on the CPU (rotary_emb.rs:47-60,
+ * 288-305, 540-558); replaces the kernels `rope_i_*`, `rope_*`, `rope_thd_*` of
+ * candle-kernels/src/reduce.cu:221-278:
+ *   CB200_ROPE_INTERLEAVED  rope_i    src [b, h, t, d], pairs (x[2k], x[2k+1])
+ *   CB200_ROPE_HALF         rope      src [b, h, t, d], pairs (x[k], x[k + d/2])
+ *   CB200_ROPE_THD          rope_thd  src [b, t, h, d], pairs (x[k], x[k + d/2])
+ *   y1 = x1 * cos[t, k] - x2 * sin[t, k];  y2 = x1 * sin[t, k] + x2 * cos[t, k]
+ * cos and sin are [>= t, d/2] contiguous, of the same dtype as src; dst has the shape of src and does
+ * not alias it.
+ */
+#define CB200_ROPE_INTERLEAVED 0
+#define CB200_ROPE_HALF 1
+#define CB200_ROPE_THD 2
+CB200_API int cb200_rope(const void* src, const void* cos, const void* sin, void* dst, int64_t b, int32_t h, int32_t t,
+                         int32_t d, int dtype, int variant, cb200_stream_t stream);
+
+/*
  * Self-test hook, not for production use: with `enable` != 0 every later launch of a kernel that
  * waits for bulk copies polls only a few dozen times and expects 16 bytes more than its copies
  * deliver, so every such wait runs out, the kernel records CB200_STATUS_WAIT_TIMEOUT, lets the
@@ -184,18 +222,20 @@ CB200_API int cb200_embedding(const void* table, const void* ids, void* out, int
                     int64_t n_ids, int dtype, int id_dtype, cb200_status* status, cb200_stream_t stream);
 
 /*
- * Whole-buffer block decode: k elements (k % 32 == 0) of Q4_0 / Q8_0 blocks -> out_dtype.
+ * Whole-buffer block decode: k elements (a whole number of blocks) of any supported format -> out_dtype.
  * Replaces QCudaStorage::dequantize / dequantize_f16 (candle-core/src/quantized/cuda.rs:69-124,
  * 391-414; kernels `dequantize_block_q{4,8}_0_{f32,f16}` of candle-kernels/src/quantized.cu:
  * 779-805, 1068-1091) and, for bf16 / f16 output, the cast kernel that follows it
  * (candle-kernels/src/cast.cu:4-25).  Values equal GgmlType::to_float on the CPU
- * (candle-core/src/quantized/k_quants.rs:163-183, 568-584) including the sign of zero.
+ * (candle-core/src/quantized/k_quants.rs:163-183, 568-584; K-quants :834-871, 1095-1149, 1313-1342,
+ * 1528-1563, 1716-1746, 1827-1839; CUDA twins candle-kernels/src/quantized.cu:807-1066) including
+ * the sign of zero and, for the formats whose decode rounds more than once, the operation order.
  */
 CB200_API int cb200_dequantize(const void* blocks, int qtype, void* out, int64_t k, int out_dtype,
                      cb200_stream_t stream);
 
 /*
- * Row lookup straight out of a block-quantised [vocab, hidden] table (hidden % 32 == 0):
+ * Row lookup straight out of a block-quantised [vocab, hidden] table (hidden a whole number of blocks):
  *   out[i, :] = T(to_float(qtable[ids[i], :]))
  * i.e. what QTensor::dequantize + to_dtype + Embedding::forward compute
  * (candle-transformers/src/models/quantized_llama.rs:378-379, candle-nn/src/embedding.rs:29-36)

@@ -19,9 +19,17 @@ _LIB_PATH = os.path.join(_HERE, "_build", "libcandle_cpu_oracle.so")
 
 DTYPES = {"f32": 0, "f16": 1, "bf16": 2}
 ID_DTYPES = {np.dtype(np.uint8): 0, np.dtype(np.uint32): 1, np.dtype(np.int64): 2}
-QTYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8}  # ggml type ids
-BLOCK_BYTES = {"q4_0": 18, "q4_1": 20, "q5_0": 22, "q5_1": 24, "q8_0": 34}
+QTYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8,
+          "q2k": 10, "q3k": 11, "q4k": 12, "q5k": 13, "q6k": 14, "q8k": 15}  # ggml type ids
+BLOCK_BYTES = {"q4_0": 18, "q4_1": 20, "q5_0": 22, "q5_1": 24, "q8_0": 34,
+               "q2k": 84, "q3k": 110, "q4k": 144, "q5k": 176, "q6k": 210, "q8k": 292}
 QK = 32
+QK_K = 256
+
+
+def block_elems(qtype: str) -> int:
+    """Elements per block: 256 for the K-quant super-blocks, 32 otherwise."""
+    return QK_K if qtype.endswith("k") else QK
 
 
 class InvalidIndex(IndexError):
@@ -34,8 +42,8 @@ class InvalidIndex(IndexError):
 
 def build(force: bool = False) -> str:
     """Compile the oracle with the committed Makefile; returns the path of the shared library."""
-    src = os.path.join(_HERE, "candle_cpu_oracle.c")
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, f) for f in ("candle_cpu_oracle.c", "candle_cpu_kquants.h", "Makefile")]
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < max(os.path.getmtime(f) for f in srcs):
         subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True)
     return _LIB_PATH
 
@@ -61,6 +69,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_norm_slow.argtypes = [ci, vp, vp, vp, vp, i64, i64, ctypes.c_double, ci, ci]
         L.oracle_avx_vec_sum.argtypes = [vp, i64]
         L.oracle_avx_vec_sum.restype = f32
+        L.oracle_softmax_last_dim.argtypes = [ci, vp, vp, i64, i64, ci]
+        L.oracle_rope.argtypes = [ci, ci, vp, vp, vp, vp, i64, i64, i64, i64, ci]
         L.oracle_max_threads.restype = ci
         L.oracle_bf16_from_f32.argtypes = [f32]
         L.oracle_bf16_from_f32.restype = ctypes.c_uint16
@@ -171,6 +181,37 @@ def avx_vec_sum(row: np.ndarray) -> float:
     return float(lib().oracle_avx_vec_sum(_ptr(row), row.size))
 
 
+def softmax_last_dim(x: np.ndarray, dtype: str, threads: int = 0) -> np.ndarray:
+    """``candle_nn::ops::softmax_last_dim`` (candle-nn/src/ops.rs:289-435, CPU path)."""
+    x = _check(x, dtype, "x")
+    cols = x.shape[-1]
+    rows = x.size // cols if cols else 0
+    y = np.empty_like(x)
+    _rc(lib().oracle_softmax_last_dim(DTYPES[dtype], _ptr(x), _ptr(y), rows, cols, threads), "softmax_last_dim")
+    return y
+
+
+ROPE_VARIANTS = {"rope_i": 0, "rope": 1, "rope_thd": 2}
+
+
+def rope(variant: str, x: np.ndarray, cos: np.ndarray, sin: np.ndarray, dtype: str, threads: int = 0) -> np.ndarray:
+    """``candle_nn::rotary_emb::{rope_i, rope, rope_thd}`` (CPU paths).  ``x`` is ``[b, h, t, d]``
+    (``[b, t, h, d]`` for ``rope_thd``), ``cos`` / ``sin`` are ``[>= t, d / 2]``."""
+    x, cos, sin = _check(x, dtype, "x"), _check(cos, dtype, "cos"), _check(sin, dtype, "sin")
+    if x.ndim != 4:
+        raise ValueError("rope expects a rank-4 tensor")
+    if variant == "rope_thd":
+        b, t, h, d = x.shape
+    else:
+        b, h, t, d = x.shape
+    if cos.shape != sin.shape or cos.ndim != 2 or cos.shape[1] * 2 != d or cos.shape[0] < t:
+        raise ValueError(f"inconsistent last dim size in rope {x.shape} {cos.shape} {sin.shape}")
+    y = np.empty_like(x)
+    _rc(lib().oracle_rope(ROPE_VARIANTS[variant], DTYPES[dtype], _ptr(x), _ptr(cos), _ptr(sin), _ptr(y), b, h, t, d,
+                          threads), "rope")
+    return y
+
+
 def index_select(src: np.ndarray, ids: np.ndarray, dim: int = 0) -> np.ndarray:
     """``Tensor::index_select``: ids must be rank 1 (u8 / u32 / i64), may be a strided view."""
     src = np.ascontiguousarray(src)
@@ -204,22 +245,23 @@ def embedding(table: np.ndarray, ids: np.ndarray) -> np.ndarray:
 
 def quantize(x: np.ndarray, qtype: str) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)
-    if x.shape[-1] % QK:
-        raise ValueError(f"last dim {x.shape[-1]} is not divisible by {QK}")
-    nb = x.size // QK
-    out = np.empty(nb * BLOCK_BYTES[qtype], dtype=np.uint8)
+    be = block_elems(qtype)
+    if x.shape[-1] % be:
+        raise ValueError(f"last dim {x.shape[-1]} is not divisible by {be}")
+    nb = x.size // be
+    out = np.zeros(nb * BLOCK_BYTES[qtype], dtype=np.uint8)
     _rc(lib().oracle_quantize(QTYPES[qtype], _ptr(x), _ptr(out), x.size), "quantize")
-    return out.reshape(x.shape[:-1] + (x.shape[-1] // QK * BLOCK_BYTES[qtype],))
+    return out.reshape(x.shape[:-1] + (x.shape[-1] // be * BLOCK_BYTES[qtype],))
 
 
 def dequantize(blocks: np.ndarray, qtype: str, threads: int = 1) -> np.ndarray:
     """Raw block bytes ``[..., n_blocks * block_bytes]`` -> f32 ``[..., n_blocks * 32]``."""
     blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
-    bb = BLOCK_BYTES[qtype]
+    bb, be = BLOCK_BYTES[qtype], block_elems(qtype)
     if blocks.shape[-1] % bb:
         raise ValueError("byte length is not a whole number of blocks")
-    k = blocks.size // bb * QK
-    y = np.empty(blocks.shape[:-1] + (blocks.shape[-1] // bb * QK,), dtype=np.float32)
+    k = blocks.size // bb * be
+    y = np.empty(blocks.shape[:-1] + (blocks.shape[-1] // bb * be,), dtype=np.float32)
     _rc(lib().oracle_dequantize(QTYPES[qtype], _ptr(blocks), _ptr(y), k, threads), "dequantize")
     return y
 
@@ -228,7 +270,7 @@ def qembedding(qtable: np.ndarray, qtype: str, ids: np.ndarray, out_dtype: str, 
     """Rows ``ids`` of a quantised ``[vocab, hidden/32*block_bytes]`` byte table, decoded to ``out_dtype``."""
     qtable = np.ascontiguousarray(qtable, dtype=np.uint8)
     vocab = qtable.shape[0]
-    hidden = qtable.shape[1] // BLOCK_BYTES[qtype] * QK
+    hidden = qtable.shape[1] // BLOCK_BYTES[qtype] * block_elems(qtype)
     flat = np.ascontiguousarray(ids).reshape(-1)
     out = np.empty((flat.size, hidden), dtype=_np_dtype(out_dtype))
     bad = ctypes.c_int64(0)

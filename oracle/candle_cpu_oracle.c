@@ -6,8 +6,8 @@
  * Parity pinning: the restatement is checked against the golden vectors held by candle's own
  * tests (candle-nn/tests/ops.rs:55-125, candle-nn/tests/layer_norm.rs:11-55,
  * candle-nn/src/layer_norm.rs:7-28, candle-core/tests/tensor_tests.rs:817-896,
- * candle-core/tests/quantized_tests.rs:222-254).  candle pins only f32 norms, gather and the
- * Q4_0 quantise->dequantise round trip; bf16/f16 norm results and Q8_0 dequant values have no
+ * candle-core/tests/quantized_tests.rs:222-254, and for the K-quant super-blocks :437-716, see
+ * candle_cpu_kquants.h).  candle pins only f32 norms, gather and the quantise->dequantise round trips; bf16/f16 norm results and Q8_0 dequant values have no
  * golden vector in candle, so for those the oracle is "parity unpinned" by the reference and is
  * anchored on the restated `half` crate semantics (cross-checked against torch CPU casts).
  *
@@ -360,7 +360,17 @@ int oracle_index_select(int64_t elem_size, int id_dtype, const void* src, const 
 #define Q5_0_BYTES 22
 #define Q5_1_BYTES 24
 
+static inline uint32_t read_u32_le(const uint8_t* p) {
+  return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+}
+
+#include "candle_cpu_kquants.h"
+
+/* elements per block: 32 for the Q4_0 .. Q8_0 family, 256 for the K-quant super-blocks */
+int64_t oracle_block_elems(int qtype) { return kq_block_bytes(qtype) > 0 ? QK_K : QK; }
+
 int64_t oracle_block_bytes(int qtype) {
+  if (kq_block_bytes(qtype) > 0) return kq_block_bytes(qtype);
   if (qtype == ORACLE_Q4_0) return Q4_0_BYTES;
   if (qtype == ORACLE_Q8_0) return Q8_0_BYTES;
   if (qtype == ORACLE_Q4_1) return Q4_1_BYTES;
@@ -369,14 +379,11 @@ int64_t oracle_block_bytes(int qtype) {
   return ORACLE_E_DTYPE;
 }
 
-static inline uint32_t read_u32_le(const uint8_t* p) {
-  return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
-}
-
 /* GgmlType::to_float: Q4_0 k_quants.rs:163-183, Q8_0 k_quants.rs:568-584 (sequential in candle). */
 int oracle_dequantize(int qtype, const void* blocks, float* y, int64_t k, int threads) {
   int nt = resolve_threads(threads);
   (void)nt;
+  if (kq_block_bytes(qtype) > 0) return kq_dequantize(qtype, (const uint8_t*)blocks, y, k, nt);
   if (k % QK != 0) return ORACLE_E_SHAPE;
   int64_t nb = k / QK;
   const uint8_t* b = (const uint8_t*)blocks;
@@ -487,6 +494,7 @@ static inline int8_t sat_i8(float v) {
 }
 
 int oracle_quantize(int qtype, const float* x, void* blocks, int64_t k) {
+  if (kq_block_bytes(qtype) > 0) return kq_quantize(qtype, x, (uint8_t*)blocks, k);
   if (k % QK != 0) return ORACLE_E_SHAPE;
   int64_t nb = k / QK;
   uint8_t* b = (uint8_t*)blocks;
@@ -619,11 +627,12 @@ int oracle_qembedding(int qtype, int out_dtype, int id_dtype, const void* qtable
                       int threads) {
   int nt = resolve_threads(threads);
   (void)nt;
-  if (hidden % QK != 0) return ORACLE_E_SHAPE;
   int64_t bb = oracle_block_bytes(qtype);
   if (bb < 0) return ORACLE_E_DTYPE;
+  const int64_t be = oracle_block_elems(qtype);
+  if (hidden % be != 0) return ORACLE_E_SHAPE;
   if (out_dtype != ORACLE_F32 && out_dtype != ORACLE_F16 && out_dtype != ORACLE_BF16) return ORACLE_E_DTYPE;
-  int64_t row_bytes = hidden / QK * bb;
+  int64_t row_bytes = hidden / be * bb;
   for (int64_t i = 0; i < n_ids; i++) {
     uint64_t index;
     if (read_id(id_dtype, ids, i, &index)) return ORACLE_E_DTYPE;
@@ -635,19 +644,19 @@ int oracle_qembedding(int qtype, int out_dtype, int id_dtype, const void* qtable
   int rc = ORACLE_OK;
 #pragma omp parallel num_threads(nt) if (nt > 1)
   {
-    float* tmp = (float*)__builtin_alloca((size_t)QK * sizeof(float));
+    float* tmp = (float*)__builtin_alloca((size_t)QK_K * sizeof(float));
 #pragma omp for schedule(static)
     for (int64_t i = 0; i < n_ids; i++) {
       uint64_t index = 0;
       read_id(id_dtype, ids, i, &index);
       const uint8_t* row = (const uint8_t*)qtable + (size_t)index * row_bytes;
-      for (int64_t blk = 0; blk < hidden / QK; blk++) {
-        oracle_dequantize(qtype, row + blk * bb, tmp, QK, 1);
-        size_t o = (size_t)i * hidden + blk * QK;
+      for (int64_t blk = 0; blk < hidden / be; blk++) {
+        oracle_dequantize(qtype, row + blk * bb, tmp, be, 1);
+        size_t o = (size_t)i * hidden + blk * be;
         if (out_dtype == ORACLE_F32)
-          memcpy((float*)out + o, tmp, QK * sizeof(float));
+          memcpy((float*)out + o, tmp, be * sizeof(float));
         else
-          oracle_cast_from_f32(out_dtype, tmp, (uint16_t*)out + o, QK, 1);
+          oracle_cast_from_f32(out_dtype, tmp, (uint16_t*)out + o, be, 1);
       }
     }
   }
@@ -752,4 +761,115 @@ int oracle_norm_slow(int dtype, const void* x, const void* weight, const void* b
     if (xf != stack_buf) free(xf);
   }
   return rc;
+}
+
+/* ------------------------------------------------------------------------------------------------
+ * softmax over the last dimension: SoftmaxLastDim::cpu_fwd, candle-nn/src/ops.rs:296-333.  Per row
+ * (a rayon task), everything in T:
+ *   max = vec_reduce_max(row)                 (f32::max / half's max: a NaN operand is ignored)
+ *   d[i] = (x[i] - max).exp()                 (T subtraction; exp of half types = T(expf(f32(v))))
+ *   sum = vec_reduce_sum(d)                   (f32: the AVX-ordered vec_sum above; f16 / bf16: the
+ *                                              default `*res += x`, i.e. a T-rounded add per element,
+ *                                              candle-core/src/cpu/kernels.rs:26-31, 84-123)
+ *   d[i] /= sum                               (T division)
+ * expf is the platform's libm, as it is for candle (Rust's f32::exp calls it).
+ */
+#define SOFTMAX_ROW_HALF(TO_F32, FROM_F32)                                                   \
+  do {                                                                                       \
+    const uint16_t* src = (const uint16_t*)x + r * cols;                                     \
+    uint16_t* dst = (uint16_t*)y + r * cols;                                                 \
+    float max = TO_F32(src[0]);                                                              \
+    for (int64_t c = 1; c < cols; c++) max = fmaxf(max, TO_F32(src[c]));                     \
+    for (int64_t c = 0; c < cols; c++) {                                                     \
+      float dlt = TO_F32(FROM_F32(TO_F32(src[c]) - max));                                    \
+      dst[c] = FROM_F32(expf(dlt));                                                          \
+    }                                                                                        \
+    uint16_t sum = FROM_F32(0.0f);                                                           \
+    for (int64_t c = 0; c < cols; c++) sum = FROM_F32(TO_F32(sum) + TO_F32(dst[c]));         \
+    for (int64_t c = 0; c < cols; c++) dst[c] = FROM_F32(TO_F32(dst[c]) / TO_F32(sum));      \
+  } while (0)
+
+int oracle_softmax_last_dim(int dtype, const void* x, void* y, int64_t rows, int64_t cols, int threads) {
+  int nt = resolve_threads(threads);
+  (void)nt;
+  if (dtype != ORACLE_F32 && dtype != ORACLE_F16 && dtype != ORACLE_BF16) return ORACLE_E_DTYPE;
+  if (cols <= 0) return rows == 0 ? ORACLE_OK : ORACLE_E_SHAPE;
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+  for (int64_t r = 0; r < rows; r++) {
+    if (dtype == ORACLE_F32) {
+      const float* src = (const float*)x + r * cols;
+      float* dst = (float*)y + r * cols;
+      float max = src[0];
+      for (int64_t c = 1; c < cols; c++) max = fmaxf(max, src[c]);
+      for (int64_t c = 0; c < cols; c++) {
+        float dlt = src[c] - max;
+        dst[c] = expf(dlt);
+      }
+      float sum = avx_vec_sum(dst, cols);
+      for (int64_t c = 0; c < cols; c++) dst[c] = dst[c] / sum;
+    } else if (dtype == ORACLE_BF16) {
+      SOFTMAX_ROW_HALF(bf16_to_f32, bf16_from_f32);
+    } else {
+      SOFTMAX_ROW_HALF(f16_to_f32, f16_from_f32);
+    }
+  }
+  return ORACLE_OK;
+}
+
+/* ------------------------------------------------------------------------------------------------
+ * Rotary embeddings, the three fused forms of candle-nn/src/rotary_emb.rs, all arithmetic in T with
+ * every product and the sum / difference rounded separately (Rust never fuses them):
+ *   variant 0  rope_i   (:47-60)   src [b, h, t, d], pairs interleaved: (x[2k], x[2k+1]) with cos/sin[i_t, k]
+ *   variant 1  rope     (:288-305) src [b, h, t, d], pairs (x[k], x[k + d/2])
+ *   variant 2  rope_thd (:540-558) src [b, t, h, d], pairs (x[k], x[k + d/2])
+ *   y1 = x1 * cos - x2 * sin;  y2 = x1 * sin + x2 * cos;   cos, sin: [t, d/2] (more rows are allowed)
+ */
+#define ROPE_PAIR(LOAD, STORE, T)                                                    \
+  do {                                                                               \
+    const T* s = (const T*)src;                                                      \
+    T* o = (T*)dst;                                                                  \
+    float x1 = LOAD(s[i1]), x2 = LOAD(s[i2]);                                        \
+    float c = LOAD(((const T*)cos_)[ics]), sn = LOAD(((const T*)sin_)[ics]);         \
+    float p1 = LOAD(STORE(x1 * c)), p2 = LOAD(STORE(x2 * sn));                       \
+    float p3 = LOAD(STORE(x1 * sn)), p4 = LOAD(STORE(x2 * c));                       \
+    o[i1] = STORE(p1 - p2);                                                          \
+    o[i2] = STORE(p3 + p4);                                                          \
+  } while (0)
+
+int oracle_rope(int variant, int dtype, const void* src, const void* cos_, const void* sin_, void* dst, int64_t b,
+                int64_t h, int64_t t, int64_t d, int threads) {
+  int nt = resolve_threads(threads);
+  (void)nt;
+  if (dtype != ORACLE_F32 && dtype != ORACLE_F16 && dtype != ORACLE_BF16) return ORACLE_E_DTYPE;
+  if (variant < 0 || variant > 2 || d % 2 != 0) return ORACLE_E_SHAPE;
+  const int64_t outer = variant == 2 ? b : b * h; /* one rayon task per [t, d] (rope, rope_i) or [t, h, d] slab */
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+  for (int64_t ob = 0; ob < outer; ob++) {
+    const int64_t base = ob * (variant == 2 ? t * h * d : t * d);
+    for (int64_t it = 0; it < t; it++) {
+      for (int64_t id = 0; id < d / 2; id++) {
+        const int64_t ics = it * (d / 2) + id;
+        for (int64_t ih = 0; ih < (variant == 2 ? h : 1); ih++) {
+          int64_t i1, i2;
+          if (variant == 0) {
+            i1 = base + it * d + 2 * id;
+            i2 = i1 + 1;
+          } else if (variant == 1) {
+            i1 = base + it * d + id;
+            i2 = i1 + d / 2;
+          } else {
+            i1 = base + it * h * d + ih * d + id;
+            i2 = i1 + d / 2;
+          }
+          if (dtype == ORACLE_F32)
+            ROPE_PAIR(ID_F32, ID_F32, float);
+          else if (dtype == ORACLE_BF16)
+            ROPE_PAIR(bf16_to_f32, bf16_from_f32, uint16_t);
+          else
+            ROPE_PAIR(f16_to_f32, f16_from_f32, uint16_t);
+        }
+      }
+    }
+  }
+  return ORACLE_OK;
 }

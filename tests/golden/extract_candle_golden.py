@@ -92,6 +92,26 @@ def main(ref: str, dst: str) -> None:
             "distribution": "uniform[0,1)", "eps": 1e-5, "max_abs_fused_vs_slow": 1e-5,
         }
 
+    # softmax: the test takes log(data) and applies softmax over each dim; the last-dim values are the
+    # ones softmax_last_dim is checked against (third and fourth expected blocks, identical)
+    body, line = function_body(ops, "softmax")
+    lits = array_literals(body)
+    assert lits[3] == lits[4]
+    kats["softmax"] = {
+        "source": f"candle-nn/tests/ops.rs:{line}", "data": lits[0], "input": "log(data)",
+        "expected_dim0_round4": lits[1], "expected_dim1_round4": lits[2], "expected_last_dim_round4": lits[4],
+    }
+    body, line = function_body(ops, "softmax_numerical_stability")
+    lits = array_literals(body)
+    kats["softmax_numerical_stability"] = {"source": f"candle-nn/tests/ops.rs:{line}", "x": lits[0], "expected": lits[1]}
+    for name in ("ropei", "rope", "rope_thd"):
+        body, line = function_body(ops, name)
+        dims = re.search(r"=\s*\((\d+),\s*(\d+),\s*(\d+),\s*(\d+)\)", body)
+        kats[name] = {
+            "source": f"candle-nn/tests/ops.rs:{line}", "b_size_num_head_seq_len_head_dim": [int(g) for g in dims.groups()],
+            "distribution": "uniform[0,1) for src, cos and sin", "fused_vs_slow_sum_abs_diff": 0.0,
+        }
+
     ln = read("candle-nn/tests/layer_norm.rs")
     body, line = function_body(ln, "layer_norm")
     lits = array_literals(body)
@@ -151,6 +171,29 @@ def main(ref: str, dst: str) -> None:
             "source": f"candle-core/tests/quantized_tests.rs:{line}", "src": "0..128 as f32",
             "dequantized_rounded_3": [repr(float(v)) for v in vec],
             "rounding": "(1000 * x).round() / 1000 in f32, round half away from zero (round_vector)",
+        }
+
+    # K-quant super-blocks: a 1024-element ramp of bound 0.5 quantised and decoded again; candle checks
+    # six decoded values (rounded to 3 decimals), a max-abs error over the vector, the same for a ramp
+    # of bound 128, and an RMSE bound on the cosine vector of the ggml unit tests
+    consts = dict(re.findall(r"const (GGML_MAX_QUANTIZATION_TOTAL_ERROR\w*): f32 = ([0-9.]+);", qt))
+    test_size = re.search(r"const GGML_TEST_SIZE: usize = ([0-9* ]+);", qt).group(1)
+    for name in ("quantize_q2k", "quantize_q3k", "quantize_q4k", "quantize_q5k", "quantize_q6k", "quantize_q8k"):
+        body, line = function_body(qt, name)
+        lits = [l for l in array_literals(body) if len(l) == 6]
+        tols = [float(t) for t in re.findall(r"compare_with_error\([^;]*?,\s*([0-9.]+)\s*\)", body)]
+        vecs = re.findall(r"get_test_vector2\(([0-9.]+),\s*(\d+),", body)
+        rmse = re.search(r"ggml_quantization_error_test\(dtype, device, (\w+)\)", body).group(1)
+        kats[name] = {
+            "source": f"candle-core/tests/quantized_tests.rs:{line}",
+            "src": "get_test_vector2(bound, size): ((v - size/2) * bound) / (size/2) in f32, v in 0..size",
+            "bound": float(vecs[0][0]), "size": int(vecs[0][1]), "points": [0, 128, 256, 512, 800, 1023],
+            "src_points": [repr(float(v)) for v in lits[0]],
+            "dequantized_points_rounded_3": [repr(float(v)) for v in lits[1]],
+            "max_abs_error": tols[0], "big_bound": float(vecs[1][0]), "big_max_abs_error": tols[1],
+            "ggml_vector": f"0.1 + 2 cos(i) for i in 0..{eval(test_size)}", "ggml_size": eval(test_size),
+            "ggml_max_rmse": float(consts[rmse]),
+            "rmse": "sqrt(sum((a - b)^2)) / len",
         }
 
     with open(dst, "w") as f:

@@ -74,7 +74,9 @@ def test_argument_validation_needs_no_device(built_lib):
     assert lib.cb200_rms_norm(None, None, one, one, None, 4, 8, 1e-5, 0, 0, None) == -1
     assert lib.cb200_rms_norm(one, None, one, one, None, 0, 8, 1e-5, 0, 0, None) == 0  # nothing to do
     assert lib.cb200_layer_norm(one, None, one, None, one, None, 4, 8, 1e-5, 0, 0, None) == -1  # beta missing
-    assert lib.cb200_qembedding(one, 10, one, one, 10, 64, 4, 0, 1, 0, 10, None, None) == -2  # Q2K: no super-blocks here
+    assert lib.cb200_qembedding(one, 9, one, one, 10, 64, 4, 0, 1, 0, 10, None, None) == -2  # Q8_1 has no to_float
+    assert lib.cb200_qembedding(one, 12, one, one, 10, 64, 4, 0, 1, 0, 10, None, None) == -1  # Q4K: hidden % 256
+    assert b"not divisible by 256" in lib.cb200_last_error()
     assert lib.cb200_qembedding(one, 8, one, one, 10, 48, 4, 0, 1, 0, 10, None, None) == -1  # hidden % 32
     assert b"not divisible by 32" in lib.cb200_last_error()
     assert lib.cb200_qembedding(one, 8, one, one, 10, 64, 4, 0, 1, 5, 11, None, None) == -1  # shard outside vocab
