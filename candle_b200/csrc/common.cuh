@@ -289,6 +289,32 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// x / m, correctly rounded, for many x and one m.  With r = RN(1/m), q = RN(x r) is within one ulp
+// of the quotient, rem = x - q m is then exact in an FMA, and RN(q + rem r) is the correctly rounded
+// quotient (Markstein's theorem) -- three instructions instead of the full IEEE division sequence.
+// It needs every intermediate to be a normal number, so it is used for 2^-60 <= |x|, m <= 2^60 only;
+// anything else (zeros, tiny or huge values, NaN, infinity) takes the division instruction sequence.
+struct RowDivisor {
+  float m, r;
+  bool fast;
+};
+__device__ __forceinline__ RowDivisor make_row_divisor(float m) {
+  RowDivisor d;
+  d.m = m;
+  d.fast = (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
+  d.r = d.fast ? __frcp_rn(m) : 0.0f;
+  return d;
+}
+__device__ __forceinline__ float div_by_row(float x, const RowDivisor& d) {
+  const float ax = fabsf(x);
+  if (d.fast && ax >= 8.6736174e-19f && ax <= 1.1529215e18f) {
+    const float q = __fmul_rn(x, d.r);
+    const float rem = __fmaf_rn(-q, d.m, x);
+    return __fmaf_rn(rem, d.r, q);
+  }
+  return __fdiv_rn(x, d.m);
+}
+
 // The f32 pipeline candle applies to a row's sum of squares (candle-nn/src/ops.rs:491):
 // sqrt(sum2 / n + eps), every operation correctly rounded.
 __device__ __forceinline__ float rms_from_sum(float sum2, float n, float eps) {

@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const Lan
   for (int r = warp; r < live; r += kLaneRowWarps) {
     if (!valid[r]) continue;
     const float2 st = stats[r];
+    const RowDivisor dv = make_row_divisor(st.x);  // (used by the RMS norm only)
     const int64_t base = (row0 + r) * a.V;
     const uint4* row = reinterpret_cast<const uint4*>(rowbuf + static_cast<size_t>(r) * a.pitch);
     for (int v = lane; v < a.V; v += 32) {
@@ -212,7 +213,7 @@ __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const Lan
           o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), g[e]), b[e]);
       } else {
 #pragma unroll
-        for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), g[e]);
+        for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(div_by_row(h[e], dv)), g[e]);
       }
       stg_stream(gy + base + v, floats_to_vec<DT>(o));
       if (gg != nullptr) stg_stream(gg + base + v, hv);
@@ -308,6 +309,7 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
         } else {
           st = make_float2(round_to<DT>(rms_from_sum(sums.y, nf, a.eps)), 0.0f);
         }
+        const RowDivisor dv = make_row_divisor(st.x);  // (used by the RMS norm only)
 #pragma unroll
         for (int j = 0; j < VPL; ++j) {
           const int v = lane + 32 * j;
@@ -319,7 +321,7 @@ __global__ void __launch_bounds__(kShortThreads, 1) norm_shortrow_kernel(const L
               o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), gam[j][e]), bet[j][e]);
           } else {
 #pragma unroll
-            for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), gam[j][e]);
+            for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(div_by_row(h[e], dv)), gam[j][e]);
           }
           stg_stream(gy + (row0 + r) * V + v, floats_to_vec<DT>(o));
         }
@@ -526,6 +528,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
       } else {
         st = make_float2(round_to<DT>(rms_from_sum(sums.y, nf, a.eps)), 0.0f);  // ops.rs:491-492
       }
+      const RowDivisor dv = make_row_divisor(st.x);  // (used by the RMS norm only)
       const uint4* xr = gx + src * V;
       const uint4* rr = RES ? gr + row * V : nullptr;
       uint4* yr = gy + row * V;
@@ -567,7 +570,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) norm_stream_kernel(const La
               o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(h[e], st.x), st.y), g[e]), b[e]);
           } else {
 #pragma unroll
-            for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(__fdiv_rn(h[e], st.x)), g[e]);
+            for (int e = 0; e < PV; ++e) o[e] = __fmul_rn(round_to<DT>(div_by_row(h[e], dv)), g[e]);
           }
           stg_stream(yr + v, floats_to_vec<DT>(o));
           if (so != nullptr) stg_stream(so + v, hv[u]);
