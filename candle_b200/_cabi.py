@@ -33,6 +33,7 @@ SIGNATURES = {
     "cb200_qembedding_rms_norm_owner": [
         _vp, _int, _vp, _vp, _vp, _int, _i64, _i32, _i64, _f32, _int, _int, _i64, _i64, _int, _vp, _vp,
     ],
+    "cb200_qembedding_route_rows": [_vp, _int, _vp, _vp, _int, _vp, _i64, _i32, _i64, _int, _i64, _i64, _vp, _vp],
     "cb200_qembedding_rms_norm_row_owner": [
         _vp, _int, _vp, _vp, _vp, _int, _vp, _i64, _i32, _i64, _f32, _int, _int, _i64, _i64, _int, _vp, _vp,
     ],

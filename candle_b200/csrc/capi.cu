@@ -487,4 +487,40 @@ int cb200_qembedding_rms_norm_row_owner(const void* qtable, int qtype, const voi
                     id_dtype, vocab_begin, vocab_end, flags, status, stream);
 }
 
+int cb200_qembedding_route_rows(const void* qtable, int qtype, const void* ids, void* const* dsts, int n_dsts,
+                                const int64_t* row_bounds, int64_t vocab, int32_t hidden, int64_t n_ids, int id_dtype,
+                                int64_t vocab_begin, int64_t vocab_end, cb200_status* status, cb200_stream_t stream) {
+  const char* name = "cb200_qembedding_route_rows";
+  if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
+  if (dsts == nullptr || row_bounds == nullptr || n_dsts < 1 || n_dsts > 8)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: between 1 and 8 destinations with their row bounds are needed, got %d", name,
+                n_dsts);
+  int rc = check_lookup(name, qtable, ids, dsts[0], vocab, hidden, n_ids, id_dtype);
+  if (rc != CB200_OK) return rc;
+  if (hidden % cb200::qblock_elems(qtype) != 0)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: hidden size %d is not divisible by %d", name, hidden,
+                cb200::qblock_elems(qtype));
+  if (vocab_begin < 0 || vocab_end < vocab_begin || vocab_end > vocab)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: bad vocab shard [%lld, %lld) of %lld", name, (long long)vocab_begin,
+                (long long)vocab_end, (long long)vocab);
+  if (row_bounds[0] != 0 || row_bounds[n_dsts] != n_ids)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: row bounds must run from 0 to n_ids (%lld), got %lld .. %lld", name,
+                (long long)n_ids, (long long)row_bounds[0], (long long)row_bounds[n_dsts]);
+  for (int d = 0; d < n_dsts; ++d) {
+    if (row_bounds[d + 1] < row_bounds[d])
+      return fail(CB200_E_INVALID_ARGUMENT, "%s: row bounds must not decrease (entry %d)", name, d + 1);
+    if (dsts[d] == nullptr && row_bounds[d + 1] != row_bounds[d])
+      return fail(CB200_E_INVALID_ARGUMENT, "%s: destination %d is null", name, d);
+    if (reinterpret_cast<uintptr_t>(dsts[d]) & 1u)
+      return fail(CB200_E_INVALID_ARGUMENT, "%s: destination %d is not 2-byte aligned", name, d);
+  }
+  if (n_ids == 0 || hidden == 0) return CB200_OK;
+  if (reinterpret_cast<uintptr_t>(qtable) & 1u)
+    return fail(CB200_E_INVALID_ARGUMENT, "%s: the table must be 2-byte aligned", name);
+  const int row_bytes = hidden / cb200::qblock_elems(qtype) * cb200::qblock_bytes(qtype);
+  return cuda_result(cb200::launch_qroute_rows(static_cast<const unsigned char*>(qtable), ids, id_dtype, vocab, vocab_begin,
+                                               vocab_end, status, n_ids, row_bytes, dsts, n_dsts, row_bounds, stream),
+                     name);
+}
+
 }  // extern "C"

@@ -324,6 +324,93 @@ cudaError_t launch_qgather(int qtype, int out_dtype, const QGatherArgs& a, cudaS
 }
 
 // ---------------------------------------------------------------------------------------------
+// Routing of raw block rows for a vocabulary-sharded table whose consumers are row-sharded: the
+// rank that owns id[i] copies the QUANTISED row (a few KB instead of the decoded 2 * hidden bytes) into
+// the staging buffer of the rank whose block of token rows contains i, at row i - row_bounds[r].
+// One warp per token row, plain 16-byte loads and stores (peer memory is only ever stored to).
+// ---------------------------------------------------------------------------------------------
+struct QRouteArgs {
+  const unsigned char* qtable;  // rows [vocab_begin, vocab_end)
+  const void* ids;
+  int id_dtype;
+  int64_t vocab, vocab_begin, vocab_end;
+  cb200_status* status;
+  int64_t rows;
+  int row_bytes;
+  int n_dsts;
+  unsigned char* dsts[8];
+  int64_t row_bounds[9];
+};
+
+template <typename W>
+__global__ void __launch_bounds__(256) qroute_rows_kernel(const QRouteArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int units = a.row_bytes / static_cast<int>(sizeof(W));
+  constexpr int K = 8;  // units per lane in flight
+  for (int64_t i = warp; i < a.rows; i += n_warps) {
+    const uint64_t id = read_id(a.ids, a.id_dtype, i);
+    if (id >= static_cast<uint64_t>(a.vocab)) {
+      if (lane == 0) report_status(a.status, CB200_STATUS_INVALID_INDEX, i, static_cast<int64_t>(id), a.vocab);
+      continue;
+    }
+    if (id < static_cast<uint64_t>(a.vocab_begin) || id >= static_cast<uint64_t>(a.vocab_end)) continue;  // another rank's
+    int r = 0;
+#pragma unroll
+    for (int d = 1; d < 8; ++d)
+      if (d < a.n_dsts && i >= a.row_bounds[d]) r = d;
+    const W* src = reinterpret_cast<const W*>(a.qtable + (id - a.vocab_begin) * static_cast<uint64_t>(a.row_bytes));
+    W* dst = reinterpret_cast<W*>(a.dsts[r] + (i - a.row_bounds[r]) * static_cast<int64_t>(a.row_bytes));
+    for (int u0 = 0; u0 < units; u0 += 32 * K) {
+      W v[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int u = u0 + 32 * k + lane;
+        if (u < units) v[k] = src[u];
+      }
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int u = u0 + 32 * k + lane;
+        if (u < units) dst[u] = v[k];
+      }
+    }
+  }
+}
+
+cudaError_t launch_qroute_rows(const unsigned char* qtable, const void* ids, int id_dtype, int64_t vocab,
+                               int64_t vocab_begin, int64_t vocab_end, cb200_status* status, int64_t rows, int row_bytes,
+                               void* const* dsts, int n_dsts, const int64_t* row_bounds, cudaStream_t stream) {
+  if (rows == 0 || row_bytes == 0) return cudaSuccess;
+  QRouteArgs a{};
+  a.qtable = qtable;
+  a.ids = ids;
+  a.id_dtype = id_dtype;
+  a.vocab = vocab;
+  a.vocab_begin = vocab_begin;
+  a.vocab_end = vocab_end;
+  a.status = status;
+  a.rows = rows;
+  a.row_bytes = row_bytes;
+  a.n_dsts = n_dsts;
+  bool vec = (reinterpret_cast<uintptr_t>(qtable) & 15u) == 0 && row_bytes % 16 == 0;
+  for (int d = 0; d < n_dsts; ++d) {
+    a.dsts[d] = static_cast<unsigned char*>(dsts[d]);
+    a.row_bounds[d] = row_bounds[d];
+    vec = vec && (reinterpret_cast<uintptr_t>(dsts[d]) & 15u) == 0;
+  }
+  a.row_bounds[n_dsts] = row_bounds[n_dsts];
+  int64_t grid = (rows + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (grid > cap) grid = cap;
+  if (vec)
+    qroute_rows_kernel<uint4><<<static_cast<unsigned>(grid), 256, 0, stream>>>(a);
+  else
+    qroute_rows_kernel<uint16_t><<<static_cast<unsigned>(grid), 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // Whole-buffer decode (QTensor::dequantize): 8 elements per thread straight from global memory
 // ---------------------------------------------------------------------------------------------
 template <int QT, int DT>

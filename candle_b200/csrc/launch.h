@@ -100,6 +100,9 @@ struct QGatherArgs {
   WaitTuning wt;  // filled by the launcher
 };
 cudaError_t launch_qgather(int qtype, int out_dtype, const QGatherArgs& a, cudaStream_t stream);
+cudaError_t launch_qroute_rows(const unsigned char* qtable, const void* ids, int id_dtype, int64_t vocab,
+                               int64_t vocab_begin, int64_t vocab_end, cb200_status* status, int64_t rows, int row_bytes,
+                               void* const* dsts, int n_dsts, const int64_t* row_bounds, cudaStream_t stream);
 cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks, void* out, int64_t n_vec,
                                    cudaStream_t stream);  // n_vec: groups of 8 elements
 

@@ -302,10 +302,19 @@ __device__ __forceinline__ void decode_half_block(const unsigned char* row, int 
     const unsigned char* b = row + (p >> 1) * QBlock<QT>::kBytes;
     const float d = __half2float(*reinterpret_cast<const __half*>(b));
     scale = d;
-    const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + (QT == CB200_QTYPE_Q8_0 ? (p & 1) * 16 : 0));
+    // The sixteen quant bytes start 2 bytes into a block of 18 or 34 bytes, so they are 4-byte aligned
+    // in every other block only.  Five aligned words cover them either way; a funnel shift by 0 or 16
+    // bits re-aligns them (five wide loads and four shifts instead of eight 16-bit loads).
+    // (`row` is 16-byte aligned: a staged row buffer)
+    const int qoff = (p >> 1) * QBlock<QT>::kBytes + 2 + (QT == CB200_QTYPE_Q8_0 ? (p & 1) * 16 : 0);
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(row) + (qoff >> 2);
+    const uint32_t sh = (static_cast<uint32_t>(qoff) & 2u) * 8u;
+    uint32_t raw[5];
+  #pragma unroll
+    for (int i = 0; i < 5; ++i) raw[i] = wp[i];
     uint32_t w[4];
   #pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] = static_cast<uint32_t>(q[2 * i]) | (static_cast<uint32_t>(q[2 * i + 1]) << 16);
+    for (int i = 0; i < 4; ++i) w[i] = __funnelshift_r(raw[i], raw[i + 1], sh);
     float bias;
     if (QT == CB200_QTYPE_Q8_0) {
   #pragma unroll

@@ -214,7 +214,7 @@ struct QSlot {
 constexpr int kOwnerNone = 0, kOwnerToAll = 1, kOwnerToRowOwner = 2;
 
 template <int QT, int DT, int HB, int OWNER>
-__global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, int stages) {
+__global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, int stages) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
   const int stage_bytes = (a.row_bytes + 15) & ~15;
@@ -225,6 +225,17 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
   const int64_t first = static_cast<int64_t>(blockIdx.x) * rpc + ty;
   const int64_t step = static_cast<int64_t>(gridDim.x) * rpc;
   uint64_t id_ahead = 0;  // issuing lane: id of the next row to be issued, already loaded
+
+  // row-invariant: this thread's alpha vectors and the position weights n - 16 p of its half blocks
+  uint4 al[2 * HB];
+  float wj[HB];
+#pragma unroll
+  for (int j = 0; j < HB; ++j) {
+    const int p = j * tpr + tx;
+    al[2 * j] = __ldg(a.alpha + 2 * p);
+    al[2 * j + 1] = __ldg(a.alpha + 2 * p + 1);
+    wj[j] = static_cast<float>(a.n - 16 * p);
+  }
 
   // without an id list the rows are taken in order (a dense source)
   auto row_id = [&](int64_t r) -> uint64_t {
@@ -308,9 +319,8 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
         const int p = j * tpr + tx;
         float d;
         decode_half_block<QT, DT>(buf, p, h[2 * j], h[2 * j + 1], d);
-        const float w0 = static_cast<float>(a.n - 16 * p);
-        accumulate_vec_w<DT>(h[2 * j], w0, lsum, lw);
-        accumulate_vec_w<DT>(h[2 * j + 1], w0 - 8.0f, lsum, lw);
+        accumulate_vec_w<DT>(h[2 * j], wj[j], lsum, lw);
+        accumulate_vec_w<DT>(h[2 * j + 1], wj[j] - 8.0f, lsum, lw);
         d = fabsf(d);
         dmin = fminf(dmin, d == 0.0f ? 3.0e38f : d);  // a zero scale makes exact zeros only
       }
@@ -320,7 +330,8 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
     }
     bool need;
     float row_dmin;
-    float m = decide_row<DT>(lsum, lw, a.n, a.eps, a.flags, sm, need, dmin, &row_dmin);
+    // (the slot's warps meet again at the end of the row, before sm.red is written for the next one)
+    float m = decide_row<DT, true>(lsum, lw, a.n, a.eps, a.flags, sm, need, dmin, &row_dmin);
     if (need && kind == kRowDecode) {
       m = replay_row<DT, QuantRow<QT, DT>>(QuantRow<QT, DT>{buf}, a.V, a.n, a.eps, sm);
 #pragma unroll
@@ -391,22 +402,21 @@ __global__ void __launch_bounds__(128, 5) qrms_rowslot_kernel(const QRmsArgs a, 
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_vec<DT, true>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
-              rms_output_vec<DT, true>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
+          put(p, rms_output_vec<DT, true>(h[2 * j], al[2 * j], m, r, fast_div),
+              rms_output_vec<DT, true>(h[2 * j + 1], al[2 * j + 1], m, r, fast_div));
         }
       } else if (plain) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_plain<DT>(h[2 * j], __ldg(a.alpha + 2 * p), m, r),
-              rms_output_plain<DT>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r));
+          put(p, rms_output_plain<DT>(h[2 * j], al[2 * j], m, r), rms_output_plain<DT>(h[2 * j + 1], al[2 * j + 1], m, r));
         }
       } else {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_rare<DT>(h[2 * j], __ldg(a.alpha + 2 * p), m, r, fast_div),
-              rms_output_rare<DT>(h[2 * j + 1], __ldg(a.alpha + 2 * p + 1), m, r, fast_div));
+          put(p, rms_output_rare<DT>(h[2 * j], al[2 * j], m, r, fast_div),
+              rms_output_rare<DT>(h[2 * j + 1], al[2 * j + 1], m, r, fast_div));
         }
       }
     }
@@ -555,7 +565,7 @@ static cudaError_t launch_q_t(const QRmsArgs& a_in, int tpr, cudaStream_t stream
   QRmsArgs a = a_in;
   a.wt = wait_tuning();
   const int rpc = 128 / tpr;  // row slots per 128-thread CTA
-  const int ctas = 5;         // CTAs per SM the register cap admits (640 threads); more ran slower
+  const int ctas = 4;         // CTAs per SM: the register budget (alpha stays resident) and the barriers admit four
   const int stage_bytes = (a.row_bytes + 15) & ~15;
   // ring depth: what 196 KB of shared memory per SM (a carve-out the hardware offers; the next one
   // is all 228 KB) allows with `ctas` CTAs resident and 1 KB reserved per CTA; at least 2 (one row ahead)

@@ -346,7 +346,10 @@ __device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, 
 // than a warp) and warp 0 of the row decides.  Returns T(m) if `need_replay` comes back false;
 // otherwise only replay_row can tell.  `lmin` is a per-thread value whose minimum over the row
 // is returned in `row_min` when that pointer is given.
-template <int DT>
+// ONE_BARRIER (rows of up to four warps, and only where the caller synchronises the row's warps again
+// before the next row): after the exchange of the warp partials every warp adds them up and decides
+// for itself -- same inputs, same operations, same answer -- instead of waiting for warp 0 to publish.
+template <int DT, bool ONE_BARRIER = false>
 __device__ __forceinline__ float decide_row(float lsum, float lw, int n, float eps, int flags, RowRegSmem& sm,
                                             bool& need_replay, float lmin = 0.0f, float* row_min = nullptr) {
   const int tx = threadIdx.x, tpr = blockDim.x;
@@ -377,6 +380,23 @@ __device__ __forceinline__ float decide_row(float lsum, float lw, int n, float e
     if (row_min != nullptr) sm.red[32 + warp] = lmin;
   }
   row_barrier(bar_id, tpr);
+  if (ONE_BARRIER && wpr <= 4) {
+    s = sm.red[0];
+    w = sm.red[16];
+    float mn = row_min != nullptr ? sm.red[32] : 0.0f;
+    for (int i = 1; i < wpr; ++i) {
+      s += sm.red[i];
+      w += sm.red[16 + i];
+      if (row_min != nullptr) mn = fminf(mn, sm.red[32 + i]);
+    }
+    if (row_min != nullptr) *row_min = mn;
+    if (fast) {
+      need_replay = false;
+      return round_to<DT>(rms_from_sum(s, nf, eps));
+    }
+    need_replay = !decide_m<DT>(s, w, nf, eps, m) || force;
+    return m;
+  }
   if (warp == 0) {
     s = warp_sum(lane < wpr ? sm.red[lane] : 0.0f);
     bool need = false;

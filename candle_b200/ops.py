@@ -398,3 +398,33 @@ def rms_norm_rows(xs: torch.Tensor, rows: torch.Tensor, alpha: torch.Tensor, eps
     if xs.dim() != 2:
         raise CandleError(f"unexpected rank, expected: 2, got: {xs.dim()} ({_dims(xs)})")
     return embedding_rms_norm(xs, rows, alpha, eps, check=check, status=status)
+
+
+def qembedding_route_rows(qtensor, ids: torch.Tensor, dst_ptrs, row_bounds, *, vocab_range: tuple[int, int], vocab: int,
+                          status: torch.Tensor | None = None) -> None:
+    """Routing step of a vocabulary-sharded lookup with row-sharded consumers: for every id inside
+    ``vocab_range`` the raw block row of this rank's slice ``qtensor`` is copied into the staging buffer
+    of the rank whose block of token rows holds the id's position (``dst_ptrs`` in rank order,
+    ``row_bounds`` the block limits).  After the ranks' barrier each staging buffer is a
+    ``[rows_r, hidden]`` table of blocks in token order, ready for a local lookup + norm."""
+    import ctypes
+
+    from .quantized import QTensor  # local import: quantized imports this module
+
+    if not isinstance(qtensor, QTensor) or len(qtensor.shape) != 2:
+        raise CandleError("qembedding expects a rank-2 QTensor")
+    local_vocab, hidden = qtensor.shape
+    flat = _ids_checks(ids.reshape(-1))
+    _same_device(qtensor.data, flat)
+    begin, end = vocab_range
+    if end - begin != local_vocab:
+        raise CandleError(f"vocab shard [{begin}, {end}) does not match the table's {local_vocab} rows")
+    ptrs = [int(p) for p in dst_ptrs]
+    bounds = [int(b) for b in row_bounds]
+    if len(bounds) != len(ptrs) + 1:
+        raise CandleError(f"{len(ptrs)} destinations need {len(ptrs) + 1} row bounds, got {len(bounds)}")
+    arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    barr = (ctypes.c_int64 * len(bounds))(*bounds)
+    _cabi.call("cb200_qembedding_route_rows", _ptr(qtensor.data), qtensor.dtype.value, _ptr(flat),
+               ctypes.cast(arr, ctypes.c_void_p), len(ptrs), ctypes.cast(barr, ctypes.c_void_p), vocab, hidden,
+               flat.shape[0], _ID_DTYPES[flat.dtype], begin, end, _ptr(status), _stream(flat))

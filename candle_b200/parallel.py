@@ -115,6 +115,42 @@ class ShardedQEmbedding:
         return bounds[self.rank], bounds[self.rank + 1]
 
 
+class RoutedQEmbedding:
+    """Vocabulary-sharded table, row-sharded consumers, exchange in QUANTISED form: each rank routes the
+    raw block rows of the ids it owns to the rank whose ``row_shard`` of the token rows holds them
+    (``cb200_qembedding_route_rows``), the ranks meet at a barrier, and every rank decodes and
+    normalises its own block locally.  Two staging buffers per rank alternate, so the stores of step
+    i + 1 never land in rows a rank still decodes from step i."""
+
+    def __init__(self, sharded: ShardedQEmbedding, max_rows: int, group=None):
+        self.emb, self.group = sharded, group
+        self.block_rows = -(-max_rows // sharded.world)
+        row_bytes = sharded.table.shape[1] // sharded.table.dtype.block_size * sharded.table.dtype.type_size
+        dev = sharded.table.data.device
+        self.staging = [peer_mapped_empty((self.block_rows, row_bytes), torch.uint8, dev, group, rank_order=True)
+                        for _ in range(2)]
+        self.iota = torch.arange(self.block_rows, dtype=torch.int32, device=dev)
+        self.flag = torch.zeros(1, device=dev)
+        self.step = 0
+
+    def forward_rms_norm(self, ids: torch.Tensor, alpha: torch.Tensor, eps: float, *, status=None) -> torch.Tensor:
+        """Returns this rank's ``row_shard`` of ``rms_norm(lookup(ids))`` as ``[rows_r, hidden]``."""
+        import torch.distributed as dist
+
+        e = self.emb
+        rows = ids.numel()
+        if -(-rows // e.world) > self.block_rows:
+            raise CandleError(f"{rows} token rows exceed the staging buffers of {self.block_rows} rows per rank")
+        bounds = [row_shard(rows, r, e.world)[0] for r in range(e.world)] + [rows]
+        local, ptrs = self.staging[self.step & 1]
+        self.step += 1
+        ops.qembedding_route_rows(e.table, ids, ptrs, bounds, vocab_range=(e.begin, e.end), vocab=e.vocab, status=status)
+        dist.all_reduce(self.flag, group=self.group)  # the ranks' barrier, in stream order
+        mine = bounds[e.rank + 1] - bounds[e.rank]
+        staged = QTensor(local[:mine].reshape(-1), e.table.dtype, (mine, e.table.shape[1]))
+        return ops.qembedding_rms_norm(staged, self.iota[:mine], alpha, eps, check=False, status=status)
+
+
 def peer_mapped_empty(shape, dtype: torch.dtype, device, group=None, rank_order: bool = False):
     """A buffer of ``shape`` on every rank of ``group`` (the same shape everywhere), each one mapped
     into every rank's address space (torch's symmetric memory: CUDA virtual-memory handles exchanged

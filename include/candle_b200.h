@@ -304,6 +304,24 @@ CB200_API int cb200_qembedding_rms_norm_row_owner(const void* qtable, int qtype,
                                         int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
                                         cb200_stream_t stream);
 
+/*
+ * The cheapest exchange for a vocabulary-sharded table with row-sharded consumers: route the RAW block
+ * rows.  For every id inside [vocab_begin, vocab_end) this rank copies the quantised row -- hidden / 32
+ * blocks, e.g. 4608 bytes of Q4_0 where the decoded bf16 row has 16384 -- into `dsts[r]`, the staging
+ * buffer of the rank r whose block of token rows [row_bounds[r], row_bounds[r + 1]) contains the id's
+ * position i, at row i - row_bounds[r] (HOST arrays in rank order as for
+ * cb200_qembedding_rms_norm_row_owner; the peers' staging buffers are mapped into this process).  After
+ * the ranks' barrier each staging buffer is a dense [rows_r, hidden] table of blocks in token order,
+ * and the rank decodes and normalises it locally with cb200_qembedding_rms_norm (ids 0 .. rows_r - 1):
+ * bit-identical to the unsharded lookup + norm, with about (N-1)/N^2 of the QUANTISED bytes crossing
+ * NVLink per GPU.  Ids of other ranks are skipped; ids >= vocab are reported through `status`.  The
+ * reference has no counterpart (its tensor-parallel example replicates the embedding,
+ * candle-examples/examples/llama_multiprocess/model.rs:181-184).
+ */
+CB200_API int cb200_qembedding_route_rows(const void* qtable, int qtype, const void* ids, void* const* dsts, int n_dsts,
+                                const int64_t* row_bounds, int64_t vocab, int32_t hidden, int64_t n_ids, int id_dtype,
+                                int64_t vocab_begin, int64_t vocab_end, cb200_status* status, cb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -63,6 +63,21 @@ def test_ctypes_signatures_match_the_header(built_lib):
             assert len(argtypes) == declared[name], name
 
 
+def test_rust_ffi_declares_the_same_entry_points():
+    """rust/candle-b200-kernels/src/ffi.rs (not compiled here) names every entry point of the headers with the
+    same number of parameters; the self-test hook and the thin NCCL wrappers (cudarc has its own) are left out."""
+    text = open(os.path.join(ROOT, "rust", "candle-b200-kernels", "src", "ffi.rs")).read()
+    rust = {}
+    for m in re.finditer(r"pub fn (cb200_\w+)\s*\(([^;]*?)\)\s*(?:->\s*[\w\s\*:]+)?;", text, flags=re.S):
+        params = m.group(2).strip()
+        rust[m.group(1)] = 0 if not params else len([p for p in params.split(",") if p.strip()])
+    skipped = {"cb200_selftest_wait_expiry", "cb200_nccl_unique_id", "cb200_nccl_comm_init", "cb200_nccl_comm_destroy"}
+    declared = {k: v for k, v in header_functions().items() if k not in skipped}
+    assert set(rust) == set(declared), set(rust) ^ set(declared)
+    for name, n in declared.items():
+        assert rust[name] == n, name
+
+
 def test_argument_validation_needs_no_device(built_lib):
     from candle_b200 import _cabi
 

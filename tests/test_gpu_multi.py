@@ -88,6 +88,21 @@ def _worker(rank, world, port, ret):
                 torch.cuda.synchronize()
                 ok = ok and (mb, me) == row_shard(n, rank, world)
                 ok = ok and np.array_equal(to_oracle(block[: me - mb]), want[mb:me]) and st3[0].item() == 0
+            # routed mode: raw block rows to the rank whose row block holds them, decoded locally
+            from candle_b200.parallel import RoutedQEmbedding
+
+            try:
+                routed = RoutedQEmbedding(emb, n)
+            except Exception as exc:
+                print(f"peer-mapped buffers unavailable, routed variant not exercised: {exc}", flush=True)
+                routed = None
+            if routed is not None:
+                for _ in range(3):  # the two staging buffers alternate
+                    yr = routed.forward_rms_norm(ids_tensor(ids, dev), from_oracle(alpha, "bf16", dev), 1e-5)
+                    torch.cuda.synchronize()
+                    rb, re = row_shard(n, rank, world)
+                    ok = ok and np.array_equal(to_oracle(yr), want[rb:re])
+                dist.barrier()
         # the same through the C entry point with a communicator of its own
         from candle_b200 import _nccl
         from candle_b200.ops import _stream, new_status

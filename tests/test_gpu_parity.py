@@ -540,6 +540,47 @@ def test_owner_writes_variant_emulated_on_one_gpu(cb, qtype, gq):
                                   vocab_range=(500, 1000), vocab=vocab, status=st)
 
 
+@pytest.mark.parametrize("qtype,gq", [("q4_0", "Q4_0"), ("q8_0", "Q8_0")])
+def test_row_owner_and_routed_variants_emulated_on_one_gpu(cb, qtype, gq):
+    # Three "ranks" run one after the other on this GPU, each over its third of the vocabulary, with the
+    # token rows cut into three blocks of unequal size.  Row-owner mode: every finished row lands in the
+    # buffer of the block that holds it.  Routed mode: the raw block rows land in that block's staging
+    # table, which is then decoded and normalised as a local table.  Both equal the unsharded oracle.
+    from candle_b200.ops import new_status, qembedding_rms_norm_row_owner, qembedding_route_rows
+
+    rng = np.random.default_rng(59)
+    vocab, hidden, n = 900, 4096, 1000
+    qt = make_qtable(rng, qtype, vocab, hidden)
+    ids = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+    alpha = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+    want = oracle.rms_norm(oracle.qembedding(qt, qtype, ids, "bf16"), alpha, 1e-5, "bf16")
+    ta, tids = from_oracle(alpha, "bf16"), ids_tensor(ids)
+    bounds = [0, 334, 667, 1000]
+    row_bytes = qt.shape[1]
+    outs = [torch.full((bounds[r + 1] - bounds[r], hidden), float("nan"), dtype=torch.bfloat16, device="cuda") for r in range(3)]
+    stage = [torch.zeros(bounds[r + 1] - bounds[r], row_bytes, dtype=torch.uint8, device="cuda") for r in range(3)]
+    st = new_status("cuda")
+    for r in range(3):
+        b, e = 300 * r, 300 * r + 300
+        local = cb.QTensor.from_raw(torch.from_numpy(qt[b:e]), getattr(cb.GgmlDType, gq), (e - b, hidden), device="cuda")
+        qembedding_rms_norm_row_owner(local, tids, ta, 1e-5, [o.data_ptr() for o in outs], bounds, vocab_range=(b, e),
+                                      vocab=vocab, status=st)
+        qembedding_route_rows(local, tids, [s_.data_ptr() for s_ in stage], bounds, vocab_range=(b, e), vocab=vocab,
+                              status=st)
+    torch.cuda.synchronize()
+    assert st[0].item() == 0
+    for r in range(3):
+        assert np.array_equal(to_oracle(outs[r]), want[bounds[r]:bounds[r + 1]])
+        assert np.array_equal(stage[r].cpu().numpy(), qt[ids[bounds[r]:bounds[r + 1]]])  # the raw rows, in token order
+        staged = cb.QTensor(stage[r].reshape(-1), getattr(cb.GgmlDType, gq), (bounds[r + 1] - bounds[r], hidden))
+        iota = torch.arange(bounds[r + 1] - bounds[r], dtype=torch.int32, device="cuda")
+        y = cb.qembedding_rms_norm(staged, iota, ta, 1e-5)
+        assert np.array_equal(to_oracle(y), want[bounds[r]:bounds[r + 1]])
+    with pytest.raises(Exception, match="row bounds"):
+        qembedding_route_rows(local, tids, [s_.data_ptr() for s_ in stage], [0, 334, 667, 999], vocab_range=(600, 900),
+                              vocab=vocab, status=st)
+
+
 # ------------------------------------------------------------------------------------------------
 # front-end error behaviour (candle's messages)
 # ------------------------------------------------------------------------------------------------
