@@ -227,15 +227,20 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
   uint64_t id_ahead = 0;  // issuing lane: id of the next row to be issued, already loaded
 
   // row-invariant: this thread's alpha vectors and the position weights n - 16 p of its half blocks
-  uint4 al[2 * HB];
+  // (with eight half blocks per thread alpha does not fit and is re-read through L1)
+  constexpr bool ALPHA_REGS = HB <= 4;
+  uint4 al[ALPHA_REGS ? 2 * HB : 1];
   float wj[HB];
 #pragma unroll
   for (int j = 0; j < HB; ++j) {
     const int p = j * tpr + tx;
-    al[2 * j] = __ldg(a.alpha + 2 * p);
-    al[2 * j + 1] = __ldg(a.alpha + 2 * p + 1);
+    if (ALPHA_REGS) {
+      al[2 * j] = __ldg(a.alpha + 2 * p);
+      al[2 * j + 1] = __ldg(a.alpha + 2 * p + 1);
+    }
     wj[j] = static_cast<float>(a.n - 16 * p);
   }
+  auto alpha_vec = [&](int k) -> uint4 { return ALPHA_REGS ? al[ALPHA_REGS ? k : 0] : __ldg(a.alpha + 2 * ((k >> 1) * tpr + tx) + (k & 1)); };
 
   // without an id list the rows are taken in order (a dense source)
   auto row_id = [&](int64_t r) -> uint64_t {
@@ -333,6 +338,9 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
     // (the slot's warps meet again at the end of the row, before sm.red is written for the next one)
     float m = decide_row<DT, true>(lsum, lw, a.n, a.eps, a.flags, sm, need, dmin, &row_dmin);
     if (need && kind == kRowDecode) {
+      // The replay reuses sm.red, which the slot's other warps may still be reading for their own
+      // copy of the decision: they all reach the same verdict, so they can all meet here first.
+      if (tpr > 32) row_barrier(bar_id, tpr);
       m = replay_row<DT, QuantRow<QT, DT>>(QuantRow<QT, DT>{buf}, a.V, a.n, a.eps, sm);
 #pragma unroll
       for (int j = 0; j < HB; ++j) {  // nothing was kept in registers across the replay
@@ -402,21 +410,22 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_vec<DT, true>(h[2 * j], al[2 * j], m, r, fast_div),
-              rms_output_vec<DT, true>(h[2 * j + 1], al[2 * j + 1], m, r, fast_div));
+          put(p, rms_output_vec<DT, true>(h[2 * j], alpha_vec(2 * j), m, r, fast_div),
+              rms_output_vec<DT, true>(h[2 * j + 1], alpha_vec(2 * j + 1), m, r, fast_div));
         }
       } else if (plain) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_plain<DT>(h[2 * j], al[2 * j], m, r), rms_output_plain<DT>(h[2 * j + 1], al[2 * j + 1], m, r));
+          put(p, rms_output_plain<DT>(h[2 * j], alpha_vec(2 * j), m, r),
+              rms_output_plain<DT>(h[2 * j + 1], alpha_vec(2 * j + 1), m, r));
         }
       } else {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = j * tpr + tx;
-          put(p, rms_output_rare<DT>(h[2 * j], al[2 * j], m, r, fast_div),
-              rms_output_rare<DT>(h[2 * j + 1], al[2 * j + 1], m, r, fast_div));
+          put(p, rms_output_rare<DT>(h[2 * j], alpha_vec(2 * j), m, r, fast_div),
+              rms_output_rare<DT>(h[2 * j + 1], alpha_vec(2 * j + 1), m, r, fast_div));
         }
       }
     }
@@ -451,6 +460,8 @@ static bool rowreg_shape(int V, int& tpr, int& vpt, int& rpc) {
 // Shape of the quantised-source kernel: HB half blocks (16 elements) per thread, a warp per row
 // up to 4096 columns.  V == 2 * HB * tpr exactly.
 static bool qrowreg_shape(int V, int& tpr, int& hb) {
+  // (a whole 4096-column row in one warp, eight half blocks per thread, was measured slower on the
+  // Q8_0 lookup: 252 us against 216 us for two warps per row)
   for (int t = 32; t <= 128; t <<= 1) {
     for (int cand = 4; cand >= 1; --cand) {
       if (V == 2 * cand * t) {

@@ -346,9 +346,10 @@ __device__ __forceinline__ bool decide_m(float s, float w, float nf, float eps, 
 // than a warp) and warp 0 of the row decides.  Returns T(m) if `need_replay` comes back false;
 // otherwise only replay_row can tell.  `lmin` is a per-thread value whose minimum over the row
 // is returned in `row_min` when that pointer is given.
-// ONE_BARRIER (rows of up to four warps, and only where the caller synchronises the row's warps again
-// before the next row): after the exchange of the warp partials every warp adds them up and decides
-// for itself -- same inputs, same operations, same answer -- instead of waiting for warp 0 to publish.
+// ONE_BARRIER (rows of up to four warps): after the exchange of the warp partials every warp adds them
+// up and decides for itself -- same inputs, same operations, same answer -- instead of waiting for
+// warp 0 to publish.  The warps then leave at different times, so the caller must synchronise the
+// row's warps again before anything overwrites sm.red: before the next row, and before replay_row.
 template <int DT, bool ONE_BARRIER = false>
 __device__ __forceinline__ float decide_row(float lsum, float lw, int n, float eps, int flags, RowRegSmem& sm,
                                             bool& need_replay, float lmin = 0.0f, float* row_min = nullptr) {

@@ -463,6 +463,30 @@ def test_qembedding_rms_norm_matches_oracle(cb, qtype, dtype):
                            y.view(torch.int16 if dtype != "f32" else torch.int32))
 
 
+@pytest.mark.parametrize("qtype,hidden", [("q4_0", 8192), ("q8_0", 4096), ("q8_0", 2048)])
+def test_qembedding_rms_norm_many_rows_equals_lookup_then_norm(cb, qtype, hidden):
+    # Rows of two and four warps, enough of them that thousands fall to the exact replay while the
+    # slot's other warps are still busy with their copy of the decision: the single-launch kernel must
+    # agree bit for bit with the lookup followed by the dense RMS norm (another kernel, another
+    # synchronisation scheme), and with itself on a second run.
+    rng = np.random.default_rng(61)
+    gq = getattr(cb.GgmlDType, qtype.upper())
+    vocab, n = 4096, 200_000
+    qt = make_qtable(rng, qtype, vocab, hidden)
+    q = cb.QTensor.from_raw(torch.from_numpy(qt), gq, (vocab, hidden), device="cuda")
+    alpha_np = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+    alpha = from_oracle(alpha_np, "bf16")
+    ids_np = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+    ids = ids_tensor(ids_np)
+    want = cb.rms_norm(q.embedding(ids, torch.bfloat16), alpha, 1e-5)
+    for _ in range(2):
+        got = cb.qembedding_rms_norm(q, ids, alpha, 1e-5)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    sample = np.arange(0, n, 997)
+    ref = oracle.rms_norm(oracle.qembedding(qt, qtype, ids_np[sample], "bf16"), alpha_np, 1e-5, "bf16")
+    assert np.array_equal(to_oracle(got[torch.from_numpy(sample).cuda()]), ref)
+
+
 def test_sharded_entry_point_single_rank(cb):
     # cb200_sharded_qembedding_rms_norm with a one-rank communicator: lookup into caller scratch,
     # all-reduce (identity), norm.  Must equal the oracle and the fused single-GPU call.
