@@ -713,23 +713,21 @@ def c4_section(args, rank, world, dev, timed, peak, headline):
                         "carries only (N-1)/N^2 of the QUANTISED rows per GPU"),
             "note": "raw block rows are routed to the rank whose row block holds them and decoded there"}
         ok_row = ok_row and ok_routed
-        # end to end for the row-owner variant: ids from pinned host memory, this rank's block back to the host
+        # end to end for the routed variant: ids from pinned host memory, this rank's block back to the host
         host_ids = [torch.from_numpy(np.ascontiguousarray(i.reshape(-1)).view(np.int32)).pin_memory() for i in wl.ids]
         dev_ids = torch.empty_like(ids[0].reshape(-1))
         host_out = torch.empty(re - rb, wl.hidden, dtype=torch.bfloat16).pin_memory()
 
         def e2e_step(i):
             dev_ids.view(torch.uint8).copy_(host_ids[i % 2].view(torch.uint8), non_blocking=True)
-            emb.forward_rms_norm_row_owner(dev_ids, alpha, wl.eps, blocks[i % 2][1], status=st)
-            dist.all_reduce(flag)
-            host_out.copy_(blocks[i % 2][0][: re - rb], non_blocking=True)
+            host_out.copy_(routed.forward_rms_norm(dev_ids, alpha, wl.eps, status=st), non_blocking=True)
 
         ke = max(2, min(steps, 5))
         ms_e2e = timed(e2e_step, ke, 1) / ke
         e2e = {"value": wl.rows / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": int(dev_ids.numel() * dev_ids.element_size()) * world,
                "d2h_bytes_per_step": out_bytes,
-               "how": "row-owner variant: every rank uploads the ids; each rank downloads its block of the finished rows"}
+               "how": "routed-rows variant: every rank uploads the ids; each rank downloads its block of the finished rows"}
     else:
         variants["owner_writes_all"] = variants["row_owner"] = variants["routed_rows"] = {"unavailable": owner_err}
     clocks = sampler.stop() if (rank == 0 and headline) else None
@@ -741,12 +739,13 @@ def c4_section(args, rank, world, dev, timed, peak, headline):
              "e2e": e2e, "parity": "bit-exact vs unsharded CPU oracle" if parity_ok else "MISMATCH"}
     if not headline:
         return entry, parity_ok
-    row = variants.get("row_owner", {})
-    roof = ({"bound": "hbm", "achieved": (wl.rows * wl.row_qbytes / world + out_bytes / world) / (row["ms_per_step"] * 1e-3) / 1e9,
-             "peak": peak, "unit": "GB/s", "frac": row["frac_of_target"], "peak_kind": "of measured", "traffic": None,
-             "note": "row-owner variant: target time = max(per-GPU HBM bytes / measured HBM peak, bytes leaving the GPU "
-                     "/ 770 GB/s measured peer-copy bandwidth); frac = target / achieved time"}
-            if "ms_per_step" in row else None)
+    hbm_best = {"routed_rows": (3 * wl.rows * wl.row_qbytes + out_bytes) / world}.get(
+        best_name, wl.rows * wl.row_qbytes / world + out_bytes / world)
+    roof = ({"bound": "hbm", "achieved": hbm_best / (best["ms_per_step"] * 1e-3) / 1e9,
+             "peak": peak, "unit": "GB/s", "frac": best["frac_of_target"], "peak_kind": "of measured", "traffic": None,
+             "note": f"{best_name} variant: target time = max(per-GPU HBM bytes / measured HBM peak, bytes leaving the "
+                     "GPU / 770 GB/s measured peer-copy bandwidth); frac = target / achieved time"}
+            if "frac_of_target" in best else None)
     line = {"metric": METRIC, "value": best["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": args.warmup, "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seed 0)",

@@ -12,6 +12,7 @@ _vp, _i64, _i32, _f32, _int, _sz = (ctypes.c_void_p, ctypes.c_int64, ctypes.c_in
 SIGNATURES = {
     "cb200_nccl_unique_id": [_vp],
     "cb200_nccl_comm_init": [ctypes.POINTER(_vp), _int, _vp, _int],
+    "cb200_nccl_comm_init_timeout": [ctypes.POINTER(_vp), _int, _vp, _int, _int],
     "cb200_nccl_comm_destroy": [_vp],
     "cb200_sharded_qembedding_rms_norm": [
         _vp, _vp, _int, _vp, _vp, _vp, _vp, _sz, _i64, _i32, _i64, _f32, _int, _int, _i64, _i64, _int, _vp, _vp,
@@ -22,6 +23,7 @@ SIGNATURES = {
 }
 UNIQUE_ID_BYTES = 128
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
+E_TIMEOUT = -6
 
 
 def _load() -> ctypes.CDLL:
@@ -56,6 +58,14 @@ def comm_init(nranks: int, uid: bytes, rank: int) -> ctypes.c_void_p:
     comm = _vp()
     buf = ctypes.create_string_buffer(uid, UNIQUE_ID_BYTES)
     call("cb200_nccl_comm_init", ctypes.byref(comm), nranks, ctypes.cast(buf, _vp), rank)
+    return comm
+
+
+def comm_init_timeout(nranks: int, uid: bytes, rank: int, timeout_ms: int) -> ctypes.c_void_p:
+    """``comm_init`` that gives up (error code ``E_TIMEOUT``) when the ranks have not all joined in time."""
+    comm = _vp()
+    buf = ctypes.create_string_buffer(uid, UNIQUE_ID_BYTES)
+    call("cb200_nccl_comm_init_timeout", ctypes.byref(comm), nranks, ctypes.cast(buf, _vp), rank, timeout_ms)
     return comm
 
 

@@ -61,7 +61,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         rebuilt = list(pool.map(compile_one, zip(srcs, objs)))
     if any(rebuilt) or not os.path.exists(LIB_PATH):
-        subprocess.run([_nvcc(), *flags, "-ccbin", "/usr/bin/g++", "-shared", "-o", LIB_PATH, *objs], check=True)
+        subprocess.run([_nvcc(), *flags, "-ccbin", "/usr/bin/g++", "-shared", "-o", LIB_PATH, *objs, "-ldl"], check=True)
     return LIB_PATH
 
 

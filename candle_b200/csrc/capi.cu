@@ -4,11 +4,23 @@
 #include <cstdarg>
 #include <cstdio>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "launch.h"
 #include "qblocks.cuh"
 #include "rms_rowreg.cuh"
 
 namespace {
+
+// An NVTX range around every entry point that enqueues work, named after it: what candle's
+// `tracing` spans around `forward` show in a Chrome trace, these show on a profiler's timeline.
+// Without a profiler attached a range is two calls through a null function table.
+struct TraceRange {
+  explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+  ~TraceRange() { nvtxRangePop(); }
+  TraceRange(const TraceRange&) = delete;
+  TraceRange& operator=(const TraceRange&) = delete;
+};
 
 thread_local char g_last_error[512] = "";
 
@@ -130,6 +142,7 @@ const char* cb200_last_error(void) { return g_last_error; }
 
 int cb200_rms_norm(const void* x, const void* residual, const void* alpha, void* y, void* sum_out, int64_t rows,
                    int32_t cols, float eps, int dtype, int flags, cb200_stream_t stream) {
+  const TraceRange trace("cb200_rms_norm");
   return norm_impl(cb200::kOpRmsNorm, x, residual, alpha, nullptr, y, sum_out, rows, cols, eps, dtype, flags, nullptr,
                    stream);
 }
@@ -137,6 +150,7 @@ int cb200_rms_norm(const void* x, const void* residual, const void* alpha, void*
 int cb200_rms_norm_checked(const void* x, const void* residual, const void* alpha, void* y, void* sum_out,
                            int64_t rows, int32_t cols, float eps, int dtype, int flags, cb200_status* status,
                            cb200_stream_t stream) {
+  const TraceRange trace("cb200_rms_norm_checked");
   return norm_impl(cb200::kOpRmsNorm, x, residual, alpha, nullptr, y, sum_out, rows, cols, eps, dtype, flags, status,
                    stream);
 }
@@ -144,6 +158,7 @@ int cb200_rms_norm_checked(const void* x, const void* residual, const void* alph
 int cb200_layer_norm(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
                      void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags,
                      cb200_stream_t stream) {
+  const TraceRange trace("cb200_layer_norm");
   return norm_impl(cb200::kOpLayerNorm, x, residual, gamma, beta, y, sum_out, rows, cols, eps, dtype, flags, nullptr,
                    stream);
 }
@@ -151,12 +166,14 @@ int cb200_layer_norm(const void* x, const void* residual, const void* gamma, con
 int cb200_layer_norm_checked(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
                              void* sum_out, int64_t rows, int32_t cols, float eps, int dtype, int flags,
                              cb200_status* status, cb200_stream_t stream) {
+  const TraceRange trace("cb200_layer_norm_checked");
   return norm_impl(cb200::kOpLayerNorm, x, residual, gamma, beta, y, sum_out, rows, cols, eps, dtype, flags, status,
                    stream);
 }
 
 int cb200_layer_norm_slow(const void* x, const void* weight, const void* bias, void* y, int64_t rows, int32_t cols,
                           float eps, int dtype, int remove_mean, cb200_stream_t stream) {
+  const TraceRange trace("cb200_layer_norm_slow");
   const char* name = "cb200_layer_norm_slow";
   if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
   if (rows < 0 || cols < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape [%lld, %d]", name, (long long)rows, cols);
@@ -168,6 +185,7 @@ int cb200_layer_norm_slow(const void* x, const void* weight, const void* bias, v
 }
 
 int cb200_softmax_last_dim(const void* x, void* y, int64_t rows, int32_t cols, int dtype, cb200_stream_t stream) {
+  const TraceRange trace("cb200_softmax_last_dim");
   const char* name = "cb200_softmax_last_dim";
   if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
   if (rows < 0 || cols < 0) return fail(CB200_E_INVALID_ARGUMENT, "%s: negative shape [%lld, %d]", name, (long long)rows, cols);
@@ -179,6 +197,7 @@ int cb200_softmax_last_dim(const void* x, void* y, int64_t rows, int32_t cols, i
 
 int cb200_rope(const void* src, const void* cos, const void* sin, void* dst, int64_t b, int32_t h, int32_t t, int32_t d,
                int dtype, int variant, cb200_stream_t stream) {
+  const TraceRange trace("cb200_rope");
   const char* name = "cb200_rope";
   if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
   if (variant < CB200_ROPE_INTERLEAVED || variant > CB200_ROPE_THD)
@@ -201,6 +220,7 @@ int cb200_selftest_wait_expiry(int enable) {
 int cb200_index_select(const void* src, const void* ids, void* out, int64_t left, int64_t src_dim, int64_t right,
                        int64_t n_ids, int32_t elem_size, int id_dtype, cb200_status* status,
                        cb200_stream_t stream) {
+  const TraceRange trace("cb200_index_select");
   const char* name = "cb200_index_select";
   if (!valid_id_dtype(id_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported ids dtype code %d", name, id_dtype);
   if (left < 0 || src_dim < 0 || right < 0 || n_ids < 0 || elem_size <= 0)
@@ -222,6 +242,7 @@ int cb200_index_select(const void* src, const void* ids, void* out, int64_t left
 
 int cb200_embedding(const void* table, const void* ids, void* out, int64_t vocab, int32_t hidden, int64_t n_ids,
                     int dtype, int id_dtype, cb200_status* status, cb200_stream_t stream) {
+  const TraceRange trace("cb200_embedding");
   if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "cb200_embedding: unsupported dtype code %d", dtype);
   int rc = check_lookup("cb200_embedding", table, ids, out, vocab, hidden, n_ids, id_dtype);
   if (rc != CB200_OK) return rc;
@@ -229,6 +250,7 @@ int cb200_embedding(const void* table, const void* ids, void* out, int64_t vocab
 }
 
 int cb200_dequantize(const void* blocks, int qtype, void* out, int64_t k, int out_dtype, cb200_stream_t stream) {
+  const TraceRange trace("cb200_dequantize");
   const char* name = "cb200_dequantize";
   if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
   if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
@@ -245,6 +267,7 @@ int cb200_dequantize(const void* blocks, int qtype, void* out, int64_t k, int ou
 int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, int64_t vocab, int32_t hidden,
                      int64_t n_ids, int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
                      cb200_status* status, cb200_stream_t stream) {
+  const TraceRange trace("cb200_qembedding");
   const char* name = "cb200_qembedding";
   if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
   if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
@@ -280,6 +303,7 @@ int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, 
 int cb200_embedding_rms_norm(const void* table, const void* ids, const void* alpha, void* y, void* gathered,
                              int64_t vocab, int32_t hidden, int64_t n_ids, float eps, int dtype, int id_dtype,
                              int flags, cb200_status* status, cb200_stream_t stream) {
+  const TraceRange trace("cb200_embedding_rms_norm");
   const char* name = "cb200_embedding_rms_norm";
   if (!valid_dtype(dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, dtype);
   int rc = check_lookup(name, table, ids, y, vocab, hidden, n_ids, id_dtype);
@@ -355,6 +379,7 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
                               void* gathered, int64_t vocab, int32_t hidden, int64_t n_ids, float eps, int out_dtype,
                               int id_dtype, int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
                               cb200_stream_t stream) {
+  const TraceRange trace("cb200_qembedding_rms_norm");
   const char* name = "cb200_qembedding_rms_norm";
   if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
   if (!valid_dtype(out_dtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported dtype code %d", name, out_dtype);
@@ -472,6 +497,7 @@ int cb200_qembedding_rms_norm_owner(const void* qtable, int qtype, const void* i
                                     void* const* dsts, int n_dsts, int64_t vocab, int32_t hidden, int64_t n_ids,
                                     float eps, int out_dtype, int id_dtype, int64_t vocab_begin, int64_t vocab_end,
                                     int flags, cb200_status* status, cb200_stream_t stream) {
+  const TraceRange trace("cb200_qembedding_rms_norm_owner");
   return owner_impl("cb200_qembedding_rms_norm_owner", qtable, qtype, ids, alpha, dsts, n_dsts, nullptr, vocab, hidden,
                     n_ids, eps, out_dtype, id_dtype, vocab_begin, vocab_end, flags, status, stream);
 }
@@ -481,6 +507,7 @@ int cb200_qembedding_rms_norm_row_owner(const void* qtable, int qtype, const voi
                                         int32_t hidden, int64_t n_ids, float eps, int out_dtype, int id_dtype,
                                         int64_t vocab_begin, int64_t vocab_end, int flags, cb200_status* status,
                                         cb200_stream_t stream) {
+  const TraceRange trace("cb200_qembedding_rms_norm_row_owner");
   const char* name = "cb200_qembedding_rms_norm_row_owner";
   if (row_bounds == nullptr) return fail(CB200_E_INVALID_ARGUMENT, "%s: null row bounds", name);
   return owner_impl(name, qtable, qtype, ids, alpha, dsts, n_dsts, row_bounds, vocab, hidden, n_ids, eps, out_dtype,
@@ -490,6 +517,7 @@ int cb200_qembedding_rms_norm_row_owner(const void* qtable, int qtype, const voi
 int cb200_qembedding_route_rows(const void* qtable, int qtype, const void* ids, void* const* dsts, int n_dsts,
                                 const int64_t* row_bounds, int64_t vocab, int32_t hidden, int64_t n_ids, int id_dtype,
                                 int64_t vocab_begin, int64_t vocab_end, cb200_status* status, cb200_stream_t stream) {
+  const TraceRange trace("cb200_qembedding_route_rows");
   const char* name = "cb200_qembedding_route_rows";
   if (!valid_qtype(qtype)) return fail(CB200_E_UNSUPPORTED_DTYPE, "%s: unsupported block format %d", name, qtype);
   if (dsts == nullptr || row_bounds == nullptr || n_dsts < 1 || n_dsts > 8)

@@ -1,8 +1,10 @@
 // The vocabulary-sharded lookup behind one C call: masked quantised lookup into scratch, NCCL sum,
 // RMS norm.  Built into its own library (libcandle_b200_nccl.so).
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
+#include <thread>
 
 #include <cuda_runtime.h>
 #include <nccl.h>
@@ -29,6 +31,21 @@ int nccl_result(ncclResult_t r, const char* what) {
 
 size_t elem_bytes(int dtype) { return dtype == CB200_DTYPE_F32 ? 4 : 2; }
 
+// On a non-blocking communicator a call may return ncclInProgress; poll the communicator until it
+// has settled or `timeout_ms` is over.  Blocking communicators never take the loop.
+constexpr int kCollectiveAcceptMs = 30000;
+int nccl_settle(ncclComm_t comm, ncclResult_t r, const char* what, int timeout_ms) {
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (r == ncclInProgress) {
+    if (std::chrono::steady_clock::now() > deadline)
+      return fail(CB200_E_TIMEOUT, "%s: not completed within %d ms", what, timeout_ms);
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+    ncclResult_t q = ncclCommGetAsyncError(comm, &r);
+    if (q != ncclSuccess) return nccl_result(q, "ncclCommGetAsyncError");
+  }
+  return nccl_result(r, what);
+}
+
 // Steps shared by the entry points: lookup into `scratch`, sum over ranks in place, normalise.
 int sharded_steps(void* comm, const void* qtable, int qtype, const void* ids, const void* alpha, void* y,
                   void* scratch, int64_t vocab, int32_t hidden, int64_t n_ids, float eps, int out_dtype, int id_dtype,
@@ -38,9 +55,10 @@ int sharded_steps(void* comm, const void* qtable, int qtype, const void* ids, co
   if (rc != CB200_OK) return fail(rc, "cb200_sharded_qembedding_rms_norm: %s", cb200_last_error());
   if (comm != nullptr) {
     const ncclDataType_t dt = out_dtype == CB200_DTYPE_F32 ? ncclFloat32 : (out_dtype == CB200_DTYPE_F16 ? ncclFloat16 : ncclBfloat16);
-    rc = nccl_result(ncclAllReduce(scratch, scratch, static_cast<size_t>(n_ids) * hidden, dt, ncclSum,
+    rc = nccl_settle(static_cast<ncclComm_t>(comm),
+                     ncclAllReduce(scratch, scratch, static_cast<size_t>(n_ids) * hidden, dt, ncclSum,
                                    static_cast<ncclComm_t>(comm), reinterpret_cast<cudaStream_t>(stream)),
-                     "ncclAllReduce");
+                     "ncclAllReduce", kCollectiveAcceptMs);
     if (rc != CB200_OK) return rc;
   }
   rc = cb200_rms_norm(scratch, nullptr, alpha, y, nullptr, n_ids, hidden, eps, out_dtype, flags, stream);
@@ -95,6 +113,29 @@ int cb200_nccl_comm_init(void** comm_out, int nranks, const void* id, int rank) 
   int rc = nccl_result(ncclCommInitRank(&comm, nranks, *static_cast<const ncclUniqueId*>(id), rank), "ncclCommInitRank");
   *comm_out = comm;
   return rc;
+}
+
+int cb200_nccl_comm_init_timeout(void** comm_out, int nranks, const void* id, int rank, int timeout_ms) {
+  if (comm_out == nullptr || id == nullptr || nranks < 1 || rank < 0 || rank >= nranks || timeout_ms < 0)
+    return fail(CB200_E_INVALID_ARGUMENT, "cb200_nccl_comm_init_timeout: bad arguments");
+  *comm_out = nullptr;
+  ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+  config.blocking = 0;
+  ncclComm_t comm = nullptr;
+  ncclResult_t r = ncclCommInitRankConfig(&comm, nranks, *static_cast<const ncclUniqueId*>(id), rank, &config);
+  if (r != ncclSuccess && r != ncclInProgress) return nccl_result(r, "ncclCommInitRankConfig");
+  int rc = comm != nullptr ? nccl_settle(comm, ncclInProgress, "ncclCommInitRankConfig", timeout_ms)
+                           : fail(CB200_E_NCCL, "ncclCommInitRankConfig returned no communicator");
+  if (rc != CB200_OK) {
+    // a peer is missing (or NCCL failed): give the half-built communicator back, keep the message
+    if (comm != nullptr) ncclCommAbort(comm);
+    if (rc == CB200_E_TIMEOUT)
+      return fail(rc, "cb200_nccl_comm_init_timeout: rank %d of %d: the ranks did not all join within %d ms", rank,
+                  nranks, timeout_ms);
+    return rc;
+  }
+  *comm_out = comm;
+  return CB200_OK;
 }
 
 int cb200_nccl_comm_destroy(void* comm) {

@@ -84,6 +84,7 @@ extern "C" {
 #define CB200_E_CUDA -3
 #define CB200_E_NCCL -4
 #define CB200_E_UNSUPPORTED_SHAPE -5
+#define CB200_E_TIMEOUT -6 /* a host-side wait with a deadline ran out (communicator setup) */
 
 /* cb200_status.code */
 #define CB200_STATUS_OK 0

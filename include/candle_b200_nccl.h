@@ -27,6 +27,18 @@ CB200_API int cb200_nccl_comm_init(void** comm_out, int nranks, const void* id, 
 CB200_API int cb200_nccl_comm_destroy(void* comm);
 
 /*
+ * ncclCommInitRank with a deadline.  The reference's set-up blocks for as long as a peer is missing
+ * (its ranks poll for the id file forever, llama_multiprocess/main.rs:156-158, and
+ * `Comm::from_rank` then waits inside NCCL); here the communicator is created in NCCL's
+ * non-blocking mode and polled on the host: if the ranks have not all joined within `timeout_ms`
+ * the half-built communicator is aborted, *comm_out stays NULL and CB200_E_TIMEOUT is returned --
+ * the caller can report the missing peer and retry or leave.  No device work is involved.  A
+ * communicator made this way stays non-blocking; the sharded entry points below wait (on the host,
+ * with the same kind of deadline) until NCCL has accepted their collective.
+ */
+CB200_API int cb200_nccl_comm_init_timeout(void** comm_out, int nranks, const void* id, int rank, int timeout_ms);
+
+/*
  * Vocabulary-sharded cb200_qembedding -> sum over ranks -> rms_norm, enqueued on `stream`:
  *   scratch = masked lookup of ALL ids in this rank's rows [vocab_begin, vocab_end) (-0.0 elsewhere)
  *   scratch = ncclAllReduce(scratch, sum)            (exact: one non-zero contributor per element)

@@ -71,7 +71,8 @@ def test_rust_ffi_declares_the_same_entry_points():
     for m in re.finditer(r"pub fn (cb200_\w+)\s*\(([^;]*?)\)\s*(?:->\s*[\w\s\*:]+)?;", text, flags=re.S):
         params = m.group(2).strip()
         rust[m.group(1)] = 0 if not params else len([p for p in params.split(",") if p.strip()])
-    skipped = {"cb200_selftest_wait_expiry", "cb200_nccl_unique_id", "cb200_nccl_comm_init", "cb200_nccl_comm_destroy"}
+    skipped = {"cb200_selftest_wait_expiry", "cb200_nccl_unique_id", "cb200_nccl_comm_init", "cb200_nccl_comm_init_timeout",
+               "cb200_nccl_comm_destroy"}
     declared = {k: v for k, v in header_functions().items() if k not in skipped}
     assert set(rust) == set(declared), set(rust) ^ set(declared)
     for name, n in declared.items():
