@@ -20,6 +20,18 @@ def kats():
         return json.load(f)
 
 
+@pytest.fixture(scope="session")
+def cb():
+    """The package under test, for the GPU tests: there is no CPU path to fall back on."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import candle_b200
+
+    return candle_b200
+
+
 def round4(a):
     """candle's test_utils::to_vec*_round(t, 4): f32::round(t * 1e4) / 1e4 evaluated in f32."""
     a = np.asarray(a, dtype=np.float32)

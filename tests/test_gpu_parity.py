@@ -14,15 +14,6 @@ pytestmark = pytest.mark.gpu
 TOL = {"f32": 1e-5, "f16": 1e-2, "bf16": 1e-2}
 
 
-@pytest.fixture(scope="module")
-def cb():
-    if not torch.cuda.is_available():
-        pytest.skip("needs a CUDA device")
-    import candle_b200
-
-    return candle_b200
-
-
 def assert_norm_equal(got: torch.Tensor, want: np.ndarray, dtype: str):
     g = to_oracle(got)
     gf, wf = oracle.cast_to_f32(g, dtype), oracle.cast_to_f32(want, dtype)

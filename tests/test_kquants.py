@@ -142,15 +142,6 @@ def test_oracle_decoders_against_numpy_statement(qtype):
 # ------------------------------------------------------------------------------------------------
 # GPU
 # ------------------------------------------------------------------------------------------------
-@pytest.fixture(scope="module")
-def cb():
-    if not torch.cuda.is_available():
-        pytest.skip("needs a CUDA device")
-    import candle_b200
-
-    return candle_b200
-
-
 @pytest.mark.gpu
 @pytest.mark.parametrize("qtype", KQ)
 def test_gpu_dequantize_kats_and_random_blocks(cb, kats, qtype):

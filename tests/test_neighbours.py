@@ -72,15 +72,6 @@ def test_rope_fused_equals_slow_on_the_oracle(kats, name):
 # ------------------------------------------------------------------------------------------------
 # GPU
 # ------------------------------------------------------------------------------------------------
-@pytest.fixture(scope="module")
-def cb():
-    if not torch.cuda.is_available():
-        pytest.skip("needs a CUDA device")
-    import candle_b200
-
-    return candle_b200
-
-
 @pytest.mark.gpu
 def test_gpu_softmax_kats(cb, kats):
     k = kats["softmax"]

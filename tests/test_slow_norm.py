@@ -96,15 +96,6 @@ def test_slow_chain_against_numpy_statement():
 # ------------------------------------------------------------------------------------------------
 # GPU
 # ------------------------------------------------------------------------------------------------
-@pytest.fixture(scope="module")
-def cb():
-    if not torch.cuda.is_available():
-        pytest.skip("needs a CUDA device")
-    import candle_b200
-
-    return candle_b200
-
-
 def check(got: torch.Tensor, want: np.ndarray, dtype: str):
     g = to_oracle(got)
     assert np.abs(oracle.cast_to_f32(g, dtype) - oracle.cast_to_f32(want, dtype)).max() <= TOL[dtype]

@@ -18,15 +18,6 @@ pytestmark = pytest.mark.gpu
 WAIT_TIMEOUT = 2
 
 
-@pytest.fixture(scope="module")
-def cb():
-    if not torch.cuda.is_available():
-        pytest.skip("needs a CUDA device")
-    import candle_b200
-
-    return candle_b200
-
-
 def expire_then_recover(cb, run, want):
     """run(status) -> output tensor.  First with every wait forced to run out, then normally."""
     from candle_b200 import _cabi
