@@ -406,6 +406,111 @@ def brief_workload(name, dev, stream, st, timed, peak, **kw):
     return out, ok
 
 
+def next_rows_section(dev, timed, peak):
+    """The operators next to the hot path (composite norm, softmax, rope, K-quant lookups, the norm
+    of selected rows), each briefly: parity against the oracle on rows of these very inputs, then 10
+    launches on inputs larger than L2."""
+    import torch
+
+    import oracle
+    from candle_b200 import ops
+    from candle_b200.quantized import GgmlDType, QTensor
+    from helpers import from_oracle, ids_tensor, make_kq_blocks, randn, to_oracle
+
+    rng = np.random.default_rng(SEED + 1)
+    out, all_ok = {}, True
+
+    def entry(name, desc, fn, nbytes, ok, how):
+        nonlocal all_ok
+        k = 10
+        ms = timed(lambda i: fn(), k, 3) / k
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"workload": desc, "us_per_step": ms * 1e3, "achieved_gbs": gbs, "frac_of_measured_peak": gbs / peak,
+                     "algorithmic_bytes_per_launch": nbytes, "parity": how if ok else "MISMATCH"}
+        all_ok = all_ok and ok
+        torch.cuda.empty_cache()
+
+    def tiled(block, reps):  # a seeded block repeated: parity is checked on the first block
+        return from_oracle(block, "bf16", dev).repeat(reps, 1)
+
+    # ---- candle's composite norm chain (layer_norm.rs:108-136), bf16 ----
+    rows, hidden, base = 65536, 4096, 512
+    xb = randn(rng, (base, hidden), "bf16")
+    w, b = randn(rng, (hidden,), "bf16", 1.0, 0.1), randn(rng, (hidden,), "bf16", 0.0, 0.1)
+    x, tw, tb = tiled(xb, rows // base), from_oracle(w, "bf16", dev), from_oracle(b, "bf16", dev)
+    for name, bias, rm in (("rms_norm_slow", None, False), ("layer_norm_slow", b, True)):
+        f = (lambda: ops.rms_norm_slow(x, tw, 1e-5)) if bias is None else (lambda: ops.layer_norm_slow(x, tw, tb, 1e-5))
+        ok = np.array_equal(to_oracle(f()[:base]), oracle.norm_slow(xb, w, bias, 1e-5, "bf16", remove_mean=rm))
+        entry(name, f"candle's composite norm chain, bf16, {rows} x {hidden}", f, 2 * rows * hidden * 2, ok,
+              f"bit-exact vs CPU oracle on {base} rows")
+    del x
+    # ---- softmax over the last dimension ----
+    rows, n, base = 65536, 2048, 256
+    for dt in ("f32", "bf16"):
+        xb = randn(rng, (base, n), dt, 0.0, 3.0)
+        x = from_oracle(xb, dt, dev).repeat(rows // base, 1)
+        got = oracle.cast_to_f32(to_oracle(ops.softmax_last_dim(x)[:base]), dt)
+        want = oracle.cast_to_f32(oracle.softmax_last_dim(xb, dt), dt)
+        tol = 1e-5 if dt == "f32" else 1e-2
+        es = 4 if dt == "f32" else 2
+        entry(f"softmax_last_dim_{dt}", f"softmax over the last dimension, {dt}, {rows} x {n}",
+              lambda: ops.softmax_last_dim(x), 2 * rows * n * es, bool(np.abs(got - want).max() <= tol),
+              f"max |diff| {float(np.abs(got - want).max()):.2e} <= {tol} vs CPU oracle on {base} rows (exp from two math libraries)")
+        del x
+    # ---- rotary embeddings ----
+    bsz, h, t, d = 8, 32, 2048, 128
+    cos, sin = randn(rng, (t, d // 2), "bf16"), randn(rng, (t, d // 2), "bf16")
+    tc, ts = from_oracle(cos, "bf16", dev), from_oracle(sin, "bf16", dev)
+    for variant in ("rope_i", "rope", "rope_thd"):
+        shape1 = (1, t, h, d) if variant == "rope_thd" else (1, h, t, d)
+        xb = randn(rng, shape1, "bf16")
+        x = from_oracle(xb, "bf16", dev).repeat(bsz, 1, 1, 1)
+        f = getattr(ops, variant)
+        ok = np.array_equal(to_oracle(f(x, tc, ts)[:1]), oracle.rope(variant, xb, cos, sin, "bf16"))
+        entry(variant, f"{variant}, bf16, b {bsz} h {h} t {t} d {d}", lambda: f(x, tc, ts), 2 * x.numel() * 2, ok,
+              "bit-exact vs CPU oracle on one batch element")
+        del x
+    # ---- lookups from K-quant tables ----
+    vocab, hidden, n_ids, sample = 8192, 4096, 65536, 512
+    ids = rng.integers(0, vocab, size=n_ids).astype(np.uint32)
+    tids = ids_tensor(ids, dev)
+    alpha = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+    ta = from_oracle(alpha, "bf16", dev)
+    for qname in ("q4k", "q6k"):
+        gq = getattr(GgmlDType, qname.upper())
+        raw = make_kq_blocks(rng, qname, vocab * hidden // 256).reshape(vocab, -1)
+        q = QTensor.from_raw(torch.from_numpy(raw), gq, (vocab, hidden), device=dev)
+        rows_q = oracle.qembedding(raw, qname, ids[:sample], "bf16")
+        ok = np.array_equal(to_oracle(q.embedding(tids, torch.bfloat16)[:sample]), rows_q)
+        entry(f"qembedding_{qname}", f"lookup from a {qname.upper()} table {vocab} x {hidden} -> bf16, {n_ids} ids",
+              lambda: q.embedding(tids, torch.bfloat16, check=False), n_ids * (raw.shape[1] + hidden * 2), ok,
+              f"bit-exact vs CPU oracle on {sample} rows")
+        ok = np.array_equal(to_oracle(ops.qembedding_rms_norm(q, tids, ta, 1e-5)[:sample]),
+                            oracle.rms_norm(rows_q, alpha, 1e-5, "bf16"))
+        entry(f"qembedding_rms_norm_{qname}", f"the same lookup + RMS norm (two launches: lookup into y, norm in place)",
+              lambda: ops.qembedding_rms_norm(q, tids, ta, 1e-5, check=False), n_ids * (raw.shape[1] + hidden * 2), ok,
+              f"bit-exact vs CPU oracle on {sample} rows")
+        del q
+    # ---- the norm of selected rows (the final norm feeds one token per sequence into the LM head) ----
+    rows, hidden, picks = 16384, 8192, 64
+    xb = randn(rng, (512, hidden), "bf16")
+    x = tiled(xb, rows // 512)
+    alpha = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+    ta = from_oracle(alpha, "bf16", dev)
+    sel = np.sort(rng.choice(rows, size=picks, replace=False)).astype(np.int64)
+    tsel = torch.from_numpy(sel).to(dev)
+    ok = np.array_equal(to_oracle(ops.rms_norm_rows(x, tsel, ta, 1e-5)), oracle.rms_norm(xb[sel % 512], alpha, 1e-5, "bf16"))
+    k = 20
+    ms_sel = timed(lambda i: ops.rms_norm_rows(x, tsel, ta, 1e-5, check=False), k, 3) / k
+    ms_all = timed(lambda i: ops.rms_norm(x, ta, 1e-5), k, 3) / k
+    out["rms_norm_selected_rows"] = {
+        "workload": f"RMS norm bf16 of {picks} selected rows of {rows} x {hidden} (candle norms all rows, then slices)",
+        "us_per_step": ms_sel * 1e3, "us_per_step_all_rows": ms_all * 1e3,
+        "parity": f"bit-exact vs CPU oracle on the {picks} rows" if ok else "MISMATCH"}
+    all_ok = all_ok and ok
+    return out, all_ok
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -493,6 +598,8 @@ def gpu_arm(args):
                 ladder[str(rows)], ok2 = brief_workload("c5", dev, stream, st, timed, peak, rows_scale=rows / 65536)
                 parity_ok = parity_ok and ok2
             others["c5_rows"] = ladder
+            others["next_rows"], ok2 = next_rows_section(dev, timed, peak)
+            parity_ok = parity_ok and ok2
         else:
             if wl.name == "c5" and args.rows_scale == 1.0:
                 # strong scaling: the 65536 rows of the configuration split over the ranks

@@ -114,6 +114,34 @@ __device__ __forceinline__ void store_elem<kDtF16>(void* p, int64_t i, float v) 
   static_cast<__half*>(p)[i] = __float2half_rn(v);
 }
 
+// One 16-byte vector <-> its elements widened to f32 (floats_to_vec rounds to T).
+template <int DT>
+__device__ __forceinline__ void vec_to_floats(const uint4& q, float (&f)[Elem<DT>::kPerVec]) {
+  if constexpr (DT == kDtF32) {
+    f[0] = __uint_as_float(q.x);
+    f[1] = __uint_as_float(q.y);
+    f[2] = __uint_as_float(q.z);
+    f[3] = __uint_as_float(q.w);
+  } else {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = unpack2<DT>(w[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+template <int DT>
+__device__ __forceinline__ uint4 floats_to_vec(const float (&f)[Elem<DT>::kPerVec]) {
+  if constexpr (DT == kDtF32) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  } else {
+    return make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
+  }
+}
+
 // The -0.0 bit pattern of T replicated over a 16-byte vector (additive identity that keeps -0.0).
 template <int DT>
 __device__ __forceinline__ uint4 neg_zero_vec() {

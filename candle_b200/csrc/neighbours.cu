@@ -49,6 +49,110 @@ __device__ __forceinline__ float exp_correctly_rounded(float v) {
   return static_cast<float>(exp(static_cast<double>(v)));
 }
 
+// exp(v) rounded once to f32 at a fraction of the cost of the library's double-precision exp, for the
+// arguments a softmax produces (v = x - max <= 0, results in the normal f32 range):
+//   v = k ln2/32 + r, |r| <= ln2/64;  exp(v) = 2^(k >> 5) * 2^((k & 31)/32) * exp(r)
+// in double precision with a 32-entry table of 2^(j/32) (shared memory, filled by the CTA) and a
+// degree-5 polynomial for exp(r) - 1 (truncation 2^-48.7).  The double result is good to well under
+// 2^-46, so rounding it to f32 gives the correctly rounded value unless its 29 discarded fraction
+// bits lie within 2^-42 (relative) of the half-way pattern; those arguments (about 4 in a million) and
+// everything outside [-87, 88] -- subnormal results, NaN -- take the library path.
+struct ExpTable {
+  const double* pow2;  // [32] 2^(j/32)
+};
+__device__ __forceinline__ void fill_exp_table(double* table) {
+  if (threadIdx.x < 32) table[threadIdx.x] = exp2(static_cast<double>(threadIdx.x) * 0.03125);
+}
+__device__ __forceinline__ float exp_rounded_once(float v, const ExpTable& tab) {
+  if (!(v >= -87.0f && v <= 88.0f)) return exp_correctly_rounded(v);
+  const double x = static_cast<double>(v);
+  constexpr double kShift = 6755399441055744.0;  // 1.5 * 2^52: adding it leaves round(t) in the low word
+  const double t = fma(x, 0x1.71547652b82fep+5, kShift);
+  const int k = __double2loint(t);
+  const double kd = t - kShift;
+  double r = fma(kd, -0x1.62e42fefa3000p-6, x);  // ln2/32, 41 significant bits: the product is exact
+  r = fma(kd, -0x1.3de6af278ece6p-47, r);
+  double p = fma(r, 1.0 / 120.0, 1.0 / 24.0);
+  p = fma(p, r, 1.0 / 6.0);
+  p = fma(p, r, 0.5);
+  p = fma(p * r, r, r);  // exp(r) - 1
+  const double T = tab.pow2[k & 31];
+  const double d = fma(T, p, T);
+  const long long bits = __double_as_longlong(d) + (static_cast<long long>(k >> 5) << 52);
+  const int low = static_cast<int>(static_cast<unsigned>(bits) & 0x1FFFFFFFu);  // the 29 bits f32 drops
+  if (abs(low - (1 << 28)) < 1024) return exp_correctly_rounded(v);
+  return static_cast<float>(__longlong_as_double(bits));
+}
+
+// Rows that are whole 16-byte vectors: a warp per row, the row staged in the warp's own shared-memory
+// buffer (16-byte global accesses only, all loads of a row in flight at once); max, exp + AVX-order sum
+// and the division run on shared memory with lane l on elements l, l + 32, ...
+constexpr int kSoftmaxStagedMaxWarps = 24;
+__global__ void __launch_bounds__(kSoftmaxStagedMaxWarps * 32) softmax_f32_staged_kernel(const uint4* __restrict__ x,
+                                                                                        uint4* __restrict__ y,
+                                                                                        int64_t rows, int n, int pitch) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* table = reinterpret_cast<double*>(smem_raw);
+  fill_exp_table(table);
+  __syncthreads();
+  const ExpTable tab{table};
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  float* buf = reinterpret_cast<float*>(smem_raw + 256 + static_cast<size_t>(wib) * pitch);
+  uint4* bufv = reinterpret_cast<uint4*>(buf);
+  const int V = n / 4;
+  const int np = n & ~31;
+  constexpr int U = 8;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * warps + wib; row < rows;
+       row += static_cast<int64_t>(gridDim.x) * warps) {
+    const uint4* xr = x + row * V;
+    float m = __int_as_float(0xff800000);  // -inf; every row has at least one element
+    for (int v0 = lane; v0 < V; v0 += 32 * U) {
+      uint4 q[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (v0 + 32 * u < V) q[u] = ldg_stream(xr + v0 + 32 * u);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (v0 + 32 * u < V) {
+          bufv[v0 + 32 * u] = q[u];
+          m = max_ignoring_nan(m, max_ignoring_nan(max_ignoring_nan(__uint_as_float(q[u].x), __uint_as_float(q[u].y)),
+                                                   max_ignoring_nan(__uint_as_float(q[u].z), __uint_as_float(q[u].w))));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max_ignoring_nan(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    __syncwarp();
+    float acc = 0.0f;
+#pragma unroll 2
+    for (int i = lane; i < np; i += 32) {
+      const float e = exp_rounded_once(__fsub_rn(buf[i], m), tab);
+      buf[i] = e;
+      acc = __fadd_rn(acc, e);
+    }
+    float sum = avx_fold(acc);
+    float tail = 0.0f;
+    if (np + lane < n) {
+      tail = exp_rounded_once(__fsub_rn(buf[np + lane], m), tab);
+      buf[np + lane] = tail;
+    }
+    for (int i = 0; i < n - np; ++i) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, tail, i));
+    __syncwarp();
+    // the division has no order to keep: 16 bytes per lane, exact three-instruction division by the sum
+    const RowDivisor dv = make_row_divisor(sum);
+    uint4* yr = y + row * V;
+#pragma unroll 2
+    for (int v = lane; v < V; v += 32) {
+      const uint4 q = bufv[v];
+      stg_stream(yr + v, make_uint4(__float_as_uint(div_by_row(__uint_as_float(q.x), dv)),
+                                    __float_as_uint(div_by_row(__uint_as_float(q.y), dv)),
+                                    __float_as_uint(div_by_row(__uint_as_float(q.z), dv)),
+                                    __float_as_uint(div_by_row(__uint_as_float(q.w), dv))));
+    }
+    __syncwarp();  // the buffer is refilled by the next row's loads
+  }
+}
+
+// Any row length and alignment: scalar accesses on global memory, the library's exp.
 __global__ void __launch_bounds__(kSoftmaxThreads) softmax_f32_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                                       int64_t rows, int n) {
   const int lane = threadIdx.x & 31;
@@ -261,60 +365,128 @@ __global__ void __launch_bounds__(256) rope_scalar_kernel(const void* __restrict
   }
 }
 
-// Vector form for the half-split variants (rope, rope_thd): a thread takes one 16-byte vector of the
-// first half of a row and its partner in the second half.  Needs d/2 to be a whole number of vectors
-// and 16-byte aligned tensors.
+// Vector forms.  16-bit types use the packed T-rounding instructions: mul.rn / add.rn on two values at
+// a time round each product and each sum once to T, which is what candle's `half` arithmetic does
+// (it widens to f32, where the product of two 16-bit values is exact and the double rounding of a
+// sum is innocuous, then rounds to T).  x - y is computed as x + (-y), the same value.
+template <int DT>
+__device__ __forceinline__ uint32_t neg2(uint32_t a) { return a ^ 0x80008000u; }
+
+// Half-split variants (rope, rope_thd): an item is one 16-byte vector of the first half of a row and
+// its partner in the second half; cos / sin are the matching vector of row `it`.
+template <int DT>
+__device__ __forceinline__ void rope_split_item(const uint4& a, const uint4& b, const uint4& c, const uint4& s, uint4& r1,
+                                                uint4& r2) {
+  const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w}, wc[4] = {c.x, c.y, c.z, c.w},
+                 ws[4] = {s.x, s.y, s.z, s.w};
+  uint32_t o1[4], o2[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (DT == kDtF32) {
+      float y1, y2;
+      rope_pair<DT>(__uint_as_float(wa[i]), __uint_as_float(wb[i]), __uint_as_float(wc[i]), __uint_as_float(ws[i]), y1, y2);
+      o1[i] = __float_as_uint(y1);
+      o2[i] = __float_as_uint(y2);
+    } else {
+      o1[i] = add2_rn<DT>(mul2_rn<DT>(wa[i], wc[i]), neg2<DT>(mul2_rn<DT>(wb[i], ws[i])));
+      o2[i] = add2_rn<DT>(mul2_rn<DT>(wa[i], ws[i]), mul2_rn<DT>(wb[i], wc[i]));
+    }
+  }
+  r1 = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+  r2 = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+}
+
+// Two items per thread and trip, all loads first.
 template <int DT, int VARIANT>
 __global__ void __launch_bounds__(256) rope_split_vec_kernel(const uint4* __restrict__ src, const uint4* __restrict__ cos_,
                                                              const uint4* __restrict__ sin_, uint4* __restrict__ dst,
                                                              int64_t n_items, int h, int t, int hv) {
-  constexpr int PV = Elem<DT>::kPerVec;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < n_items; p += stride) {
-    const int64_t rowi = p / hv;
-    const int k = static_cast<int>(p - rowi * hv);
-    const int it = VARIANT == kRopeThd ? static_cast<int>((rowi / h) % t) : static_cast<int>(rowi % t);
-    const int64_t v1 = rowi * 2 * hv + k, v2 = v1 + hv;
-    const uint4 a = ldg_stream(src + v1), b = ldg_stream(src + v2);
-    const uint4 c = __ldg(cos_ + static_cast<int64_t>(it) * hv + k), s = __ldg(sin_ + static_cast<int64_t>(it) * hv + k);
-    float fa[PV], fb[PV], fc[PV], fs[PV], o1[PV], o2[PV];
-    if constexpr (DT == kDtF32) {
-      const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w}, wc[4] = {c.x, c.y, c.z, c.w},
-                     ws[4] = {s.x, s.y, s.z, s.w};
+  for (int64_t p0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p0 < n_items; p0 += 2 * stride) {
+    uint4 a[2], b[2], c[2], s[2];
+    int64_t v1[2];
+    bool live[2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        fa[i] = __uint_as_float(wa[i]);
-        fb[i] = __uint_as_float(wb[i]);
-        fc[i] = __uint_as_float(wc[i]);
-        fs[i] = __uint_as_float(ws[i]);
-      }
-    } else {
-      const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w}, wc[4] = {c.x, c.y, c.z, c.w},
-                     ws[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 t2 = unpack2<DT>(wa[i]);
-        fa[2 * i] = t2.x, fa[2 * i + 1] = t2.y;
-        t2 = unpack2<DT>(wb[i]);
-        fb[2 * i] = t2.x, fb[2 * i + 1] = t2.y;
-        t2 = unpack2<DT>(wc[i]);
-        fc[2 * i] = t2.x, fc[2 * i + 1] = t2.y;
-        t2 = unpack2<DT>(ws[i]);
-        fs[2 * i] = t2.x, fs[2 * i + 1] = t2.y;
-      }
+    for (int u = 0; u < 2; ++u) {
+      const int64_t p = p0 + u * stride;
+      live[u] = p < n_items;
+      const int64_t pp = live[u] ? p : p0;
+      const int64_t rowi = pp / hv;
+      const int k = static_cast<int>(pp - rowi * hv);
+      const int it = VARIANT == kRopeThd ? static_cast<int>((rowi / h) % t) : static_cast<int>(rowi % t);
+      v1[u] = rowi * 2 * hv + k;
+      a[u] = ldg_stream(src + v1[u]);
+      b[u] = ldg_stream(src + v1[u] + hv);
+      c[u] = __ldg(cos_ + static_cast<int64_t>(it) * hv + k);
+      s[u] = __ldg(sin_ + static_cast<int64_t>(it) * hv + k);
     }
 #pragma unroll
-    for (int i = 0; i < PV; ++i) rope_pair<DT>(fa[i], fb[i], fc[i], fs[i], o1[i], o2[i]);
-    uint4 r1, r2;
-    if constexpr (DT == kDtF32) {
-      r1 = make_uint4(__float_as_uint(o1[0]), __float_as_uint(o1[1]), __float_as_uint(o1[2]), __float_as_uint(o1[3]));
-      r2 = make_uint4(__float_as_uint(o2[0]), __float_as_uint(o2[1]), __float_as_uint(o2[2]), __float_as_uint(o2[3]));
-    } else {
-      r1 = make_uint4(pack2<DT>(o1[0], o1[1]), pack2<DT>(o1[2], o1[3]), pack2<DT>(o1[4], o1[5]), pack2<DT>(o1[6], o1[7]));
-      r2 = make_uint4(pack2<DT>(o2[0], o2[1]), pack2<DT>(o2[2], o2[3]), pack2<DT>(o2[4], o2[5]), pack2<DT>(o2[6], o2[7]));
+    for (int u = 0; u < 2; ++u) {
+      if (!live[u]) continue;
+      uint4 r1, r2;
+      rope_split_item<DT>(a[u], b[u], c[u], s[u], r1, r2);
+      stg_stream(dst + v1[u], r1);
+      stg_stream(dst + v1[u] + hv, r2);
     }
-    stg_stream(dst + v1, r1);
-    stg_stream(dst + v2, r2);
+  }
+}
+
+// Interleaved variant (rope_i): an item is one 16-byte vector of a row, i.e. PV / 2 adjacent pairs
+// (x1, x2); cos / sin contribute PV / 2 values, 8 bytes.  16-bit: a word is one pair; with cc = (c, c)
+// and ss = (s, s), P = w * cc = (x1 c, x2 c), Q = w * ss = (x1 s, x2 s) and the result is
+// (P.lo - Q.hi, P.hi + Q.lo) = P + (-Q.hi, Q.lo).
+template <int DT>
+__device__ __forceinline__ uint4 rope_interleaved_item(const uint4& x, const uint2& c, const uint2& s) {
+  const uint32_t wx[4] = {x.x, x.y, x.z, x.w};
+  uint32_t o[4];
+  if constexpr (DT == kDtF32) {
+    const uint32_t wc[2] = {c.x, c.y}, ws[2] = {s.x, s.y};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float y1, y2;
+      rope_pair<DT>(__uint_as_float(wx[2 * i]), __uint_as_float(wx[2 * i + 1]), __uint_as_float(wc[i]),
+                    __uint_as_float(ws[i]), y1, y2);
+      o[2 * i] = __float_as_uint(y1);
+      o[2 * i + 1] = __float_as_uint(y2);
+    }
+  } else {
+    const uint32_t wc[2] = {c.x, c.y}, ws[2] = {s.x, s.y};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t sel = (i & 1) ? 0x3232u : 0x1010u;
+      const uint32_t cc = __byte_perm(wc[i >> 1], 0u, sel), ss = __byte_perm(ws[i >> 1], 0u, sel);
+      const uint32_t P = mul2_rn<DT>(wx[i], cc), Q = mul2_rn<DT>(wx[i], ss);
+      o[i] = add2_rn<DT>(P, __byte_perm(Q, 0u, 0x1032u) ^ 0x00008000u);
+    }
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) rope_interleaved_vec_kernel(const uint4* __restrict__ src,
+                                                                   const uint2* __restrict__ cos_,
+                                                                   const uint2* __restrict__ sin_, uint4* __restrict__ dst,
+                                                                   int64_t n_items, int t, int V) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t p0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p0 < n_items; p0 += 4 * stride) {
+    uint4 x[4];
+    uint2 c[4], s[4];
+    bool live[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t p = p0 + u * stride;
+      live[u] = p < n_items;
+      const int64_t pp = live[u] ? p : p0;
+      const int64_t rowi = pp / V;  // row of d elements: (b, h, t)
+      const int k = static_cast<int>(pp - rowi * V);
+      const int64_t ics = (rowi % t) * V + k;
+      x[u] = ldg_stream(src + pp);
+      c[u] = __ldg(cos_ + ics);
+      s[u] = __ldg(sin_ + ics);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (live[u]) stg_stream(dst + p0 + u * stride, rope_interleaved_item<DT>(x[u], c[u], s[u]));
   }
 }
 
@@ -327,14 +499,25 @@ cudaError_t launch_rope_t(const void* src, const void* cos_, const void* sin_, v
   if (n_pairs == 0) return cudaSuccess;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   constexpr int PV = Elem<DT>::kPerVec;
-  if (VARIANT != kRopeI && (d / 2) % PV == 0 && aligned16(src) && aligned16(cos_) && aligned16(sin_) && aligned16(dst)) {
+  const bool aligned = aligned16(src) && aligned16(cos_) && aligned16(sin_) && aligned16(dst);
+  if (VARIANT != kRopeI && (d / 2) % PV == 0 && aligned) {
     const int hv = d / 2 / PV;
     const int64_t n_items = b * h * t * hv;
-    int64_t grid = (n_items + 255) / 256;
+    int64_t grid = (n_items + 511) / 512;
     if (grid > cap) grid = cap;
     rope_split_vec_kernel<DT, VARIANT><<<static_cast<unsigned>(grid), 256, 0, stream>>>(
         static_cast<const uint4*>(src), static_cast<const uint4*>(cos_), static_cast<const uint4*>(sin_),
         static_cast<uint4*>(dst), n_items, h, t, hv);
+    return cudaGetLastError();
+  }
+  if (VARIANT == kRopeI && d % PV == 0 && aligned) {
+    const int V = d / PV;
+    const int64_t n_items = b * h * t * V;
+    int64_t grid = (n_items + 1023) / 1024;
+    if (grid > cap) grid = cap;
+    rope_interleaved_vec_kernel<DT><<<static_cast<unsigned>(grid), 256, 0, stream>>>(
+        static_cast<const uint4*>(src), static_cast<const uint2*>(cos_), static_cast<const uint2*>(sin_),
+        static_cast<uint4*>(dst), n_items, t, V);
     return cudaGetLastError();
   }
   int64_t grid = (n_pairs + 255) / 256;
@@ -390,6 +573,24 @@ cudaError_t launch_softmax16(const void* x, void* y, int64_t rows, int n, cudaSt
 cudaError_t launch_softmax_last_dim(int dtype, const void* x, void* y, int64_t rows, int n, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   if (dtype == kDtF32) {
+    const size_t row_bytes = static_cast<size_t>(n) * 4;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0;
+    if (aligned && row_bytes % 16 == 0 && row_bytes <= 96 * 1024) {
+      int warps = static_cast<int>((200 * 1024) / row_bytes);
+      if (warps > kSoftmaxStagedMaxWarps) warps = kSoftmaxStagedMaxWarps;
+      const size_t smem = 256 + static_cast<size_t>(warps) * row_bytes;
+      auto kern = softmax_f32_staged_kernel;
+      int per_sm = 1;
+      cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), warps * 32, smem,
+                                           static_cast<int>((2 * (smem + 1024) * 100) / (228 * 1024) + 1), &per_sm);
+      if (e != cudaSuccess) return e;
+      int64_t grid = (rows + warps - 1) / warps;
+      const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm;
+      if (grid > cap) grid = cap;
+      kern<<<static_cast<unsigned>(grid), warps * 32, smem, stream>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y),
+                                                                     rows, n, static_cast<int>(row_bytes));
+      return cudaGetLastError();
+    }
     int64_t grid = (rows + 7) / 8;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     if (grid > cap) grid = cap;

@@ -24,33 +24,6 @@ namespace cb200 {
 constexpr int kLaneRowThreads = 256;
 constexpr int kLaneRowWarps = kLaneRowThreads / 32;
 
-template <int DT>
-__device__ __forceinline__ void vec_to_floats(const uint4& q, float (&f)[Elem<DT>::kPerVec]) {
-  if constexpr (DT == kDtF32) {
-    f[0] = __uint_as_float(q.x);
-    f[1] = __uint_as_float(q.y);
-    f[2] = __uint_as_float(q.z);
-    f[3] = __uint_as_float(q.w);
-  } else {
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 t = unpack2<DT>(w[i]);
-      f[2 * i] = t.x;
-      f[2 * i + 1] = t.y;
-    }
-  }
-}
-
-template <int DT>
-__device__ __forceinline__ uint4 floats_to_vec(const float (&f)[Elem<DT>::kPerVec]) {
-  if constexpr (DT == kDtF32) {
-    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
-  } else {
-    return make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
-  }
-}
-
 template <int DT, int OP>
 __global__ void __launch_bounds__(kLaneRowThreads) norm_lanerow_kernel(const LaneRowArgs a) {
   constexpr int PV = Elem<DT>::kPerVec;

@@ -213,6 +213,7 @@ struct QSlot {
 
 constexpr int kOwnerNone = 0, kOwnerToAll = 1, kOwnerToRowOwner = 2;
 
+
 template <int QT, int DT, int HB, int OWNER>
 __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, int stages) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -228,19 +229,24 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
 
   // row-invariant: this thread's alpha vectors and the position weights n - 16 p of its half blocks
   // (with eight half blocks per thread alpha does not fit and is re-read through L1)
+  // Half block j of this thread: interleaved over the slot's threads, so that a warp's 16-byte stores
+  // are contiguous.  (Giving each thread HB consecutive half blocks makes the 32-bit block loads
+  // conflict-free -- lanes 17 words apart -- but spreads a lane's stores 128 bytes apart: measured
+  // 252 us against 215 us on the Q8_0 lookup of 65536 rows of 4096 columns.)
+  auto half_block = [&](int j) -> int { return j * tpr + tx; };
   constexpr bool ALPHA_REGS = HB <= 4;
   uint4 al[ALPHA_REGS ? 2 * HB : 1];
   float wj[HB];
 #pragma unroll
   for (int j = 0; j < HB; ++j) {
-    const int p = j * tpr + tx;
+    const int p = half_block(j);
     if (ALPHA_REGS) {
       al[2 * j] = __ldg(a.alpha + 2 * p);
       al[2 * j + 1] = __ldg(a.alpha + 2 * p + 1);
     }
     wj[j] = static_cast<float>(a.n - 16 * p);
   }
-  auto alpha_vec = [&](int k) -> uint4 { return ALPHA_REGS ? al[ALPHA_REGS ? k : 0] : __ldg(a.alpha + 2 * ((k >> 1) * tpr + tx) + (k & 1)); };
+  auto alpha_vec = [&](int k) -> uint4 { return ALPHA_REGS ? al[ALPHA_REGS ? k : 0] : __ldg(a.alpha + 2 * half_block(k >> 1) + (k & 1)); };
 
   // without an id list the rows are taken in order (a dense source)
   auto row_id = [&](int64_t r) -> uint64_t {
@@ -321,7 +327,7 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
     if (kind == kRowDecode) {
 #pragma unroll
       for (int j = 0; j < HB; ++j) {
-        const int p = j * tpr + tx;
+        const int p = half_block(j);
         float d;
         decode_half_block<QT, DT>(buf, p, h[2 * j], h[2 * j + 1], d);
         accumulate_vec_w<DT>(h[2 * j], wj[j], lsum, lw);
@@ -344,7 +350,7 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
       m = replay_row<DT, QuantRow<QT, DT>>(QuantRow<QT, DT>{buf}, a.V, a.n, a.eps, sm);
 #pragma unroll
       for (int j = 0; j < HB; ++j) {  // nothing was kept in registers across the replay
-        const HalfBlockVecs hb = decode_half_block_cold<QT, DT>(buf, j * tpr + tx);
+        const HalfBlockVecs hb = decode_half_block_cold<QT, DT>(buf, half_block(j));
         h[2 * j] = hb.lo;
         h[2 * j + 1] = hb.hi;
       }
@@ -367,7 +373,7 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
         uint4* g = a.gathered + row * a.V;
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
-          const int p = j * tpr + tx;
+          const int p = half_block(j);
           stg_stream(g + 2 * p, h[2 * j]);
           stg_stream(g + 2 * p + 1, h[2 * j + 1]);
         }
@@ -409,21 +415,21 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
       if (QT == kQTypeDense16 && !plain) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
-          const int p = j * tpr + tx;
+          const int p = half_block(j);
           put(p, rms_output_vec<DT, true>(h[2 * j], alpha_vec(2 * j), m, r, fast_div),
               rms_output_vec<DT, true>(h[2 * j + 1], alpha_vec(2 * j + 1), m, r, fast_div));
         }
       } else if (plain) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
-          const int p = j * tpr + tx;
+          const int p = half_block(j);
           put(p, rms_output_plain<DT>(h[2 * j], alpha_vec(2 * j), m, r),
               rms_output_plain<DT>(h[2 * j + 1], alpha_vec(2 * j + 1), m, r));
         }
       } else {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
-          const int p = j * tpr + tx;
+          const int p = half_block(j);
           put(p, rms_output_rare<DT>(h[2 * j], alpha_vec(2 * j), m, r, fast_div),
               rms_output_rare<DT>(h[2 * j + 1], alpha_vec(2 * j + 1), m, r, fast_div));
         }

@@ -66,3 +66,27 @@ def make_qtable(rng, qtype: str, vocab: int, hidden: int) -> np.ndarray:
         parts.append(rng.integers(0, 256, size=(vocab, nb, 16), dtype=np.int16).astype(np.uint8))
     blocks = np.concatenate(parts, axis=2)
     return np.ascontiguousarray(blocks.reshape(vocab, -1))
+
+
+def _oracle():
+    import oracle
+
+    return oracle
+
+
+def make_kq_blocks(rng, qtype, n_blocks):
+    """Random but well-formed super-blocks: every byte uniform, the f16 / f32 scales |N(0, 0.01)|."""
+    bb = _oracle().BLOCK_BYTES[qtype]
+    raw = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.int16).astype(np.uint8)
+    d = np.abs(rng.standard_normal((n_blocks, 2)) * 0.01).astype(np.float16).view(np.uint8).reshape(n_blocks, 4)
+    if qtype == "q2k":
+        raw[:, 80:84] = d
+    elif qtype == "q3k":
+        raw[:, 108:110] = d[:, :2]
+    elif qtype in ("q4k", "q5k"):
+        raw[:, 0:4] = d
+    elif qtype == "q6k":
+        raw[:, 208:210] = d[:, :2]
+    else:
+        raw[:, 0:4] = np.abs(rng.standard_normal(n_blocks) * 0.01).astype(np.float32).view(np.uint8).reshape(n_blocks, 4)
+    return raw

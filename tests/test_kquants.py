@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import bits, from_oracle, ids_tensor, randn, to_oracle
+from helpers import bits, from_oracle, ids_tensor, make_kq_blocks, randn, to_oracle
 
 KQ = ["q2k", "q3k", "q4k", "q5k", "q6k", "q8k"]
 
@@ -45,24 +45,6 @@ def test_oracle_reproduces_candles_round_trip_vectors(kats, qtype):
     dg = oracle.dequantize(oracle.quantize(g, qtype), qtype)
     rmse = np.sqrt(np.sum((g - dg).astype(np.float32) ** 2, dtype=np.float32)) / np.float32(g.size)
     assert rmse <= k["ggml_max_rmse"]
-
-
-def make_kq_blocks(rng, qtype, n_blocks):
-    """Random but well-formed super-blocks: every byte uniform, the f16 / f32 scales |N(0, 0.01)|."""
-    bb = oracle.BLOCK_BYTES[qtype]
-    raw = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.int16).astype(np.uint8)
-    d = np.abs(rng.standard_normal((n_blocks, 2)) * 0.01).astype(np.float16).view(np.uint8).reshape(n_blocks, 4)
-    if qtype == "q2k":
-        raw[:, 80:84] = d
-    elif qtype == "q3k":
-        raw[:, 108:110] = d[:, :2]
-    elif qtype in ("q4k", "q5k"):
-        raw[:, 0:4] = d
-    elif qtype == "q6k":
-        raw[:, 208:210] = d[:, :2]
-    else:
-        raw[:, 0:4] = np.abs(rng.standard_normal(n_blocks) * 0.01).astype(np.float32).view(np.uint8).reshape(n_blocks, 4)
-    return raw
 
 
 @pytest.mark.parametrize("qtype", KQ)

@@ -108,6 +108,34 @@ def test_gpu_softmax_matches_oracle(cb, dtype, shape):
         assert same.mean() > 0.999, f"{(~same).sum()} of {same.size} elements differ"
 
 
+@pytest.mark.gpu
+def test_gpu_softmax_f32_staged_and_scalar_kernels_agree(cb):
+    # Two kernels, two ways to the once-rounded exp (a table-driven double-precision evaluation with a
+    # rounding check against the library's exp): bit-equal on rows whose x - max spans the whole range
+    # down to results that underflow.  A tensor 4 bytes off 16-byte alignment takes the scalar kernel.
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    rows, n = 2048, 4096
+    scale = torch.logspace(-3, 2, rows, device="cuda").unsqueeze(1)  # row spreads from 1e-3 to 100
+    x = torch.randn(rows, n, device="cuda", generator=g) * scale
+    x[::7, 5] = float("-inf")
+    x[3::11, 9] = float("nan")
+    store = torch.empty(rows * n + 1, device="cuda")
+    xu = store[1:].view(rows, n)
+    xu.copy_(x)
+    assert x.data_ptr() % 16 == 0 and xu.data_ptr() % 16 == 4
+    ya, yu = cb.softmax_last_dim(x), cb.softmax_last_dim(xu)
+    a, u = ya.view(torch.int32), yu.view(torch.int32)
+    nan = torch.isnan(ya)
+    assert torch.equal(nan, torch.isnan(yu))
+    assert torch.equal(a[~nan], u[~nan])
+    # and both are the correctly rounded exp: numpy's double-precision exp rounded to f32
+    xs = x[100].cpu().numpy()
+    e = np.exp((xs - xs.max()).astype(np.float32).astype(np.float64)).astype(np.float32)  # (x - max) is an f32 value
+    tot = np.float32(oracle.avx_vec_sum(e))
+    assert np.array_equal((e / tot).astype(np.float32).view(np.uint32), ya[100].cpu().numpy().view(np.uint32))
+
+
 ROPE_SHAPES = [(2, 5, 10, 16), (1, 3, 7, 6), (2, 8, 33, 128), (1, 32, 64, 64), (3, 2, 5, 2)]
 
 
