@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
     if (kind == 0) {
       for (int v = tx; v < V; v += kQGatherThreads) {
         float f[8];
-        decode8<QT>(buf, v, f);
+        decode8<QT, true>(buf, v, f);  // the staged row starts on a 16-byte boundary
         store_decoded<DT>(out_row, v, f);
       }
     } else if (kind == 1) {
@@ -415,13 +415,16 @@ cudaError_t launch_qroute_rows(const unsigned char* qtable, const void* ids, int
 // ---------------------------------------------------------------------------------------------
 template <int QT, int DT>
 __global__ void __launch_bounds__(256) dequantize_flat_kernel(const unsigned char* __restrict__ blocks,
-                                                              void* __restrict__ out, int64_t n_vec) {
+                                                              void* __restrict__ out, int64_t n_vec, int aligned16) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec; v += stride) {
     constexpr int kVecs = qblock_elems(QT) / 8;  // 8-element groups per block
     const unsigned char* blk = blocks + (v / kVecs) * QBlock<QT>::kBytes;
     float f[8];
-    decode8<QT>(blk, static_cast<int>(v % kVecs), f);
+    if (aligned16)  // (uniform: a property of the `blocks` pointer)
+      decode8<QT, true>(blk, static_cast<int>(v % kVecs), f);
+    else
+      decode8<QT, false>(blk, static_cast<int>(v % kVecs), f);
     // element offset 8v: express as a row of one vector
     unsigned char* o = static_cast<unsigned char*>(out) + static_cast<size_t>(v) * 8 * Elem<DT>::kBytes;
     store_decoded<DT>(o, 0, f);
@@ -435,16 +438,17 @@ cudaError_t launch_dequantize_flat(int qtype, int out_dtype, const void* blocks,
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
   if (grid > cap) grid = cap;
   const unsigned char* b = static_cast<const unsigned char*>(blocks);
+  const int aligned16 = (reinterpret_cast<uintptr_t>(blocks) & 15u) == 0;
 #define CB200_DQ(QT)                                                                            \
   switch (out_dtype) {                                                                          \
     case kDtF32:                                                                                \
-      dequantize_flat_kernel<QT, kDtF32><<<static_cast<unsigned>(grid), 256, 0, stream>>>(b, out, n_vec);  \
+      dequantize_flat_kernel<QT, kDtF32><<<static_cast<unsigned>(grid), 256, 0, stream>>>(b, out, n_vec, aligned16);  \
       break;                                                                                    \
     case kDtF16:                                                                                \
-      dequantize_flat_kernel<QT, kDtF16><<<static_cast<unsigned>(grid), 256, 0, stream>>>(b, out, n_vec);  \
+      dequantize_flat_kernel<QT, kDtF16><<<static_cast<unsigned>(grid), 256, 0, stream>>>(b, out, n_vec, aligned16);  \
       break;                                                                                    \
     default:                                                                                    \
-      dequantize_flat_kernel<QT, kDtBF16><<<static_cast<unsigned>(grid), 256, 0, stream>>>(b, out, n_vec); \
+      dequantize_flat_kernel<QT, kDtBF16><<<static_cast<unsigned>(grid), 256, 0, stream>>>(b, out, n_vec, aligned16); \
       break;                                                                                    \
   }
   if (qtype == CB200_QTYPE_Q8_0) {

@@ -129,6 +129,32 @@ __device__ __forceinline__ float half_at(const unsigned char* p) {
   return __half2float(*reinterpret_cast<const __half*>(p));
 }
 
+// Small integer held in byte `k` of `w` -> float, without the slow int-to-float conversion: the
+// byte is spliced into the low mantissa bits of 2^23 (0x4B000000) and 2^23 + bias subtracted,
+// which is exact.  For a signed byte the caller flips bit 7 first and passes bias = 128.
+template <int K>
+__device__ __forceinline__ float byte_to_float(uint32_t w, float magic_plus_bias) {
+  return __fadd_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650 | K)), -magic_plus_bias);
+}
+
+// A small non-negative integer -> float the same way.
+__device__ __forceinline__ float small_int_to_float(int v) {
+  return __fadd_rn(__uint_as_float(0x4B000000u | static_cast<uint32_t>(v)), -8388608.0f);
+}
+
+// Eight consecutive bytes at a 2-byte aligned address as two words (four 16-bit loads), or with one
+// 8-byte load where the caller knows the address is 8-byte aligned.
+template <bool ALIGNED8>
+__device__ __forceinline__ uint2 load8(const unsigned char* p) {
+  if constexpr (ALIGNED8) {
+    return *reinterpret_cast<const uint2*>(p);
+  } else {
+    const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
+    return make_uint2(static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16),
+                      static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16));
+  }
+}
+
 // The 6-bit (scale, min) pair j of a Q4K / Q5K block (get_scale_min_k4, quantized/utils.rs:49-59).
 __device__ __forceinline__ void scale_min_k4(int j, const unsigned char* q, float& sc, float& mn) {
   int d, m;
@@ -139,12 +165,15 @@ __device__ __forceinline__ void scale_min_k4(int j, const unsigned char* q, floa
     d = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
     m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
   }
-  sc = static_cast<float>(d);
-  mn = static_cast<float>(m);
+  sc = small_int_to_float(d);
+  mn = small_int_to_float(m);
 }
 
-// Elements [8s, 8s+8) of ONE super-block `b` (s = 0..31), with candle's operation order.
-template <int QT>
+// Elements [8s, 8s+8) of ONE super-block `b` (s = 0..31), with candle's operation order.  The eight
+// source bytes are consecutive: they are fetched as two words and turned into floats four at a time
+// (byte_to_float), so that neither byte loads nor integer-to-float conversions are on the path.
+// ALIGNED16: `b` is 16-byte aligned (blocks of 144 and 176 bytes in a 16-byte aligned row).
+template <int QT, bool ALIGNED16 = false>
 __device__ __forceinline__ void decode8_kquant(const unsigned char* b, int s, float (&out)[8]) {
   const int e0 = 8 * s;
   if constexpr (QT == CB200_QTYPE_Q4K || QT == CB200_QTYPE_Q5K) {
@@ -154,26 +183,38 @@ __device__ __forceinline__ void decode8_kquant(const unsigned char* b, int s, fl
     float sc, mn;
     scale_min_k4(2 * g + hi, b + 4, sc, mn);
     const float dl = __fmul_rn(d, sc), ml = __fmul_rn(dmin, mn);
-    const unsigned char* q = b + (kFive ? 48 : 16) + 32 * g + l0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      int v = hi ? (q[i] >> 4) : (q[i] & 0xF);
-      if (kFive) v += ((b[16 + l0 + i] >> (2 * g + hi)) & 1) << 4;
-      out[i] = __fsub_rn(__fmul_rn(dl, static_cast<float>(v)), ml);
+    uint2 w = load8<ALIGNED16>(b + (kFive ? 48 : 16) + 32 * g + l0);
+    const int shift = 4 * hi;  // low nibbles are elements 0..31 of the group, high nibbles 32..63
+    w.x = (w.x >> shift) & 0x0F0F0F0Fu;
+    w.y = (w.y >> shift) & 0x0F0F0F0Fu;
+    if (kFive) {
+      const uint2 h = load8<ALIGNED16>(b + 16 + l0);
+      const int bit = 2 * g + hi;
+      w.x |= ((h.x >> bit) & 0x01010101u) << 4;
+      w.y |= ((h.y >> bit) & 0x01010101u) << 4;
     }
+    const float v[8] = {byte_to_float<0>(w.x, 8388608.0f), byte_to_float<1>(w.x, 8388608.0f),
+                        byte_to_float<2>(w.x, 8388608.0f), byte_to_float<3>(w.x, 8388608.0f),
+                        byte_to_float<0>(w.y, 8388608.0f), byte_to_float<1>(w.y, 8388608.0f),
+                        byte_to_float<2>(w.y, 8388608.0f), byte_to_float<3>(w.y, 8388608.0f)};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = __fsub_rn(__fmul_rn(dl, v[i]), ml);
   } else if constexpr (QT == CB200_QTYPE_Q6K) {
     const float d = half_at(b + 208);
     const int n = e0 >> 7, r = e0 & 127, j = r >> 5, l0 = r & 31, is = l0 >> 4;
-    const unsigned char* ql = b + 64 * n + ((j & 1) ? 32 : 0) + l0;
-    const unsigned char* qh = b + 128 + 32 * n + l0;
+    uint2 lo = load8<false>(b + 64 * n + ((j & 1) ? 32 : 0) + l0);  // blocks of 210 bytes: 2-byte aligned only
+    const uint2 hq = load8<false>(b + 128 + 32 * n + l0);
     const float sc = static_cast<float>(static_cast<signed char>(b[192 + 8 * n + is + 2 * j]));
     const float ds = __fmul_rn(d, sc);
+    const int shift = (j & 2) ? 4 : 0;
+    lo.x = ((lo.x >> shift) & 0x0F0F0F0Fu) | (((hq.x >> (2 * j)) & 0x03030303u) << 4);
+    lo.y = ((lo.y >> shift) & 0x0F0F0F0Fu) | (((hq.y >> (2 * j)) & 0x03030303u) << 4);
+    constexpr float kBias = 8388608.0f + 32.0f;  // the six-bit value minus 32, exactly
+    const float v[8] = {byte_to_float<0>(lo.x, kBias), byte_to_float<1>(lo.x, kBias), byte_to_float<2>(lo.x, kBias),
+                        byte_to_float<3>(lo.x, kBias), byte_to_float<0>(lo.y, kBias), byte_to_float<1>(lo.y, kBias),
+                        byte_to_float<2>(lo.y, kBias), byte_to_float<3>(lo.y, kBias)};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int lo = (j & 2) ? (ql[i] >> 4) : (ql[i] & 0xF);
-      const int v = (lo | (((qh[i] >> (2 * j)) & 3) << 4)) - 32;
-      out[i] = __fmul_rn(ds, static_cast<float>(v));
-    }
+    for (int i = 0; i < 8; ++i) out[i] = __fmul_rn(ds, v[i]);
   } else if constexpr (QT == CB200_QTYPE_Q8K) {
     // d is an f32 at a 2-byte aligned address: read it as two halves
     const uint16_t* d16 = reinterpret_cast<const uint16_t*>(b);
@@ -209,21 +250,14 @@ __device__ __forceinline__ void decode8_kquant(const unsigned char* b, int s, fl
   }
 }
 
-// Small integer held in byte `k` of `w` -> float, without the slow int-to-float conversion: the
-// byte is spliced into the low mantissa bits of 2^23 (0x4B000000) and 2^23 + bias subtracted,
-// which is exact.  For a signed byte the caller flips bit 7 first and passes bias = 128.
-template <int K>
-__device__ __forceinline__ float byte_to_float(uint32_t w, float magic_plus_bias) {
-  return __fadd_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650 | K)), -magic_plus_bias);
-}
-
 // Decodes elements [8v, 8v+8) of a row of blocks starting at `row` (shared or global memory).
 // `scale`, when given, receives the block's scale d.
-template <int QT>
+// ALIGNED16: `row` is 16-byte aligned (a staged row buffer).
+template <int QT, bool ALIGNED16 = false>
 __device__ __forceinline__ void decode8(const unsigned char* row, int v, float (&out)[8], float* scale = nullptr) {
   if constexpr (is_kquant(QT)) {
     if (scale != nullptr) *scale = 1.0f;
-    decode8_kquant<QT>(row + (v >> 5) * QBlock<QT>::kBytes, v & 31, out);
+    decode8_kquant<QT, ALIGNED16>(row + (v >> 5) * QBlock<QT>::kBytes, v & 31, out);
     return;
   }
   constexpr bool kHasMin = QT == CB200_QTYPE_Q4_1 || QT == CB200_QTYPE_Q5_1;
