@@ -218,87 +218,230 @@ __device__ __forceinline__ uint32_t narrow16(float v) {
     return __half_as_ushort(__float2half_rn(v));
 }
 
-constexpr int kSoftmax16Threads = 128;
+constexpr int kSoftmax16Threads = 256;
 
-// R rows of V 16-byte vectors per CTA, staged in shared memory at a pitch of an odd number of
-// 16-byte units (conflict-free when 32 lanes walk 32 rows).
+// s = T(T(s + lo(w)) + hi(w)): two T-rounded additions on 16-bit registers.  The halves of `w` are
+// named, not extracted -- the add instruction selects the half of a 32-bit register it reads -- so
+// the dependent chain is the two additions and nothing else.
 template <int DT>
-__global__ void __launch_bounds__(kSoftmax16Threads) softmax16_staged_kernel(const uint4* __restrict__ x,
+__device__ __forceinline__ void add_pair_t(unsigned short& s, uint32_t w) {
+  if constexpr (DT == kDtBF16)
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; add.rn.bf16 %0, %0, lo; add.rn.bf16 %0, %0, hi; }" : "+h"(s) : "r"(w));
+  else
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; add.rn.f16 %0, %0, lo; add.rn.f16 %0, %0, hi; }" : "+h"(s) : "r"(w));
+}
+
+// e = T(exp(v)) for v = T(x - max) <= 0 depends on the 16 bits of v only, and only a few thousand
+// magnitudes give anything but 1 (tiny |v|) or 0 (|v| beyond the underflow point): a table over those
+// magnitudes, filled once per CTA with exp_rounded_to, replaces the evaluation per element.
+//   bf16: |v| <= 2^-10 gives 1 (exp(v) > 1 - 2^-9, the midpoint below 1); |v| >= 105 gives 0.
+//   f16:  |v| <= 2^-13 gives 1 (midpoint 1 - 2^-12);                      |v| >= 17.5 gives 0 (< 2^-25).
+// The first and the last entry are those two constants, so clamping the magnitude into the table's
+// range is all the lookup needs; both halves of a word are clamped at once.
+template <int DT>
+struct ExpLut {
+  static constexpr uint32_t kLo = DT == kDtBF16 ? 0x3A80u : 0x0800u;   // bit pattern of 2^-10 / 2^-13
+  static constexpr uint32_t kHi = DT == kDtBF16 ? 0x42D2u : 0x4C60u;   // bit pattern of 105 / 17.5: the entry is 0
+  static constexpr uint32_t kInf = DT == kDtBF16 ? 0x7F80u : 0x7C00u;
+  static constexpr uint32_t kOne = DT == kDtBF16 ? 0x3F80u : 0x3C00u;
+  static constexpr uint32_t kNan = DT == kDtBF16 ? 0x7FC0u : 0x7E00u;
+  // results below this pattern (2^-116 / never for f16) can make e / sum subnormal in T
+  static constexpr uint32_t kTiny = DT == kDtBF16 ? 0x0580u : 0x0000u;
+  static constexpr int kEntries = static_cast<int>(kHi - kLo + 1);
+  static constexpr int kBytes = (kEntries * 2 + 15) & ~15;
+};
+
+template <int DT>
+__device__ __forceinline__ void fill_exp_lut(uint16_t* lut) {
+  for (int i = threadIdx.x; i < ExpLut<DT>::kEntries; i += blockDim.x) {
+    const float v = -widen16<DT>(ExpLut<DT>::kLo + static_cast<uint32_t>(i));
+    lut[i] = static_cast<uint16_t>(narrow16<DT>(exp_rounded_to<DT>(v)));
+  }
+}
+
+// (T(exp(lo)), T(exp(hi))) for the two 16-bit patterns in `v2`, each <= 0 (or NaN).
+template <int DT>
+__device__ __forceinline__ uint32_t exp_lookup2(uint32_t v2, const uint16_t* lut) {
+  constexpr uint32_t kLo2 = ExpLut<DT>::kLo * 0x00010001u, kHi2 = ExpLut<DT>::kHi * 0x00010001u,
+                     kInf2 = ExpLut<DT>::kInf * 0x00010001u;
+  const uint32_t mag2 = v2 & 0x7FFF7FFFu;
+  const uint32_t idx2 = __vsub2(__vminu2(__vmaxu2(mag2, kLo2), kHi2), kLo2);
+  uint32_t e2 = static_cast<uint32_t>(lut[idx2 & 0xFFFFu]) | (static_cast<uint32_t>(lut[idx2 >> 16]) << 16);
+  if (__vcmpgtu2(mag2, kInf2) != 0u) {  // a NaN in one of the halves
+    if ((mag2 & 0xFFFFu) > ExpLut<DT>::kInf) e2 = (e2 & 0xFFFF0000u) | ExpLut<DT>::kNan;
+    if ((mag2 >> 16) > ExpLut<DT>::kInf) e2 = (e2 & 0x0000FFFFu) | (ExpLut<DT>::kNan << 16);
+  }
+  return e2;
+}
+
+// Persistent CTAs, tiles of R rows of V 16-byte vectors staged in shared memory at a pitch of an odd
+// number of 16-byte units.  Per tile:
+//   1. a warp per row: load, max (any order), e = T(exp(T(x - max))) through the table, in place;
+//   2. warp 0 walks the rows sequentially, one lane per row -- the T-rounded sum is a chain of
+//      dependent additions, and nothing but the addition itself is on the chain;
+//   3. a warp per row: y = T(e / sum), stored with 16-byte accesses.
+// Several CTAs share an SM, so one CTA's walk overlaps the other CTAs' loads and stores.
+// Rows a warp loads together in phase 1: up to 16 vectors per lane in flight, at most 4 rows (a tile
+// has at most 32 rows for 8 warps).
+__host__ __device__ constexpr int softmax16_rows_per_batch(int vpl) { return vpl <= 0 ? 1 : (16 / vpl > 4 ? 4 : 16 / vpl); }
+
+// VPL: 16-byte vectors per lane and row (V <= 32 VPL; 1, 2, 4, 8 or 16), or 0 for longer rows.
+template <int DT, int VPL>
+__global__ void __launch_bounds__(kSoftmax16Threads, 3) softmax16_staged_kernel(const uint4* __restrict__ x,
                                                                              uint4* __restrict__ y, int64_t rows,
                                                                              int V, int R, int pitch_vecs) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint4* buf = reinterpret_cast<uint4*>(smem_raw);
+  uint16_t* lut = reinterpret_cast<uint16_t*>(smem_raw);
+  uint4* buf = reinterpret_cast<uint4*>(smem_raw + ExpLut<DT>::kBytes);
   uint32_t* sums = reinterpret_cast<uint32_t*>(buf + static_cast<size_t>(R) * pitch_vecs);  // [R]
+  int* tiny = reinterpret_cast<int*>(sums + R);                                              // [R]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kWarps = kSoftmax16Threads / 32;
-  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * R;
-  const int live = static_cast<int>(min(static_cast<int64_t>(R), rows - row0));
-
-  // phases 1 and 2: a warp per row -- max, then e = T(exp(T(x - max))) into shared memory
-  for (int r = warp; r < live; r += kWarps) {
-    const uint4* xr = x + (row0 + r) * V;
+  fill_exp_lut<DT>(lut);
+  __syncthreads();
+  const int64_t tiles = (rows + R - 1) / R;
+  // -max, then e = T(exp(T(x - max))) in place for row r of the tile, whose max is m
+  auto exp_row = [&](int r, float m) {
     uint4* br = buf + static_cast<size_t>(r) * pitch_vecs;
-    float m = __int_as_float(0xff800000);
-    for (int v = lane; v < V; v += 32) {
-      const uint4 q = ldg_stream(xr + v);
-      br[v] = q;
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = unpack2<DT>(w[i]);
-        m = max_ignoring_nan(m, max_ignoring_nan(f.x, f.y));
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = max_ignoring_nan(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    // -max in both halves; x - max = x + (-max), rounded once to T by the packed add.  (A row of NaNs
+    // only keeps max = -inf: x + inf is NaN for them, as x - (-inf) is.)
+    const uint32_t nm16 = narrow16<DT>(-m);
+    const uint32_t nm2 = nm16 | (nm16 << 16);
+    uint32_t least = 0xFFFFFFFFu;  // per half: the smallest e - 1 (mod 2^16) seen, i.e. the smallest non-zero e
     for (int v = lane; v < V; v += 32) {  // each lane re-reads the vectors it staged itself
       const uint4 q = br[v];
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
       uint32_t o[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float2 f = unpack2<DT>(w[i]);
-        const float e0 = exp_rounded_to<DT>(round_to<DT>(__fsub_rn(f.x, m)));
-        const float e1 = exp_rounded_to<DT>(round_to<DT>(__fsub_rn(f.y, m)));
-        o[i] = pack2<DT>(e0, e1);
+        o[i] = exp_lookup2<DT>(add2_rn<DT>(w[i], nm2), lut);
+        if (DT == kDtBF16) least = __vminu2(least, __vsub2(o[i], 0x00010001u));
       }
       br[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-  }
-  __syncthreads();
-  // phase 3: one lane per row, the T-rounded sum in candle's order
-  if (tid < live) {
-    const uint4* br = buf + static_cast<size_t>(tid) * pitch_vecs;
-    uint32_t s = 0;  // +0 in T
-#pragma unroll 2
-    for (int v = 0; v < V; ++v) {
-      const uint4 q = br[v];
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    if (DT == kDtBF16) {
+      uint32_t t = min(least & 0xFFFFu, least >> 16);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        s = add_t<DT>(s, w[i] & 0xFFFFu);
-        s = add_t<DT>(s, w[i] >> 16);
+      for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xFFFFFFFFu, t, o));
+      // a non-zero e under 2^-116: e / sum may be subnormal in bf16, where only the division is safe
+      if (lane == 0) tiny[r] = (t + 1u < ExpLut<DT>::kTiny) ? 1 : 0;
+    }
+  };
+  auto vec_max = [&](const uint4& q, float m) -> float {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack2<DT>(w[i]);
+      m = max_ignoring_nan(m, max_ignoring_nan(f.x, f.y));
+    }
+    return m;
+  };
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int64_t row0 = tile * R;
+    const int live = static_cast<int>(min(static_cast<int64_t>(R), rows - row0));
+    // ---- 1: load, max (any order), then e in place ----
+    if constexpr (VPL > 0) {
+      // a warp takes RB rows at a time and has all their loads in flight before it uses the first
+      constexpr int RB = softmax16_rows_per_batch(VPL);
+      for (int rbase = warp * RB; rbase < live; rbase += kWarps * RB) {
+        uint4 q[RB * VPL];
+#pragma unroll
+        for (int ri = 0; ri < RB; ++ri)
+#pragma unroll
+          for (int u = 0; u < VPL; ++u) {
+            const int r = rbase + ri, v = lane + 32 * u;
+            q[ri * VPL + u] = (r < live && v < V) ? ldg_stream(x + (row0 + r) * V + v) : make_uint4(0, 0, 0, 0);
+          }
+        float m[RB];
+#pragma unroll
+        for (int ri = 0; ri < RB; ++ri) {
+          m[ri] = __int_as_float(0xff800000);
+#pragma unroll
+          for (int u = 0; u < VPL; ++u) {
+            const int r = rbase + ri, v = lane + 32 * u;
+            if (r < live && v < V) {
+              buf[static_cast<size_t>(r) * pitch_vecs + v] = q[ri * VPL + u];
+              m[ri] = vec_max(q[ri * VPL + u], m[ri]);
+            }
+          }
+        }
+#pragma unroll
+        for (int ri = 0; ri < RB; ++ri) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) m[ri] = max_ignoring_nan(m[ri], __shfl_xor_sync(0xFFFFFFFFu, m[ri], o));
+          if (rbase + ri < live) exp_row(rbase + ri, m[ri]);  // (warp-uniform)
+        }
+      }
+    } else {
+      for (int r = warp; r < live; r += kWarps) {
+        const uint4* xr = x + (row0 + r) * V;
+        uint4* br = buf + static_cast<size_t>(r) * pitch_vecs;
+        float m = __int_as_float(0xff800000);
+        constexpr int U = 8;
+        for (int v0 = lane; v0 < V; v0 += 32 * U) {
+          uint4 q[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (v0 + 32 * u < V) q[u] = ldg_stream(xr + v0 + 32 * u);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (v0 + 32 * u >= V) continue;
+            br[v0 + 32 * u] = q[u];
+            m = vec_max(q[u], m);
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = max_ignoring_nan(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        exp_row(r, m);
       }
     }
-    sums[tid] = s;
-  }
-  __syncthreads();
-  // phase 4: y = T(e / sum)
-  for (int r = warp; r < live; r += kWarps) {
-    const float sum = widen16<DT>(sums[r]);
-    const uint4* br = buf + static_cast<size_t>(r) * pitch_vecs;
-    uint4* yr = y + (row0 + r) * V;
-    for (int v = lane; v < V; v += 32) {
-      const uint4 q = br[v];
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-      uint32_t o[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = unpack2<DT>(w[i]);
-        o[i] = pack2<DT>(__fdiv_rn(f.x, sum), __fdiv_rn(f.y, sum));
+    __syncthreads();
+    // ---- 2: the T-rounded sums, candle's order ----
+    if (warp == 0 && lane < live) {
+      const uint4* pr = buf + static_cast<size_t>(lane) * pitch_vecs;
+      unsigned short s16 = 0;  // +0 in T
+#pragma unroll 4
+      for (int v = 0; v < V; ++v) {
+        const uint4 q = pr[v];
+        add_pair_t<DT>(s16, q.x);
+        add_pair_t<DT>(s16, q.y);
+        add_pair_t<DT>(s16, q.z);
+        add_pair_t<DT>(s16, q.w);
       }
-      stg_stream(yr + v, make_uint4(o[0], o[1], o[2], o[3]));
+      sums[lane] = s16;
     }
+    __syncthreads();
+    // ---- 3: y = T(e / sum) ----
+    for (int r = warp; r < live; r += kWarps) {
+      const float sum = widen16<DT>(sums[r]);
+      const RowDivisor dv = make_row_divisor(sum);
+      // e is 0 or at least the smallest T value and the sum lies in [1, 2^12]: no intermediate of the
+      // three-instruction division can be subnormal (f16).  For bf16 the quotient of two 8-bit
+      // significands is never within 2^-17 of a rounding boundary, so T(e * (1 / sum)) is T(e / sum)
+      // wherever the result is a normal number -- rows with a tiny non-zero e divide instead.
+      const bool quick = dv.fast && (DT == kDtF16 || tiny[r] == 0);
+      const uint4* br = buf + static_cast<size_t>(r) * pitch_vecs;
+      uint4* yr = y + (row0 + r) * V;
+      for (int v = lane; v < V; v += 32) {
+        const uint4 q = br[v];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = unpack2<DT>(w[i]);
+          if (!quick) {
+            o[i] = pack2<DT>(__fdiv_rn(f.x, sum), __fdiv_rn(f.y, sum));
+          } else if (DT == kDtBF16) {
+            o[i] = pack2<DT>(__fmul_rn(f.x, dv.r), __fmul_rn(f.y, dv.r));
+          } else {
+            const float qx = __fmul_rn(f.x, dv.r), qy = __fmul_rn(f.y, dv.r);
+            o[i] = pack2<DT>(__fmaf_rn(__fmaf_rn(-qx, sum, f.x), dv.r, qx), __fmaf_rn(__fmaf_rn(-qy, sum, f.y), dv.r, qy));
+          }
+        }
+        stg_stream(yr + v, make_uint4(o[0], o[1], o[2], o[3]));
+      }
+    }
+    __syncthreads();  // the tile buffer is refilled
   }
 }
 
@@ -542,21 +685,42 @@ cudaError_t launch_rope_dt(int variant, const void* src, const void* cos_, const
 template <int DT>
 cudaError_t launch_softmax16(const void* x, void* y, int64_t rows, int n, cudaStream_t stream) {
   const int64_t row_bytes = static_cast<int64_t>(n) * 2;
-  constexpr int64_t kBudget = 56 * 1024;  // shared memory per CTA: four CTAs per SM
-  if (row_bytes % 16 == 0 && aligned16(x) && aligned16(y) && row_bytes + 16 + 128 <= kBudget) {
-    const int V = static_cast<int>(row_bytes / 16);
-    const int pitch_vecs = V | 1;
-    int R = static_cast<int>((kBudget - 128) / (static_cast<int64_t>(pitch_vecs) * 16));
+  constexpr int64_t kLut = ExpLut<DT>::kBytes;
+  const int V = static_cast<int>(row_bytes / 16);
+  const int pitch_vecs = V | 1;
+  const int64_t pitch = static_cast<int64_t>(pitch_vecs) * 16;
+  if (row_bytes % 16 == 0 && aligned16(x) && aligned16(y) && kLut + pitch + 64 <= 226 * 1024) {
+    // three CTAs per SM where the rows allow it (their walks overlap the others' loads and stores),
+    // up to 32 rows per tile (one per lane of the walking warp)
+    const int64_t budget = 74 * 1024 - kLut;
+    int R = static_cast<int>(budget > pitch ? budget / (pitch + 8) : 1);
     if (R > 32) R = 32;
-    // spread small problems over the device
-    const int64_t spread = (rows + 2 * sm_count() - 1) / (2 * sm_count());
+    const int sms = sm_count();
+    const int64_t spread = (rows + 3 * sms - 1) / (3 * sms);  // spread small problems over the device
     if (R > spread) R = static_cast<int>(spread);
     if (R < 1) R = 1;
-    const size_t smem = static_cast<size_t>(R) * pitch_vecs * 16 + static_cast<size_t>(R) * 4;
-    auto kern = softmax16_staged_kernel<DT>;
-    cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), kSoftmax16Threads, smem, -1, nullptr);
+    // whole batches per warp: phase 1 then takes one round of loads per tile
+    const int vpl = V <= 32 ? 1 : (V <= 64 ? 2 : (V <= 128 ? 4 : (V <= 256 ? 8 : (V <= 512 ? 16 : 0))));
+    const int round_rows = softmax16_rows_per_batch(vpl) * (kSoftmax16Threads / 32);
+    if (R >= round_rows) R = R / round_rows * round_rows;
+    const size_t smem = static_cast<size_t>(kLut) + static_cast<size_t>(R) * pitch + static_cast<size_t>(R) * 8 + 16;
+    void (*kern)(const uint4*, uint4*, int64_t, int, int, int) = softmax16_staged_kernel<DT, 0>;
+    switch (vpl) {
+      case 1: kern = softmax16_staged_kernel<DT, 1>; break;
+      case 2: kern = softmax16_staged_kernel<DT, 2>; break;
+      case 4: kern = softmax16_staged_kernel<DT, 4>; break;
+      case 8: kern = softmax16_staged_kernel<DT, 8>; break;
+      case 16: kern = softmax16_staged_kernel<DT, 16>; break;
+      default: break;
+    }
+    int per_sm = 1;
+    const int want = smem * 3 + 3072 <= 227 * 1024 ? 3 : (smem * 2 + 2048 <= 227 * 1024 ? 2 : 1);
+    cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), kSoftmax16Threads, smem,
+                                         static_cast<int>(((smem + 1024) * want * 100) / (228 * 1024) + 1), &per_sm);
     if (e != cudaSuccess) return e;
-    const int64_t grid = (rows + R - 1) / R;
+    const int64_t tiles = (rows + R - 1) / R;
+    int64_t grid = static_cast<int64_t>(sms) * per_sm;
+    if (grid > tiles) grid = tiles;
     kern<<<static_cast<unsigned>(grid), kSoftmax16Threads, smem, stream>>>(static_cast<const uint4*>(x),
                                                                          static_cast<uint4*>(y), rows, V, R, pitch_vecs);
     return cudaGetLastError();
