@@ -500,12 +500,35 @@ def next_rows_section(dev, timed, peak):
     sel = np.sort(rng.choice(rows, size=picks, replace=False)).astype(np.int64)
     tsel = torch.from_numpy(sel).to(dev)
     ok = np.array_equal(to_oracle(ops.rms_norm_rows(x, tsel, ta, 1e-5)), oracle.rms_norm(xb[sel % 512], alpha, 1e-5, "bf16"))
+    # a call this small is shorter than the host's launch path: device time inside a CUDA graph
+    from candle_b200 import _cabi
+
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    ysel = torch.empty(picks, hidden, dtype=torch.bfloat16, device=dev)
+    st = ops.new_status(dev)
+
+    def launch():
+        _cabi.call("cb200_embedding_rms_norm", x.data_ptr(), tsel.data_ptr(), ta.data_ptr(), ysel.data_ptr(), None, rows,
+                   hidden, picks, 1e-5, 2, 2, 0, st.data_ptr(), side.cuda_stream)
+
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            launch()
+    torch.cuda.synchronize()
+    n_cap = 32
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(n_cap):
+            launch()
+    torch.cuda.synchronize()
+    ms_sel = timed(lambda i: graph.replay(), 10, 3) / (10 * n_cap)
     k = 20
-    ms_sel = timed(lambda i: ops.rms_norm_rows(x, tsel, ta, 1e-5, check=False), k, 3) / k
     ms_all = timed(lambda i: ops.rms_norm(x, ta, 1e-5), k, 3) / k
     out["rms_norm_selected_rows"] = {
         "workload": f"RMS norm bf16 of {picks} selected rows of {rows} x {hidden} (candle norms all rows, then slices)",
         "us_per_step": ms_sel * 1e3, "us_per_step_all_rows": ms_all * 1e3,
+        "timing": f"device time per launch inside a CUDA graph of {n_cap} back-to-back launches",
         "parity": f"bit-exact vs CPU oracle on the {picks} rows" if ok else "MISMATCH"}
     all_ok = all_ok and ok
     return out, all_ok
@@ -529,6 +552,14 @@ def gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev)
     timed = Timer(dev, world)
     peak, peak_kind = measured_peak()
+    if args.workload == "next":
+        if world != 1:
+            raise SystemExit("--workload next runs on one GPU")
+        out, ok = next_rows_section(dev, timed, peak)
+        print(json.dumps({"next_rows": out}), flush=True)
+        if not ok:
+            raise SystemExit(3)
+        return
     if args.workload == "c4":
         if world < 2:
             raise SystemExit("the vocab-sharded C4 workload needs --gpus >= 2 (launch with torch.distributed.run)")
@@ -971,7 +1002,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5", "next"],
+                    help="'next' runs only the operators next to the hot path (one GPU) and prints their record")
     ap.add_argument("--no-sweep", action="store_true", help="skip the brief runs of the other workloads")
     ap.add_argument("--rows-scale", type=float, default=1.0, help="c4 / c5 only: fraction of the configured rows")
     ap.add_argument("--impl", default="candle_b200", choices=["candle_b200", "reference"])

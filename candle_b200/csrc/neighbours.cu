@@ -243,7 +243,6 @@ struct ExpLut {
   static constexpr uint32_t kLo = DT == kDtBF16 ? 0x3A80u : 0x0800u;   // bit pattern of 2^-10 / 2^-13
   static constexpr uint32_t kHi = DT == kDtBF16 ? 0x42D2u : 0x4C60u;   // bit pattern of 105 / 17.5: the entry is 0
   static constexpr uint32_t kInf = DT == kDtBF16 ? 0x7F80u : 0x7C00u;
-  static constexpr uint32_t kOne = DT == kDtBF16 ? 0x3F80u : 0x3C00u;
   static constexpr uint32_t kNan = DT == kDtBF16 ? 0x7FC0u : 0x7E00u;
   // results below this pattern (2^-116 / never for f16) can make e / sum subnormal in T
   static constexpr uint32_t kTiny = DT == kDtBF16 ? 0x0580u : 0x0000u;
@@ -319,7 +318,7 @@ __global__ void __launch_bounds__(kSoftmax16Threads, 3) softmax16_staged_kernel(
       }
       br[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    if (DT == kDtBF16) {
+    if constexpr (DT == kDtBF16) {
       uint32_t t = min(least & 0xFFFFu, least >> 16);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xFFFFFFFFu, t, o));

@@ -7,7 +7,7 @@ import torch
 
 import oracle
 from conftest import round4
-from helpers import ID_NP, TORCH_DT, bits, from_oracle, ids_tensor, make_qtable, randn, to_oracle
+from helpers import ID_NP, TORCH_DT, bits, from_oracle, ids_tensor, make_kq_blocks, make_qtable, randn, to_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -454,7 +454,8 @@ def test_qembedding_rms_norm_matches_oracle(cb, qtype, dtype):
                            y.view(torch.int16 if dtype != "f32" else torch.int32))
 
 
-@pytest.mark.parametrize("qtype,hidden", [("q4_0", 8192), ("q8_0", 4096), ("q8_0", 2048)])
+@pytest.mark.parametrize("qtype,hidden", [("q4_0", 8192), ("q8_0", 4096), ("q8_0", 2048), ("q4k", 4096), ("q6k", 2048),
+                                          ("q5k", 8192)])
 def test_qembedding_rms_norm_many_rows_equals_lookup_then_norm(cb, qtype, hidden):
     # Rows of two and four warps, enough of them that thousands fall to the exact replay while the
     # slot's other warps are still busy with their copy of the decision: the single-launch kernel must
@@ -463,7 +464,10 @@ def test_qembedding_rms_norm_many_rows_equals_lookup_then_norm(cb, qtype, hidden
     rng = np.random.default_rng(61)
     gq = getattr(cb.GgmlDType, qtype.upper())
     vocab, n = 4096, 200_000
-    qt = make_qtable(rng, qtype, vocab, hidden)
+    if qtype.endswith("k"):
+        qt = make_kq_blocks(rng, qtype, vocab * hidden // 256).reshape(vocab, -1)
+    else:
+        qt = make_qtable(rng, qtype, vocab, hidden)
     q = cb.QTensor.from_raw(torch.from_numpy(qt), gq, (vocab, hidden), device="cuda")
     alpha_np = randn(rng, (hidden,), "bf16", 1.0, 0.1)
     alpha = from_oracle(alpha_np, "bf16")

@@ -170,3 +170,32 @@ def test_gpu_lookup_and_lookup_norm(cb, qtype, dtype):
     y, g = cb.qembedding_rms_norm(q, ids_tensor(ids), from_oracle(alpha, dtype), 1e-5, return_gathered=True)
     assert np.array_equal(to_oracle(g), rows)
     assert np.array_equal(to_oracle(y), oracle.rms_norm(rows, alpha, 1e-5, dtype))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("qtype", KQ)
+def test_gpu_lookup_norm_long_rows(cb, qtype, dtype):
+    # Lookup + RMS norm at the row lengths of real tables, with the gathered rows returned too; special
+    # rows: a super-block of zero bytes (exact zeros) and a row made of one repeated super-block.
+    gq = getattr(cb.GgmlDType, qtype.upper())
+    rng = np.random.default_rng(31)
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    for vocab, hidden, n in [(64, 2048, 300), (40, 4096, 257), (24, 8192, 130)]:
+        table = make_kq_blocks(rng, qtype, vocab * hidden // 256).reshape(vocab, -1)
+        bb = oracle.BLOCK_BYTES[qtype]
+        table[1, :bb] = 0                      # a super-block of zeros
+        table[2] = np.tile(table[2, :bb], hidden // 256)
+        ids = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+        ids[:3] = [1, 2, 1]
+        alpha = randn(rng, (hidden,), dtype, 1.0, 0.1)
+        rows = oracle.qembedding(table, qtype, ids, dtype)
+        want = oracle.rms_norm(rows, alpha, 1e-5, dtype)
+        q = cb.QTensor.from_raw(torch.from_numpy(table), gq, (vocab, hidden), device="cuda")
+        y, g = cb.qembedding_rms_norm(q, ids_tensor(ids), from_oracle(alpha, dtype), 1e-5, return_gathered=True)
+        assert y.dtype == tdt
+        assert np.array_equal(to_oracle(g), rows)
+        assert np.array_equal(to_oracle(y), want), (qtype, dtype, hidden)
+        # the norm forced onto its lane-per-row kernel: the same bits
+        y2 = cb.qembedding_rms_norm(q, ids_tensor(ids), from_oracle(alpha, dtype), 1e-5, flags=cb.ops.FLAG_FORCE_LANEROW)
+        assert torch.equal(y2.view(torch.int16), y.view(torch.int16))
