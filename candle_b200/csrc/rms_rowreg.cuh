@@ -81,16 +81,17 @@ struct RowRegSmem {
   int4* chunks;  // [tpr] replay: {A, B - A, L, -}: while the sum's bit pattern stays in the
                  // binade that starts at L, a chunk adds A to an even and B to an odd one
   int4* segs;    // [tpr] replay: the same for runs of chunks, {A, B - A, L, first | count << 16}
+                 // (a third array of [tpr] follows segs: the second parts of chunks that cross a binade)
   uint4* rows;   // [V]: h, parked for the replay
   __device__ RowRegSmem(unsigned char* base, int rpc, int tpr, int V, int ty) {
     unsigned char* mine = base + static_cast<size_t>(ty) * slot_bytes(tpr);
     chunks = reinterpret_cast<int4*>(mine);
     segs = chunks + tpr;
-    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 32);
+    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 48);
     pub = red + 48;
     rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * slot_bytes(tpr)) + static_cast<size_t>(ty) * V;
   }
-  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 32 + 52 * sizeof(float); }
+  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 48 + 52 * sizeof(float); }
   __host__ __device__ static size_t bytes(int rpc, int tpr, int V, bool with_rows) {
     return static_cast<size_t>(rpc) * slot_bytes(tpr) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
   }
@@ -179,10 +180,13 @@ __device__ __forceinline__ float sequential_sum_sq(const Row& row, int v0, int v
 // start value of that binade is "S + A if S is even, S + B if S is odd", and A, B can be measured
 // by running the run twice, from an even and from an odd reference value of the same binade.
 // Every thread measures (A, B) for its own contiguous chunk, using the approximate prefix sum to
-// pick the binade; thread 0 then walks the chunks with exact integer updates, checking that the
-// true value really is in the assumed binade before and after each chunk (the sum is monotone, so
-// that covers the whole chunk) and falling back to plain sequential addition for the chunk
-// otherwise.  The checks make the result exact whatever the quality of the guesses.
+// pick the binade -- and, where that prefix says the sum leaves the binade inside the chunk, cuts
+// the chunk there: (A, B) up to the crossing element, the element itself, (A, B) after it in the
+// next binade.  Thread 0 then walks the chunks with exact integer updates (the crossing element
+// with a real addition), checking that the true value really is in the assumed binade before and
+// after each part (the sum is monotone, so that covers the whole part) and falling back to plain
+// sequential addition for the chunk otherwise.  The checks make the result exact whatever the
+// quality of the guesses.
 template <int DT, typename Row>
 __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* segs, float* red, int V,
                                             int bar_id) {
@@ -218,36 +222,89 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
   }
   const float prefix = incl - sig;
 
-  // measure the chunk from an even and an odd reference value next to the approximate prefix
-  const uint32_t e0 = __float_as_uint(prefix) & ~1u;
-  const int e = static_cast<int>(e0 >> 23);
-  bool ok = (v0 < v1) && (prefix > 0.0f) && (e >= 67) && (e <= 187);  // 2^-60 .. 2^60
-  float s0 = __uint_as_float(e0), s1 = __uint_as_float(e0 + 1u);
+  // Measure the chunk from an even and an odd reference value next to the approximate prefix.  The
+  // approximate running sum `t` also tells where the sum leaves the binade: the chunk is then cut at
+  // that element -- {A, B} before it, the element itself (added for real by the walk), {A, B} after it
+  // in the next binade.  A second crossing in one chunk leaves the chunk to the sequential fallback.
+  int4* chunks2 = segs + tpr;
+  uint32_t base = __float_as_uint(prefix) & ~1u;
+  int e = static_cast<int>(base >> 23);
+  const bool ok = (v0 < v1) && (prefix > 0.0f) && (e >= 67) && (e <= 187);  // 2^-60 .. 2^60
+  float s0 = __uint_as_float(base), s1 = __uint_as_float(base + 1u);
+  float t = prefix, pcross = 0.0f;
+  uint32_t A1 = 0u, BA1 = 0u, lo1 = 0xFFFFFFFFu, A2 = 0u, BA2 = 0u, lo2 = 0xFFFFFFFFu;
+  int ncross = 0;
   if (ok) {
     for (int v = v0; v < v1; ++v) {
       uint4 q = rows.vec(v);
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      float p[8];
+      float vs = 0.0f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float2 f = unpack2<DT>(w[i]);
-        s0 = fmaf(f.x, f.x, s0);  // h*h is exact, so this rounds like fl(s + h*h)
-        s1 = fmaf(f.x, f.x, s1);
-        s0 = fmaf(f.y, f.y, s0);
-        s1 = fmaf(f.y, f.y, s1);
+        p[2 * i] = __fmul_rn(f.x, f.x);  // exact
+        p[2 * i + 1] = __fmul_rn(f.y, f.y);
+        vs += p[2 * i] + p[2 * i + 1];
+      }
+      const float t8 = t + vs;
+      if ((__float_as_uint(t8) >> 23) == (__float_as_uint(t) >> 23)) {
+        // (the sum never decreases: equal ends mean no crossing inside these eight elements)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          s0 = __fadd_rn(s0, p[i]);
+          s1 = __fadd_rn(s1, p[i]);
+        }
+        t = t8;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float tn = t + p[i];
+          if ((__float_as_uint(tn) >> 23) == (__float_as_uint(t) >> 23)) {
+            s0 = __fadd_rn(s0, p[i]);
+            s1 = __fadd_rn(s1, p[i]);
+          } else if (ncross == 0) {
+            const bool in = static_cast<int>(__float_as_uint(s1) >> 23) == e;  // the references stayed in the binade
+            A1 = __float_as_uint(s0) - base;
+            BA1 = (__float_as_uint(s1) - (base + 1u)) - A1;
+            lo1 = in ? (static_cast<uint32_t>(e) << 23) : 0xFFFFFFFFu;
+            pcross = p[i];
+            ncross = 1;
+            base = __float_as_uint(tn) & ~1u;
+            e = static_cast<int>(base >> 23);
+            s0 = __uint_as_float(base);
+            s1 = __uint_as_float(base + 1u);
+          } else {
+            ncross = 2;
+          }
+          t = tn;
+        }
       }
     }
-    ok = static_cast<int>(__float_as_uint(s1) >> 23) == e;  // the references stayed in the binade
+    const bool in = static_cast<int>(__float_as_uint(s1) >> 23) == e && e <= 187;
+    const uint32_t A = __float_as_uint(s0) - base, BA = (__float_as_uint(s1) - (base + 1u)) - A;
+    const uint32_t lo_last = in ? (static_cast<uint32_t>(e) << 23) : 0xFFFFFFFFu;
+    if (ncross == 0) {
+      A1 = A, BA1 = BA, lo1 = lo_last;
+    } else {
+      A2 = A, BA2 = BA, lo2 = lo_last;
+    }
   }
-  // chunk record: {A, B - A, first bit pattern of the binade}; an unusable chunk gets a binade
-  // start no running sum can reach, so the range check of the walk rejects it
-  uint32_t inc_even = __float_as_uint(s0) - e0, inc_odd = __float_as_uint(s1) - (e0 + 1u);
-  const uint32_t lo = ok ? (static_cast<uint32_t>(e) << 23) : 0xFFFFFFFFu;
-  chunks[tx] = make_int4(static_cast<int>(inc_even), static_cast<int>(inc_odd - inc_even), static_cast<int>(lo), 0);
+  if (ncross == 2) lo1 = 0xFFFFFFFFu;
+  // chunk record: {A, B - A, first bit pattern of the binade, crosses}; an unusable chunk gets a binade
+  // start no running sum can reach, so the range check of the walk rejects it.  Only chunks that stay
+  // in one binade take part in the composition below.
+  const bool whole = lo1 != 0xFFFFFFFFu && ncross == 0;
+  uint32_t inc_even = A1, inc_odd = A1 + BA1;
+  const uint32_t lo = whole ? lo1 : 0xFFFFFFFFu;
+  chunks[tx] = make_int4(static_cast<int>(A1), static_cast<int>(BA1), static_cast<int>(lo1), ncross == 1 ? 1 : 0);
+  if (ncross == 1)
+    chunks2[tx] = make_int4(static_cast<int>(A2), static_cast<int>(BA2), static_cast<int>(lo2), __float_as_int(pcross));
 
   // Runs of consecutive chunks of one warp that share a binade compose into one record: for an
   // even start the run adds A1 + (A1 odd ? B2 : A2), for an odd start B1 + (B1 odd ? A2 : B2).
   // A suffix scan restricted to the run leaves the whole run's record in its first lane.
-  const uint32_t key = ok ? lo : (0xFFFFFF00u | static_cast<uint32_t>(lane));  // unusable chunks stay alone
+  const uint32_t key = whole ? lo : (0xFFFFFF00u | static_cast<uint32_t>(lane));  // the others stay alone
   const uint32_t prev_key = __shfl_up_sync(0xFFFFFFFFu, key, 1);
   const bool head = (lane == 0) || (key != prev_key);
   const uint32_t heads = __ballot_sync(0xFFFFFFFFu, head);
@@ -296,22 +353,33 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
       const int4 k = chunks[c];
       const uint32_t lo_c = static_cast<uint32_t>(k.z);
       const uint32_t S2 = S + static_cast<uint32_t>(k.x) + (S & 1u) * static_cast<uint32_t>(k.y);
-      if (S >= lo_c && (S2 - lo_c) < 0x800000u) {
-        S = S2;
-      } else {
-        const int c0 = min(V, c * vpc), c1 = min(V, c0 + vpc);
-        S = __float_as_uint(sequential_sum_sq<DT, Row>(rows, c0, c1, __uint_as_float(S)));
+      if (lo_c != 0xFFFFFFFFu && S >= lo_c && (S2 - lo_c) < 0x800000u) {
+        if (k.w == 0) {
+          S = S2;
+          return;
+        }
+        // the chunk crosses into the next binade: the crossing element for real, then the second part
+        const int4 k2 = chunks2[c];
+        const uint32_t lo_2 = static_cast<uint32_t>(k2.z);
+        const uint32_t S3 = __float_as_uint(__fadd_rn(__uint_as_float(S2), __int_as_float(k2.w)));
+        const uint32_t S4 = S3 + static_cast<uint32_t>(k2.x) + (S3 & 1u) * static_cast<uint32_t>(k2.y);
+        if (lo_2 != 0xFFFFFFFFu && S3 >= lo_2 && (S4 - lo_2) < 0x800000u) {
+          S = S4;
+          return;
+        }
       }
+      const int c0 = min(V, c * vpc), c1 = min(V, c0 + vpc);
+      S = __float_as_uint(sequential_sum_sq<DT, Row>(rows, c0, c1, __uint_as_float(S)));
     };
     int4 cur = segs[0];
     for (int r = 0; r < total_runs; ++r) {
       const int4 nxt = segs[min(r + 1, total_runs - 1)];  // off the dependency chain
       const uint32_t lo_r = static_cast<uint32_t>(cur.z);
       const uint32_t S2 = S + static_cast<uint32_t>(cur.x) + (S & 1u) * static_cast<uint32_t>(cur.y);
-      if (S >= lo_r && (S2 - lo_r) < 0x800000u) {
+      if (lo_r != 0xFFFFFFFFu && S >= lo_r && (S2 - lo_r) < 0x800000u) {
         S = S2;
       } else {
-        // the run as a whole does not apply: take its chunks one at a time
+        // the run as a whole does not apply (or is a chunk that crosses): take its chunks one at a time
         const int first = cur.w & 0xFFFF, count = cur.w >> 16;
         for (int c = first; c < first + count; ++c) chunk_step(c);
       }
