@@ -81,17 +81,18 @@ struct RowRegSmem {
   int4* chunks;  // [tpr] replay: {A, B - A, L, -}: while the sum's bit pattern stays in the
                  // binade that starts at L, a chunk adds A to an even and B to an odd one
   int4* segs;    // [tpr] replay: the same for runs of chunks, {A, B - A, L, first | count << 16}
-                 // (a third array of [tpr] follows segs: the second parts of chunks that cross a binade)
+                 // (two more arrays of [tpr] follow segs: the second parts of chunks, and of runs, that
+                 // cross a binade)
   uint4* rows;   // [V]: h, parked for the replay
   __device__ RowRegSmem(unsigned char* base, int rpc, int tpr, int V, int ty) {
     unsigned char* mine = base + static_cast<size_t>(ty) * slot_bytes(tpr);
     chunks = reinterpret_cast<int4*>(mine);
     segs = chunks + tpr;
-    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 48);
+    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 64);
     pub = red + 48;
     rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * slot_bytes(tpr)) + static_cast<size_t>(ty) * V;
   }
-  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 48 + 52 * sizeof(float); }
+  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 64 + 52 * sizeof(float); }
   __host__ __device__ static size_t bytes(int rpc, int tpr, int V, bool with_rows) {
     return static_cast<size_t>(rpc) * slot_bytes(tpr) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
   }
@@ -227,6 +228,7 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
   // that element -- {A, B} before it, the element itself (added for real by the walk), {A, B} after it
   // in the next binade.  A second crossing in one chunk leaves the chunk to the sequential fallback.
   int4* chunks2 = segs + tpr;
+  int4* segs2 = chunks2 + tpr;
   uint32_t base = __float_as_uint(prefix) & ~1u;
   int e = static_cast<int>(base >> 23);
   const bool ok = (v0 < v1) && (prefix > 0.0f) && (e >= 67) && (e <= 187);  // 2^-60 .. 2^60
@@ -234,9 +236,14 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
   float t = prefix, pcross = 0.0f;
   uint32_t A1 = 0u, BA1 = 0u, lo1 = 0xFFFFFFFFu, A2 = 0u, BA2 = 0u, lo2 = 0xFFFFFFFFu;
   int ncross = 0;
-  if (ok) {
-    for (int v = v0; v < v1; ++v) {
-      uint4 q = rows.vec(v);
+  {
+    // second pair of references: they start, in the next binade, at the crossing element
+    float s0b = 0.0f, s1b = 0.0f;
+    uint32_t base2 = 0u;
+    uint32_t texp = __float_as_uint(t) >> 23;
+    for (int k = 0; k < vpc; ++k) {  // every thread of the warp makes vpc trips: the vote below is warp-wide
+      const int v = v0 + k;
+      const uint4 q = v < v1 ? rows.vec(v) : make_uint4(0, 0, 0, 0);  // (past the row: zeros change nothing)
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
       float p[8];
       float vs = 0.0f;
@@ -248,8 +255,10 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
         vs += p[2 * i] + p[2 * i + 1];
       }
       const float t8 = t + vs;
-      if ((__float_as_uint(t8) >> 23) == (__float_as_uint(t) >> 23)) {
-        // (the sum never decreases: equal ends mean no crossing inside these eight elements)
+      const bool calm = ok && ncross == 0 && (__float_as_uint(t8) >> 23) == texp;
+      if (__all_sync(0xFFFFFFFFu, calm || !ok)) {
+        // no lane of the warp sees a crossing in these eight elements (the sum never decreases: equal
+        // ends mean none inside): the plain pair of chains
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           s0 = __fadd_rn(s0, p[i]);
@@ -257,40 +266,47 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
         }
         t = t8;
       } else {
+        // branch-free form: an element goes to the first pair of references before the crossing, to
+        // the second pair after it, and is kept aside if it is the crossing element itself
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float tn = t + p[i];
-          if ((__float_as_uint(tn) >> 23) == (__float_as_uint(t) >> 23)) {
-            s0 = __fadd_rn(s0, p[i]);
-            s1 = __fadd_rn(s1, p[i]);
-          } else if (ncross == 0) {
-            const bool in = static_cast<int>(__float_as_uint(s1) >> 23) == e;  // the references stayed in the binade
-            A1 = __float_as_uint(s0) - base;
-            BA1 = (__float_as_uint(s1) - (base + 1u)) - A1;
-            lo1 = in ? (static_cast<uint32_t>(e) << 23) : 0xFFFFFFFFu;
+          const uint32_t nexp = __float_as_uint(tn) >> 23;
+          const bool changed = nexp != texp;
+          const bool first = changed && ncross == 0;
+          const float a1 = (ncross == 0 && !changed) ? p[i] : 0.0f;
+          const float a2 = (ncross == 1 && !changed) ? p[i] : 0.0f;
+          s0 = __fadd_rn(s0, a1);
+          s1 = __fadd_rn(s1, a1);
+          s0b = __fadd_rn(s0b, a2);
+          s1b = __fadd_rn(s1b, a2);
+          if (first) {
             pcross = p[i];
-            ncross = 1;
-            base = __float_as_uint(tn) & ~1u;
-            e = static_cast<int>(base >> 23);
-            s0 = __uint_as_float(base);
-            s1 = __uint_as_float(base + 1u);
-          } else {
-            ncross = 2;
+            base2 = __float_as_uint(tn) & ~1u;
+            s0b = __uint_as_float(base2);
+            s1b = __uint_as_float(base2 + 1u);
           }
+          ncross += changed ? 1 : 0;
           t = tn;
+          texp = nexp;
         }
       }
     }
-    const bool in = static_cast<int>(__float_as_uint(s1) >> 23) == e && e <= 187;
-    const uint32_t A = __float_as_uint(s0) - base, BA = (__float_as_uint(s1) - (base + 1u)) - A;
-    const uint32_t lo_last = in ? (static_cast<uint32_t>(e) << 23) : 0xFFFFFFFFu;
-    if (ncross == 0) {
-      A1 = A, BA1 = BA, lo1 = lo_last;
-    } else {
-      A2 = A, BA2 = BA, lo2 = lo_last;
+    if (ok) {
+      const bool in1 = static_cast<int>(__float_as_uint(s1) >> 23) == e;  // the references stayed in the binade
+      A1 = __float_as_uint(s0) - base;
+      BA1 = (__float_as_uint(s1) - (base + 1u)) - A1;
+      lo1 = in1 ? (static_cast<uint32_t>(e) << 23) : 0xFFFFFFFFu;
+      if (ncross == 1) {
+        const int e2 = static_cast<int>(base2 >> 23);
+        const bool in2 = static_cast<int>(__float_as_uint(s1b) >> 23) == e2 && e2 <= 187;
+        A2 = __float_as_uint(s0b) - base2;
+        BA2 = (__float_as_uint(s1b) - (base2 + 1u)) - A2;
+        lo2 = in2 ? (static_cast<uint32_t>(e2) << 23) : 0xFFFFFFFFu;
+      }
     }
   }
-  if (ncross == 2) lo1 = 0xFFFFFFFFu;
+  if (ncross >= 2) lo1 = 0xFFFFFFFFu;
   // chunk record: {A, B - A, first bit pattern of the binade, crosses}; an unusable chunk gets a binade
   // start no running sum can reach, so the range check of the walk rejects it.  Only chunks that stay
   // in one binade take part in the composition below.
@@ -332,8 +348,16 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
     // length of the run: distance to the next head of the warp
     const uint32_t later = heads & ~(0xFFFFFFFFu >> (31 - lane));
     const int len = (later ? __ffs(later) - 1 : 32) - lane;
-    segs[run_base + sid - 1] = make_int4(static_cast<int>(inc_even), static_cast<int>(inc_odd - inc_even),
-                                         static_cast<int>(lo), tx | (len << 16));
+    if (ncross == 1) {
+      // a chunk that crosses is a run of its own, and the run record carries both of its parts
+      segs[run_base + sid - 1] = make_int4(static_cast<int>(A1), static_cast<int>(BA1), static_cast<int>(lo1),
+                                           tx | (1 << 16) | (1 << 30));
+      segs2[run_base + sid - 1] =
+          make_int4(static_cast<int>(A2), static_cast<int>(BA2), static_cast<int>(lo2), __float_as_int(pcross));
+    } else {
+      segs[run_base + sid - 1] = make_int4(static_cast<int>(inc_even), static_cast<int>(inc_odd - inc_even),
+                                           static_cast<int>(lo), tx | (len << 16));
+    }
   }
   int total_runs = n_runs;
   if (wpr > 1) {
@@ -371,19 +395,31 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
       const int c0 = min(V, c * vpc), c1 = min(V, c0 + vpc);
       S = __float_as_uint(sequential_sum_sq<DT, Row>(rows, c0, c1, __uint_as_float(S)));
     };
-    int4 cur = segs[0];
+    int4 cur = segs[0], cur2 = segs2[0];
     for (int r = 0; r < total_runs; ++r) {
-      const int4 nxt = segs[min(r + 1, total_runs - 1)];  // off the dependency chain
+      const int rn = min(r + 1, total_runs - 1);
+      const int4 nxt = segs[rn], nxt2 = segs2[rn];  // off the dependency chain (segs2 is read even where unused)
+      const bool cross = (cur.w >> 30) & 1;
       const uint32_t lo_r = static_cast<uint32_t>(cur.z);
       const uint32_t S2 = S + static_cast<uint32_t>(cur.x) + (S & 1u) * static_cast<uint32_t>(cur.y);
-      if (lo_r != 0xFFFFFFFFu && S >= lo_r && (S2 - lo_r) < 0x800000u) {
-        S = S2;
+      bool ok = lo_r != 0xFFFFFFFFu && S >= lo_r && (S2 - lo_r) < 0x800000u;
+      uint32_t Sn = S2;
+      if (cross) {
+        // the crossing element for real, then the second part in the next binade
+        const uint32_t lo_2 = static_cast<uint32_t>(cur2.z);
+        const uint32_t S3 = __float_as_uint(__fadd_rn(__uint_as_float(S2), __int_as_float(cur2.w)));
+        Sn = S3 + static_cast<uint32_t>(cur2.x) + (S3 & 1u) * static_cast<uint32_t>(cur2.y);
+        ok = ok && lo_2 != 0xFFFFFFFFu && S3 >= lo_2 && (Sn - lo_2) < 0x800000u;
+      }
+      if (ok) {
+        S = Sn;
       } else {
-        // the run as a whole does not apply (or is a chunk that crosses): take its chunks one at a time
-        const int first = cur.w & 0xFFFF, count = cur.w >> 16;
+        // the run as a whole does not apply: take its chunks one at a time
+        const int first = cur.w & 0xFFFF, count = (cur.w >> 16) & 0x3FFF;
         for (int c = first; c < first + count; ++c) chunk_step(c);
       }
       cur = nxt;
+      cur2 = nxt2;
     }
     result = __uint_as_float(S);
   }
