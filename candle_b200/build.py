@@ -11,7 +11,7 @@ LIB_DIR = os.path.join(_HERE, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libcandle_b200.so")
 NCCL_LIB_PATH = os.path.join(LIB_DIR, "libcandle_b200_nccl.so")
 
-CORE_SOURCES = ["capi.cu", "launch_cache.cu", "rms_rowreg.cu", "norm_lanerow.cu", "norm_slow.cu", "neighbours.cu", "embedding.cu"]
+CORE_SOURCES = ["capi.cu", "launch_cache.cu", "rms_rowreg.cu", "kqrms.cu", "norm_lanerow.cu", "norm_slow.cu", "neighbours.cu", "embedding.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--use_fast_math=false",

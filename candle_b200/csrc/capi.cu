@@ -400,6 +400,29 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
   const bool fused = fusable_qtype(qtype) && out_dtype != CB200_DTYPE_F32 && aligned16(qtable) &&
                      cb200::qrms_rowreg_supported(out_dtype, hidden) &&
                      !(flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC));
+  const bool forced = (flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC)) != 0;
+  if (!fused && !forced && aligned16(qtable) && cb200::kqrms_supported(qtype, out_dtype, hidden)) {
+    // K-quant super-blocks: the row-register kernel with a decoder in front, one launch
+    cb200::QRmsArgs a{};
+    a.qtable = static_cast<const unsigned char*>(qtable);
+    a.ids = ids;
+    a.alpha = static_cast<const uint4*>(alpha);
+    a.y = static_cast<uint4*>(y);
+    a.gathered = static_cast<uint4*>(gathered);
+    a.id_dtype = id_dtype;
+    a.vocab = vocab;
+    a.vocab_begin = vocab_begin;
+    a.vocab_end = vocab_end;
+    a.status = status;
+    a.rows = n_ids;
+    a.V = hidden / 8;
+    a.n = hidden;
+    a.row_bytes = hidden / cb200::qblock_elems(qtype) * cb200::qblock_bytes(qtype);
+    a.bulk = 1;
+    a.eps = eps;
+    a.flags = flags;
+    return cuda_result(cb200::launch_kqrms(qtype, out_dtype, a, stream), name);
+  }
   if (!fused) {
     // Two launches (f32 output, a row length the fused kernel has no exact split for, or a forced
     // implementation): decode into `gathered`, or into y itself, then normalise (in place if y).

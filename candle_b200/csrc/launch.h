@@ -58,6 +58,9 @@ bool rms_rowreg_supported(int dtype, int cols);
 bool qrms_rowreg_supported(int dtype, int cols);
 cudaError_t launch_rms_rowreg(int dtype, const RmsRowRegArgs& a, cudaStream_t stream);
 cudaError_t launch_qrms_rowreg(int qtype, int dtype, const QRmsArgs& a, cudaStream_t stream);
+// lookup + RMS norm for the K-quant super-block formats (kqrms.cu)
+bool kqrms_supported(int qtype, int dtype, int cols);
+cudaError_t launch_kqrms(int qtype, int dtype, const QRmsArgs& a, cudaStream_t stream);
 
 bool norm_lanerow_supported(int dtype, int cols);
 cudaError_t launch_norm_lanerow(int dtype, int op, const LaneRowArgs& a, cudaStream_t stream);

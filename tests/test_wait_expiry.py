@@ -85,3 +85,17 @@ def test_quantised_gather(cb):
     it = ids_tensor(ids)
     want = oracle.qembedding(qt, "q4_0", ids, "f16")
     expire_then_recover(cb, lambda st: q.embedding(it, torch.float16, check=False, status=st), want)
+
+
+def test_kquant_lookup_norm(cb):
+    from helpers import make_kq_blocks
+
+    rng = np.random.default_rng(6)
+    vocab, hidden = 256, 4096
+    raw = make_kq_blocks(rng, "q4k", vocab * hidden // 256).reshape(vocab, -1)
+    ids = rng.integers(0, vocab, size=1500).astype(np.uint32)
+    alpha = randn(rng, (hidden,), "bf16", 1.0, 0.1)
+    q = cb.QTensor.from_raw(torch.from_numpy(raw), cb.GgmlDType.Q4K, (vocab, hidden), device="cuda")
+    it, at = ids_tensor(ids), from_oracle(alpha, "bf16")
+    want = oracle.rms_norm(oracle.qembedding(raw, "q4k", ids, "bf16"), alpha, 1e-5, "bf16")
+    expire_then_recover(cb, lambda st: cb.qembedding_rms_norm(q, it, at, 1e-5, check=False, status=st), want)
