@@ -487,7 +487,7 @@ def next_rows_section(dev, timed, peak):
               f"bit-exact vs CPU oracle on {sample} rows")
         ok = np.array_equal(to_oracle(ops.qembedding_rms_norm(q, tids, ta, 1e-5)[:sample]),
                             oracle.rms_norm(rows_q, alpha, 1e-5, "bf16"))
-        entry(f"qembedding_rms_norm_{qname}", f"the same lookup + RMS norm (two launches: lookup into y, norm in place)",
+        entry(f"qembedding_rms_norm_{qname}", "the same lookup + RMS norm, one launch",
               lambda: ops.qembedding_rms_norm(q, tids, ta, 1e-5, check=False), n_ids * (raw.shape[1] + hidden * 2), ok,
               f"bit-exact vs CPU oracle on {sample} rows")
         del q

@@ -36,7 +36,7 @@ struct KqStage {
 };
 
 template <int QT, int DT, int VPT>
-__global__ void __launch_bounds__(256, 3) kq_rowreg_kernel(const QRmsArgs a) {
+__global__ void __launch_bounds__(256, 4) kq_rowreg_kernel(const QRmsArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tx = threadIdx.x, ty = threadIdx.y, tpr = blockDim.x, rpc = blockDim.y;
   RowRegSmem sm(smem_raw, rpc, tpr, a.V, ty);
@@ -46,13 +46,10 @@ __global__ void __launch_bounds__(256, 3) kq_rowreg_kernel(const QRmsArgs a) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * rpc;
   const int64_t first = static_cast<int64_t>(blockIdx.x) * rpc + ty;
 
-  uint4 al[VPT];
+  // (alpha is re-read through L1 for every row: keeping it in registers would cost the fourth CTA per SM)
   float wv[VPT];
 #pragma unroll
-  for (int k = 0; k < VPT; ++k) {
-    al[k] = __ldg(a.alpha + k * tpr + tx);
-    wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
-  }
+  for (int k = 0; k < VPT; ++k) wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
 
   // issuing thread: classify `row`, publish its kind, start its copy into stage `s`
   auto issue = [&](int64_t row, int s) {
@@ -134,10 +131,7 @@ __global__ void __launch_bounds__(256, 3) kq_rowreg_kernel(const QRmsArgs a) {
     }
     if (replayed) {  // nothing was kept in registers across the out-of-line replay
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        al[k] = __ldg(a.alpha + k * tpr + tx);
-        wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
-      }
+      for (int k = 0; k < VPT; ++k) wv[k] = static_cast<float>(a.n - 8 * (k * tpr + tx));
     }
     if (kind != kRowBadId) {
       if (a.gathered != nullptr) {
@@ -150,7 +144,8 @@ __global__ void __launch_bounds__(256, 3) kq_rowreg_kernel(const QRmsArgs a) {
       const float r = fast_div ? __frcp_rn(m) : 0.0f;
       uint4* yr = a.y + row * a.V + tx;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) stg_stream(yr + k * tpr, rms_output_vec<DT>(h[k], al[k], m, r, fast_div));
+      for (int k = 0; k < VPT; ++k)
+        stg_stream(yr + k * tpr, rms_output_vec<DT>(h[k], __ldg(a.alpha + k * tpr + tx), m, r, fast_div));
     }
   }
 }
@@ -176,11 +171,11 @@ cudaError_t launch_kq_t(const QRmsArgs& a_in, int tpr, int rpc, cudaStream_t str
   a.wt = wait_tuning();
   const int stage_bytes = (a.row_bytes + 15) & ~15;
   const size_t smem = RowRegSmem::bytes(rpc, tpr, a.V, true) + static_cast<size_t>(rpc) * KqStage::bytes(stage_bytes);
-  if (smem > 75 * 1024) return cudaErrorInvalidValue;  // three CTAs per SM
+  if (smem > 56 * 1024) return cudaErrorInvalidValue;  // four CTAs per SM
   auto kern = kq_rowreg_kernel<QT, DT, VPT>;
   int per_sm = 1, sms = 1;
   cudaError_t e = kernel_launch_config(reinterpret_cast<const void*>(kern), 256, smem,
-                                       static_cast<int>(((smem + 1024) * 3 * 100 + 228 * 1024 - 1) / (228 * 1024)), &per_sm);
+                                       static_cast<int>(((smem + 1024) * 4 * 100 + 228 * 1024 - 1) / (228 * 1024)), &per_sm);
   if (e != cudaSuccess) return e;
   e = device_sm_count(&sms);
   if (e != cudaSuccess) return e;
@@ -215,14 +210,14 @@ cudaError_t launch_kq(int dtype, const QRmsArgs& a, cudaStream_t stream) {
 }  // namespace
 
 // Row lengths the kernel takes: 16-bit output, a whole number of super-blocks, V = tpr * vpt with the
-// split above, the staged rows and the parked row within the shared memory of a third of an SM.
+// split above, the staged rows and the parked row within the shared memory of a quarter of an SM.
 bool kqrms_supported(int qtype, int dtype, int cols) {
   int tpr, vpt, rpc;
   if (!is_kquant(qtype) || (dtype != kDtBF16 && dtype != kDtF16) || cols <= 0 || cols % 256 != 0) return false;
   if (!kq_shape(cols / 8, tpr, vpt, rpc)) return false;
   const int row_bytes = cols / 256 * qblock_bytes(qtype);
   if (row_bytes % 16 != 0) return false;
-  return RowRegSmem::bytes(rpc, tpr, cols / 8, true) + static_cast<size_t>(rpc) * KqStage::bytes(row_bytes) <= 75 * 1024;
+  return RowRegSmem::bytes(rpc, tpr, cols / 8, true) + static_cast<size_t>(rpc) * KqStage::bytes(row_bytes) <= 56 * 1024;
 }
 
 cudaError_t launch_kqrms(int qtype, int dtype, const QRmsArgs& a, cudaStream_t stream) {

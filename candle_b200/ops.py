@@ -232,7 +232,8 @@ def qembedding_rms_norm(qtensor, ids: torch.Tensor, alpha: torch.Tensor, eps: fl
                         return_gathered: bool = False, flags: int = 0, check: bool = True,
                         status: torch.Tensor | None = None, vocab_range: tuple[int, int] | None = None,
                         vocab: int | None = None):
-    """Rows ``ids`` of a Q4_0 / Q8_0 table decoded to ``alpha.dtype`` and RMS-normalised, one launch."""
+    """Rows ``ids`` of a block-quantised table decoded to ``alpha.dtype`` and RMS-normalised: one launch
+    for Q4_0 / Q8_0 and the K-quant formats at the usual row lengths, lookup followed by the norm otherwise."""
     from .quantized import QTensor  # local import: quantized imports this module
 
     if not isinstance(qtensor, QTensor) or len(qtensor.shape) != 2:
