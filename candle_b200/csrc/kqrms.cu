@@ -19,8 +19,9 @@ namespace {
 
 constexpr int kRowDecode = 0, kRowMasked = 1, kRowBadId = 2;
 
-// Per row slot, after the RowRegSmem area of the CTA: two staging buffers, their barriers, the kinds of
-// the rows they hold and the slot's abort flag.
+// Per row slot, after the RowRegSmem area of the CTA: a ring of staging buffers, their barriers, the
+// kinds of the rows they hold and the slot's abort flag.
+constexpr int kKqStages = 3;
 struct KqStage {
   unsigned char* buf;
   uint64_t* bars;
@@ -28,11 +29,13 @@ struct KqStage {
   volatile int* abort_flag;
   __device__ KqStage(unsigned char* base, int stage_bytes) {
     buf = base;
-    bars = reinterpret_cast<uint64_t*>(base + 2 * static_cast<size_t>(stage_bytes));
-    kinds = reinterpret_cast<volatile int*>(bars + 2);
-    abort_flag = kinds + 2;
+    bars = reinterpret_cast<uint64_t*>(base + kKqStages * static_cast<size_t>(stage_bytes));
+    kinds = reinterpret_cast<volatile int*>(bars + kKqStages);
+    abort_flag = kinds + kKqStages;
   }
-  __host__ __device__ static size_t bytes(int stage_bytes) { return 2 * static_cast<size_t>(stage_bytes) + 16 + 16; }
+  __host__ __device__ static size_t bytes(int stage_bytes) {
+    return (kKqStages * static_cast<size_t>(stage_bytes) + kKqStages * 8 + (kKqStages + 1) * 4 + 15) & ~static_cast<size_t>(15);
+  }
 };
 
 template <int QT, int DT, int VPT>
@@ -76,20 +79,23 @@ __global__ void __launch_bounds__(256, 4) kq_rowreg_kernel(const QRmsArgs a) {
   };
 
   if (tx == 0) {
-    mbar_init(&st.bars[0], 1);
-    mbar_init(&st.bars[1], 1);
+    for (int s = 0; s < kKqStages; ++s) mbar_init(&st.bars[s], 1);
     mbar_init_fence();
     *st.abort_flag = 0;
-    if (first < a.rows) issue(first, 0);
+    for (int j = 0; j < kKqStages - 1; ++j)
+      if (first + j * stride < a.rows) issue(first + j * stride, j);
   }
   slot_sync();
 
   uint32_t phase = 0;  // one parity bit per stage
   int stage = 0;
-  for (int64_t row = first; row < a.rows; row += stride, stage ^= 1) {
-    // The other buffer held the previous row: its readers are past their decode, which precedes the
-    // slot-wide synchronisation every row ends with.  Refill it with the next row.
-    if (tx == 0 && row + stride < a.rows) issue(row + stride, stage ^ 1);
+  for (int64_t row = first; row < a.rows; row += stride, stage = stage + 1 == kKqStages ? 0 : stage + 1) {
+    // The buffer of the previous row is free: its readers are past their decode, which precedes the
+    // slot-wide synchronisation every row ends with.  Refill it with the row kKqStages - 1 ahead.
+    if (tx == 0) {
+      const int64_t ahead = row + static_cast<int64_t>(kKqStages - 1) * stride;
+      if (ahead < a.rows) issue(ahead, stage == 0 ? kKqStages - 1 : stage - 1);
+    }
     const int kind = st.kinds[stage];
     const unsigned char* buf = st.buf + static_cast<size_t>(stage) * stage_bytes;
     bool wait_ok = true;
@@ -117,14 +123,18 @@ __global__ void __launch_bounds__(256, 4) kq_rowreg_kernel(const QRmsArgs a) {
     for (int k = 0; k < VPT; ++k) accumulate_vec_w<DT>(h[k], wv[k], lsum, lw);
     bool replayed;
     const float m = resolve_row_m<DT, VPT>(h, lsum, lw, a.V, a.n, a.eps, a.flags, sm, sm.rows, replayed);
-    slot_sync();  // every thread of the slot is past its decode, and sees the abort flag
+    // (slots wider than a warp passed two named barriers inside resolve_row_m: every thread is past its
+    // decode and sees the abort flag)
+    if (tpr == 32) __syncwarp();
     if (*st.abort_flag) {
       if (tx == 0) {
         report_status(a.status, CB200_STATUS_WAIT_TIMEOUT, row, 0, a.vocab);
         // bounded second chance for the copies still in flight before the slot retires
-        if (kind == kRowDecode && !wait_ok) mbar_wait(&st.bars[stage], (phase >> stage) & 1u, a.wt.spins);
-        if (row + stride < a.rows && st.kinds[stage ^ 1] == kRowDecode)
-          mbar_wait(&st.bars[stage ^ 1], (phase >> (stage ^ 1)) & 1u, a.wt.spins);
+        for (int j = 0; j < kKqStages; ++j) {
+          const int64_t rj = row + static_cast<int64_t>((j - stage + kKqStages) % kKqStages) * stride;
+          if (rj < a.rows && st.kinds[j] == kRowDecode && !(j == stage && wait_ok))
+            mbar_wait(&st.bars[j], (phase >> j) & 1u, a.wt.spins);
+        }
         drain_pause();
       }
       return;
