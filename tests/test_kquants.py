@@ -199,3 +199,33 @@ def test_gpu_lookup_norm_long_rows(cb, qtype, dtype):
         # the norm forced onto its lane-per-row kernel: the same bits
         y2 = cb.qembedding_rms_norm(q, ids_tensor(ids), from_oracle(alpha, dtype), 1e-5, flags=cb.ops.FLAG_FORCE_LANEROW)
         assert torch.equal(y2.view(torch.int16), y.view(torch.int16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("qtype", ["q4k", "q6k"])
+def test_gpu_single_launch_lookup_norm_on_a_vocab_shard(cb, qtype):
+    # A slice of the vocabulary: ids outside it are rows of -0.0 going into the norm, an id outside the
+    # whole vocabulary is reported and its row left alone.  The single-launch kernel and the forced
+    # two-launch route (lookup, then the dense norm) must agree bit for bit on every other row.
+    gq = getattr(cb.GgmlDType, qtype.upper())
+    rng = np.random.default_rng(41)
+    vocab, hidden, n = 96, 2048, 500
+    table = make_kq_blocks(rng, qtype, vocab * hidden // 256).reshape(vocab, -1)
+    ids = rng.integers(0, vocab, size=(n,)).astype(np.int64)
+    ids[7] = vocab + 5
+    alpha = from_oracle(randn(rng, (hidden,), "bf16", 1.0, 0.1), "bf16")
+    part = cb.QTensor.from_raw(torch.from_numpy(table[32:64]), gq, (32, hidden), device="cuda")
+    kw = dict(vocab_range=(32, 64), vocab=vocab, check=False)
+    st1, st2 = cb.ops.new_status("cuda"), cb.ops.new_status("cuda")
+    y1 = cb.qembedding_rms_norm(part, ids_tensor(ids), alpha, 1e-5, status=st1, **kw)
+    y2 = cb.qembedding_rms_norm(part, ids_tensor(ids), alpha, 1e-5, status=st2, flags=cb.ops.FLAG_FORCE_LANEROW, **kw)
+    torch.cuda.synchronize()
+    keep = np.ones(n, bool)
+    keep[7] = False
+    keep_t = torch.from_numpy(keep).cuda()
+    assert torch.equal(y1[keep_t].view(torch.int16), y2[keep_t].view(torch.int16))
+    for st in (st1, st2):
+        assert int(st[0].item()) & 0xFFFFFFFF == 1  # CB200_STATUS_INVALID_INDEX
+    owned = (ids >= 32) & (ids < 64) & keep
+    rows = oracle.qembedding(table, qtype, ids[owned], "bf16")
+    assert np.array_equal(to_oracle(y1[torch.from_numpy(owned).cuda()]), oracle.rms_norm(rows, to_oracle(alpha), 1e-5, "bf16"))
