@@ -81,18 +81,18 @@ struct RowRegSmem {
   int4* chunks;  // [tpr] replay: {A, B - A, L, -}: while the sum's bit pattern stays in the
                  // binade that starts at L, a chunk adds A to an even and B to an odd one
   int4* segs;    // [tpr] replay: the same for runs of chunks, {A, B - A, L, first | count << 16}
-                 // (two more arrays of [tpr] follow segs: the second parts of chunks, and of runs, that
-                 // cross a binade)
+                 // (one more array of [tpr] follows segs: the second parts of runs that cross a binade)
   uint4* rows;   // [V]: h, parked for the replay
   __device__ RowRegSmem(unsigned char* base, int rpc, int tpr, int V, int ty) {
     unsigned char* mine = base + static_cast<size_t>(ty) * slot_bytes(tpr);
     chunks = reinterpret_cast<int4*>(mine);
     segs = chunks + tpr;
-    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 64);
+    red = reinterpret_cast<float*>(mine + static_cast<size_t>(tpr) * 48);
     pub = red + 48;
     rows = reinterpret_cast<uint4*>(base + static_cast<size_t>(rpc) * slot_bytes(tpr)) + static_cast<size_t>(ty) * V;
   }
-  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 64 + 52 * sizeof(float); }
+  // (48 bytes per thread; every byte of shared memory is taken from L1, where the data of loads in flight lands)
+  __host__ __device__ static size_t slot_bytes(int tpr) { return static_cast<size_t>(tpr) * 48 + 52 * sizeof(float); }
   __host__ __device__ static size_t bytes(int rpc, int tpr, int V, bool with_rows) {
     return static_cast<size_t>(rpc) * slot_bytes(tpr) + (with_rows ? static_cast<size_t>(rpc) * V * 16 : 0);
   }
@@ -227,8 +227,7 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
   // approximate running sum `t` also tells where the sum leaves the binade: the chunk is then cut at
   // that element -- {A, B} before it, the element itself (added for real by the walk), {A, B} after it
   // in the next binade.  A second crossing in one chunk leaves the chunk to the sequential fallback.
-  int4* chunks2 = segs + tpr;
-  int4* segs2 = chunks2 + tpr;
+  int4* segs2 = segs + tpr;
   uint32_t base = __float_as_uint(prefix) & ~1u;
   int e = static_cast<int>(base >> 23);
   const bool ok = (v0 < v1) && (prefix > 0.0f) && (e >= 67) && (e <= 187);  // 2^-60 .. 2^60
@@ -307,15 +306,13 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
     }
   }
   if (ncross >= 2) lo1 = 0xFFFFFFFFu;
-  // chunk record: {A, B - A, first bit pattern of the binade, crosses}; an unusable chunk gets a binade
+  // chunk record: {A, B - A, first bit pattern of the binade, -}; an unusable chunk gets a binade
   // start no running sum can reach, so the range check of the walk rejects it.  Only chunks that stay
   // in one binade take part in the composition below.
   const bool whole = lo1 != 0xFFFFFFFFu && ncross == 0;
   uint32_t inc_even = A1, inc_odd = A1 + BA1;
   const uint32_t lo = whole ? lo1 : 0xFFFFFFFFu;
-  chunks[tx] = make_int4(static_cast<int>(A1), static_cast<int>(BA1), static_cast<int>(lo1), ncross == 1 ? 1 : 0);
-  if (ncross == 1)
-    chunks2[tx] = make_int4(static_cast<int>(A2), static_cast<int>(BA2), static_cast<int>(lo2), __float_as_int(pcross));
+  chunks[tx] = make_int4(static_cast<int>(A1), static_cast<int>(BA1), static_cast<int>(ncross == 0 ? lo1 : 0xFFFFFFFFu), 0);
 
   // Runs of consecutive chunks of one warp that share a binade compose into one record: for an
   // even start the run adds A1 + (A1 odd ? B2 : A2), for an odd start B1 + (B1 odd ? A2 : B2).
@@ -378,20 +375,11 @@ __device__ __noinline__ float replay_sum_sq(const Row rows, int4* chunks, int4* 
       const uint32_t lo_c = static_cast<uint32_t>(k.z);
       const uint32_t S2 = S + static_cast<uint32_t>(k.x) + (S & 1u) * static_cast<uint32_t>(k.y);
       if (lo_c != 0xFFFFFFFFu && S >= lo_c && (S2 - lo_c) < 0x800000u) {
-        if (k.w == 0) {
-          S = S2;
-          return;
-        }
-        // the chunk crosses into the next binade: the crossing element for real, then the second part
-        const int4 k2 = chunks2[c];
-        const uint32_t lo_2 = static_cast<uint32_t>(k2.z);
-        const uint32_t S3 = __float_as_uint(__fadd_rn(__uint_as_float(S2), __int_as_float(k2.w)));
-        const uint32_t S4 = S3 + static_cast<uint32_t>(k2.x) + (S3 & 1u) * static_cast<uint32_t>(k2.y);
-        if (lo_2 != 0xFFFFFFFFu && S3 >= lo_2 && (S4 - lo_2) < 0x800000u) {
-          S = S4;
-          return;
-        }
+        S = S2;
+        return;
       }
+      // (a chunk that crosses a binade has its two parts in its run record only: if that did not apply,
+      // the prediction was off and the chunk is added element by element)
       const int c0 = min(V, c * vpc), c1 = min(V, c0 + vpc);
       S = __float_as_uint(sequential_sum_sq<DT, Row>(rows, c0, c1, __uint_as_float(S)));
     };
