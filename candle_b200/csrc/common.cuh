@@ -142,12 +142,11 @@ __device__ __forceinline__ uint4 floats_to_vec(const float (&f)[Elem<DT>::kPerVe
   }
 }
 
-// The -0.0 bit pattern of T replicated over a 16-byte vector (additive identity that keeps -0.0).
-template <int DT>
-__device__ __forceinline__ uint4 neg_zero_vec() {
-  uint32_t w = (DT == kDtF32) ? 0x80000000u : 0x80008000u;
-  return make_uint4(w, w, w, w);
-}
+// What a vocabulary shard writes for a row it does not own: zero BITS.  The shards' partial rows are
+// combined by adding their bit patterns as unsigned integers (one non-zero contributor per element),
+// which is exact for every value: -0.0, subnormals and NaN payloads come through unchanged, whatever a
+// floating-point reduction would make of them.
+__device__ __forceinline__ uint4 masked_row_vec() { return make_uint4(0, 0, 0, 0); }
 
 // 16-byte global accesses.  Inputs are read once: bypass L1 allocation; outputs are streamed.
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {

@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
   }
   __syncthreads();
 
-  auto classify = [&](int64_t row, uint64_t& id) -> int {  // 0 decode, 1 masked (-0.0), 2 bad id
+  auto classify = [&](int64_t row, uint64_t& id) -> int {  // 0 decode, 1 masked (zero bits), 2 bad id
     id = read_id(a.ids, a.id_dtype, row);
     if (id >= static_cast<uint64_t>(a.vocab)) return 2;
     if (id < static_cast<uint64_t>(a.vocab_begin) || id >= static_cast<uint64_t>(a.vocab_end)) return 1;
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
     } else if (kind == 1) {
       const int n_vec = static_cast<int>(out_row_bytes / 16);
       for (int v = tx; v < n_vec; v += kQGatherThreads)
-        stg_stream(reinterpret_cast<uint4*>(out_row) + v, neg_zero_vec<DT>());
+        stg_stream(reinterpret_cast<uint4*>(out_row) + v, masked_row_vec());
     } else if (tx == 0) {
       report_status(a.status, CB200_STATUS_INVALID_INDEX, row, static_cast<int64_t>(id), a.vocab);
     }

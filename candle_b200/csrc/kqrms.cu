@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(256, 4) kq_rowreg_kernel(const QRmsArgs a) {
       }
     } else {
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) h[k] = (kind == kRowMasked) ? neg_zero_vec<DT>() : make_uint4(0, 0, 0, 0);
+      for (int k = 0; k < VPT; ++k) h[k] = masked_row_vec();  // masked row or bad id
     }
     float lsum = 0.0f, lw = 0.0f;
 #pragma unroll

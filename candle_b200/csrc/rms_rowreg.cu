@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
       }
     } else {
 #pragma unroll
-      for (int k = 0; k < 2 * HB; ++k) h[k] = (kind == kRowMasked) ? neg_zero_vec<DT>() : make_uint4(0, 0, 0, 0);
+      for (int k = 0; k < 2 * HB; ++k) h[k] = masked_row_vec();  // masked row or bad id
     }
     bool need;
     float row_dmin;

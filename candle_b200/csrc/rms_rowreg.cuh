@@ -62,7 +62,7 @@ struct QRmsArgs {
   float eps;
   int flags;
   // Owner-writes-to-all mode for a vocabulary-sharded table: rows whose id lies outside
-  // [vocab_begin, vocab_end) are skipped instead of written as -0.0, and every finished row also
+  // [vocab_begin, vocab_end) are skipped instead of written as zero bits, and every finished row also
   // goes to `n_more` further buffers of the same shape (peers' memory mapped into this process).
   // owned_only == 2 (row-owner mode): a finished row goes to exactly one buffer, that of the rank
   // whose block of token rows contains it: destination r (y for r == 0, y_more[r - 1] otherwise)

@@ -54,9 +54,12 @@ int sharded_steps(void* comm, const void* qtable, int qtype, const void* ids, co
                             vocab_end, status, stream);
   if (rc != CB200_OK) return fail(rc, "cb200_sharded_qembedding_rms_norm: %s", cb200_last_error());
   if (comm != nullptr) {
-    const ncclDataType_t dt = out_dtype == CB200_DTYPE_F32 ? ncclFloat32 : (out_dtype == CB200_DTYPE_F16 ? ncclFloat16 : ncclBfloat16);
+    // The partial rows are summed as unsigned integers over their bit patterns: foreign rows are zero
+    // bits, so every word has one non-zero contributor and comes out unchanged, whatever it encodes.
+    const size_t bytes = static_cast<size_t>(n_ids) * hidden * elem_bytes(out_dtype);
+    const bool words = bytes % 4 == 0;
     rc = nccl_settle(static_cast<ncclComm_t>(comm),
-                     ncclAllReduce(scratch, scratch, static_cast<size_t>(n_ids) * hidden, dt, ncclSum,
+                     ncclAllReduce(scratch, scratch, words ? bytes / 4 : bytes, words ? ncclUint32 : ncclUint8, ncclSum,
                                    static_cast<ncclComm_t>(comm), reinterpret_cast<cudaStream_t>(stream)),
                      "ncclAllReduce", kCollectiveAcceptMs);
     if (rc != CB200_OK) return rc;

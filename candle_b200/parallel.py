@@ -4,9 +4,10 @@ Token rows are independent for every op here, so the default is to give each ran
 block of rows with the table and the norm weights replicated and no collective at all
 (``row_shard``).  The exception is a vocabulary-sharded table (the way candle's sharded loader
 splits dim 0, candle-nn/src/var_builder.rs:687-715): every rank looks all ids up in its slice of
-the table, writes rows it does not own as -0.0 -- the additive identity that also preserves a
--0.0 coming from the owner -- and one NCCL sum over NVLink assembles the rows, exactly, because
-each element has a single non-zero contributor.  The collective mirrors the only one candle has,
+the table, writes rows it does not own as zero bits, and one NCCL sum over NVLink assembles the
+rows.  The sum runs over the BIT PATTERNS taken as unsigned integers: each element has a single
+non-zero contributor, so its bits come through whatever they encode (-0.0, subnormals, NaN
+payloads), which a floating-point sum does not promise.  The collective mirrors the only one candle has,
 ``AllReduce: CustomOp1`` around ``Comm::all_reduce`` in
 candle-examples/examples/llama_multiprocess/model.rs:31-90.
 
@@ -41,6 +42,14 @@ def vocab_shard(vocab: int, rank: int, world: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
+def as_words(t: torch.Tensor) -> torch.Tensor:
+    """A contiguous tensor's storage as a flat integer tensor (32-bit words when the byte count
+    allows, bytes otherwise): what the shards' partial rows are summed as."""
+    flat = t.reshape(-1)
+    nbytes = flat.numel() * flat.element_size()
+    return flat.view(torch.int32) if nbytes % 4 == 0 else flat.view(torch.uint8)
+
+
 class ShardedQEmbedding:
     """A Q4_0 / Q8_0 table split by vocabulary over the ranks of ``group``.
 
@@ -65,7 +74,7 @@ class ShardedQEmbedding:
 
         part = self.partial(ids, check=check)
         if self.world > 1:
-            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+            dist.all_reduce(as_words(part), op=dist.ReduceOp.SUM, group=self.group)
         return part
 
     def forward_rms_norm(self, ids: torch.Tensor, alpha: torch.Tensor, eps: float, *, scatter: bool = False,
@@ -78,13 +87,13 @@ class ShardedQEmbedding:
         if self.world == 1:
             return ops.rms_norm(flat, alpha, eps).reshape(part.shape)
         if not scatter:
-            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+            dist.all_reduce(as_words(flat), op=dist.ReduceOp.SUM, group=self.group)
             return ops.rms_norm(flat, alpha, eps).reshape(part.shape)
         rows = flat.shape[0]
         if rows % self.world != 0:
             raise CandleError(f"reduce-scatter needs the {rows} token rows to divide by the world size {self.world}")
         mine = torch.empty(rows // self.world, hidden, dtype=flat.dtype, device=flat.device)
-        dist.reduce_scatter_tensor(mine, flat, op=dist.ReduceOp.SUM, group=self.group)
+        dist.reduce_scatter_tensor(as_words(mine), as_words(flat), op=dist.ReduceOp.SUM, group=self.group)
         return ops.rms_norm(mine, alpha, eps)
 
     def forward_rms_norm_owner(self, ids: torch.Tensor, alpha: torch.Tensor, eps: float, dst_ptrs, *,

@@ -86,7 +86,7 @@ class QTensor:
                   vocab: int | None = None) -> torch.Tensor:
         """Rows ``ids`` decoded to ``dtype``: ``dequantize().to_dtype(dtype).embedding(ids)`` without
         the decoded table.  With ``vocab_range=(begin, end)`` this tensor holds only that slice of
-        a ``vocab``-row table and ids outside it give rows of -0.0 (see cb200_qembedding)."""
+        a ``vocab``-row table and ids outside it give rows of zero bits (see cb200_qembedding)."""
         if len(self.shape) != 2:
             raise CandleError("embedding expects a rank-2 table")
         if dtype not in _DTYPES:

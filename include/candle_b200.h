@@ -242,9 +242,10 @@ CB200_API int cb200_dequantize(const void* blocks, int qtype, void* out, int64_t
  * (candle-transformers/src/models/quantized_llama.rs:378-379, candle-nn/src/embedding.rs:29-36)
  * without materialising the decoded table.  The reference has no such device entry point.
  * Vocab sharding: `qtable` holds rows [vocab_begin, vocab_end) of the full table; ids inside that
- * range are decoded, ids outside it (but < vocab) produce rows of -0.0, the value that keeps a
- * sum over shards bit-exact; pass 0 and `vocab` for an unsharded table.  ids >= vocab are reported
- * through `status`.
+ * range are decoded, ids outside it (but < vocab) produce rows of zero BITS, so that adding the
+ * shards' partial rows as unsigned integers (one non-zero contributor per element) assembles the
+ * unsharded result bit for bit, -0.0, subnormals and NaN payloads included; pass 0 and `vocab` for
+ * an unsharded table.  ids >= vocab are reported through `status`.
  */
 CB200_API int cb200_qembedding(const void* qtable, int qtype, const void* ids, void* out, int64_t vocab,
                      int32_t hidden, int64_t n_ids, int out_dtype, int id_dtype, int64_t vocab_begin,

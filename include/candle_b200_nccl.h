@@ -40,9 +40,13 @@ CB200_API int cb200_nccl_comm_init_timeout(void** comm_out, int nranks, const vo
 
 /*
  * Vocabulary-sharded cb200_qembedding -> sum over ranks -> rms_norm, enqueued on `stream`:
- *   scratch = masked lookup of ALL ids in this rank's rows [vocab_begin, vocab_end) (-0.0 elsewhere)
- *   scratch = ncclAllReduce(scratch, sum)            (exact: one non-zero contributor per element)
+ *   scratch = masked lookup of ALL ids in this rank's rows [vocab_begin, vocab_end) (zero bits elsewhere)
+ *   scratch = ncclAllReduce(scratch, sum over the bit patterns taken as unsigned integers)
  *   y       = rms_norm(scratch, alpha, eps)
+ * Each element has one non-zero contributor, so the integer sum returns that contributor's bits
+ * whatever they encode.  A floating-point sum does not: NCCL's bf16 sum over 8 GPUs returned +0.0
+ * where every rank held -0.0 and altered NaN payloads on large buffers, while its 2- and 4-GPU sums
+ * (and the 8-GPU sum of a small buffer) kept them.
  * `scratch` is caller-provided device memory of at least n_ids * hidden * sizeof(out_dtype)
  * bytes, 16-byte aligned; its contents after the call are the gathered rows.  The reference has
  * no such entry point: its embedding is replicated under tensor parallelism

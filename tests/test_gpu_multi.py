@@ -1,6 +1,6 @@
 """Multi-GPU checks (need >= 2 CUDA devices; skipped otherwise): the vocab-sharded lookup summed by
-NCCL equals the unsharded CPU oracle bit for bit (-0.0 included), with and without the
-reduce-scatter variant, with the owner-writes-to-all and the row-owner variants over peer-mapped
+NCCL equals the unsharded CPU oracle bit for bit (-0.0 included: the sum runs on the bit patterns),
+with and without the reduce-scatter variant, with the owner-writes-to-all and the row-owner variants over peer-mapped
 buffers, and through the C entry points (caller scratch and built-in scratch) with a communicator."""
 import os
 import socket

@@ -394,8 +394,9 @@ def test_qembedding_matches_oracle(cb, qtype, out_dtype):
 
 @pytest.mark.parametrize("qtype", ["q8_0", "q4_0", "q5_1"])
 def test_vocab_sharded_partials_sum_to_the_unsharded_lookup(cb, qtype):
-    # Each shard decodes the ids it owns and writes -0.0 elsewhere; summing the partials in bf16
-    # (what the all-reduce does) must reproduce the unsharded lookup bit for bit, -0.0 included.
+    # Each shard decodes the ids it owns and writes zero bits elsewhere; adding the partials' bit patterns
+    # as 32-bit integers (what the all-reduce does) must reproduce the unsharded lookup bit for bit, -0.0
+    # included.
     rng = np.random.default_rng(17)
     gq = getattr(cb.GgmlDType, qtype.upper())
     vocab, hidden, n = 512, 1024, 300
@@ -409,8 +410,9 @@ def test_vocab_sharded_partials_sum_to_the_unsharded_lookup(cb, qtype):
         for s in range(shards):
             q = cb.QTensor.from_raw(torch.from_numpy(qt[s * per:(s + 1) * per]), gq, (per, hidden), device="cuda")
             part = q.embedding(ids_tensor(ids), torch.bfloat16, vocab_range=(s * per, (s + 1) * per), vocab=vocab)
-            total = part if total is None else total + part
-        assert np.array_equal(to_oracle(total), want)
+            words = part.view(torch.int32)
+            total = words if total is None else total + words
+        assert np.array_equal(to_oracle(total.view(torch.bfloat16)), want)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -158,13 +158,12 @@ def test_gpu_lookup_and_lookup_norm(cb, qtype, dtype):
     tdt = torch.float32 if dtype == "f32" else torch.bfloat16
     rows = oracle.qembedding(table, qtype, ids, dtype)
     assert np.array_equal(to_oracle(q.embedding(ids_tensor(ids), tdt)), rows)
-    # a vocabulary shard: ids outside it give -0.0
+    # a vocabulary shard: ids outside it give rows of zero bits
     part = q_part = cb.QTensor.from_raw(torch.from_numpy(table[50:150]), gq, (100, hidden), device="cuda")
     got = to_oracle(part.embedding(ids_tensor(ids), tdt, vocab_range=(50, 150), vocab=vocab))
     owned = (ids >= 50) & (ids < 150)
     assert np.array_equal(got[owned], rows[owned])
-    neg0 = np.uint32(0x80000000) if dtype == "f32" else np.uint16(0x8000)
-    assert (got[~owned].view(neg0.dtype) == neg0).all()
+    assert not got[~owned].view(np.uint8).any()
     del q_part
     alpha = randn(rng, (hidden,), dtype, 1.0, 0.1)
     y, g = cb.qembedding_rms_norm(q, ids_tensor(ids), from_oracle(alpha, dtype), 1e-5, return_gathered=True)
@@ -204,7 +203,7 @@ def test_gpu_lookup_norm_long_rows(cb, qtype, dtype):
 @pytest.mark.gpu
 @pytest.mark.parametrize("qtype", ["q4k", "q6k"])
 def test_gpu_single_launch_lookup_norm_on_a_vocab_shard(cb, qtype):
-    # A slice of the vocabulary: ids outside it are rows of -0.0 going into the norm, an id outside the
+    # A slice of the vocabulary: ids outside it are rows of zeros going into the norm, an id outside the
     # whole vocabulary is reported and its row left alone.  The single-launch kernel and the forced
     # two-launch route (lookup, then the dense norm) must agree bit for bit on every other row.
     gq = getattr(cb.GgmlDType, qtype.upper())

@@ -136,6 +136,42 @@ def test_gpu_softmax_f32_staged_and_scalar_kernels_agree(cb):
     assert np.array_equal((e / tot).astype(np.float32).view(np.uint32), ya[100].cpu().numpy().view(np.uint32))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("n", [2048, 136])
+def test_gpu_softmax16_staged_and_scalar_kernels_agree(cb, dtype, n):
+    # The staged kernel takes T(exp(T(x - max))) from a table over the magnitudes that matter and divides
+    # by reciprocal (bf16) or in three instructions (f16); the scalar kernel evaluates every element and
+    # divides for real.  Bit-equal on rows that reach every corner: spreads from 1e-3 to beyond the
+    # underflow point (the table's two ends, results that are subnormal in T, rows whose quotients could
+    # be), -inf entries, NaN entries, rows of one repeated value, rows that are all -inf.
+    tdt = TORCH_DT[dtype]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11 + n)
+    rows = 1536
+    scale = torch.logspace(-3, 2.1, rows, device="cuda").unsqueeze(1)
+    x = (torch.randn(rows, n, device="cuda", generator=g) * scale).to(tdt)
+    x[::7, 5] = float("-inf")
+    x[3::11, 9] = float("nan")
+    x[4::97] = 1.5
+    x[5::101] = float("-inf")
+    x[6::103, : n // 2] = -30000.0 if dtype == "f16" else -1e30
+    store = torch.empty(rows * n + 8, dtype=tdt, device="cuda")
+    xu = store[1:1 + rows * n].view(rows, n)
+    xu.copy_(x)
+    assert x.data_ptr() % 16 == 0 and xu.data_ptr() % 16 == 2
+    ya, yu = cb.softmax_last_dim(x), cb.softmax_last_dim(xu)
+    nan = torch.isnan(ya)
+    assert torch.equal(nan, torch.isnan(yu))
+    a, u = ya.view(torch.int16), yu.view(torch.int16)
+    assert torch.equal(a[~nan], u[~nan]), f"{(a[~nan] != u[~nan]).sum().item()} elements differ"
+    # and a slice of ordinary rows against the oracle, within the stated tolerance
+    want = oracle.cast_to_f32(oracle.softmax_last_dim(to_oracle(x[600:700]), dtype), dtype)
+    got = oracle.cast_to_f32(to_oracle(ya[600:700]), dtype)
+    ok = ~np.isnan(want)
+    assert np.abs(got[ok] - want[ok]).max() <= TOL[dtype]
+
+
 ROPE_SHAPES = [(2, 5, 10, 16), (1, 3, 7, 6), (2, 8, 33, 128), (1, 32, 64, 64), (3, 2, 5, 2)]
 
 

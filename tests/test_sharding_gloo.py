@@ -1,7 +1,8 @@
 """World-size-2 (and 4) CPU runs over gloo of the vocab-sharded path.
 
 ``test_masked_partials_sum_to_unsharded_lookup``: the algebra -- every rank decodes the ids it owns,
-writes -0.0 elsewhere, and the sum over ranks equals the unsharded lookup bit for bit.
+writes zero bits elsewhere, and the sum of the bit patterns over ranks equals the unsharded lookup bit
+for bit (-0.0 included).
 ``test_sharded_embedding_host_logic``: the library's own ``ShardedQEmbedding`` driven over gloo --
 shard arithmetic, the all-reduce and the reduce-scatter route with its row split, reshapes and error
 cases.  There is no GPU here, so the two device steps the class calls (the masked lookup of its table
@@ -44,14 +45,14 @@ def _worker(rank, world, port, qtype, ret):
         ids = rng.integers(0, vocab, size=n).astype(np.uint32)
         begin, end = vocab_shard(vocab, rank, world)
         owned = (ids >= begin) & (ids < end)
-        part = np.full((n, hidden), 0x8000, dtype=np.uint16)  # bf16 -0.0
+        part = np.zeros((n, hidden), dtype=np.uint16)  # foreign rows: zero bits
         if owned.any():
             part[owned] = oracle.qembedding(qt[begin:end], qtype, (ids[owned] - begin).astype(np.uint32), "bf16")
-        # bf16 sum over ranks; each element has one non-zero contributor, so summing in f32 and
-        # rounding back is the exact bf16 sum NCCL computes
-        t = torch.from_numpy(part.view(np.int16)).view(torch.bfloat16).to(torch.float32)
+        # the sum over ranks runs on the bit patterns as 32-bit integers, as the product's collective does:
+        # each word has one non-zero contributor
+        t = torch.from_numpy(part.view(np.int32).copy())
         dist.all_reduce(t)
-        total = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+        total = t.numpy().view(np.uint16).reshape(n, hidden)
         want = oracle.qembedding(qt, qtype, ids, "bf16")
         ok = np.array_equal(total, want)
         # the row-sharded continuation: each rank normalises its block of rows; together = unsharded
@@ -91,7 +92,7 @@ class _CpuTable:
         assert flat.max() < vocab
         begin, end = vocab_range
         owned = (flat >= begin) & (flat < end)
-        part = np.full((flat.size, self.shape[1]), 0x8000, dtype=np.uint16)
+        part = np.zeros((flat.size, self.shape[1]), dtype=np.uint16)
         if owned.any():
             part[owned] = oracle.qembedding(self.qt, self.qtype, (flat[owned] - begin).astype(np.uint32), "bf16")
         return torch.from_numpy(part.view(np.int16)).view(torch.bfloat16).reshape(tuple(ids.shape) + (self.shape[1],))
