@@ -90,3 +90,11 @@ def make_kq_blocks(rng, qtype, n_blocks):
     else:
         raw[:, 0:4] = np.abs(rng.standard_normal(n_blocks) * 0.01).astype(np.float32).view(np.uint8).reshape(n_blocks, 4)
     return raw
+
+
+def stable_seed(*parts) -> int:
+    """A seed that depends only on the test's parameters (Python's own hash() of a string changes from
+    one process to the next)."""
+    import zlib
+
+    return zlib.crc32(repr(parts).encode())

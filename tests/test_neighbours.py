@@ -14,7 +14,7 @@ import torch
 
 import oracle
 from conftest import round4
-from helpers import TORCH_DT, bits, from_oracle, ids_tensor, randn, to_oracle
+from helpers import TORCH_DT, bits, from_oracle, ids_tensor, randn, stable_seed, to_oracle
 
 TOL = {"f32": 1e-5, "f16": 1e-2, "bf16": 1e-2}
 
@@ -90,7 +90,7 @@ SOFTMAX_SHAPES = [(1, 1), (3, 7), (5, 31), (4, 33), (9, 100), (64, 128), (40, 10
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("shape", SOFTMAX_SHAPES)
 def test_gpu_softmax_matches_oracle(cb, dtype, shape):
-    rng = np.random.default_rng(hash((dtype, shape)) & 0xFFFF)
+    rng = np.random.default_rng(stable_seed(dtype, shape))
     x = randn(rng, shape, dtype, 0.0, 3.0)
     if len(shape) == 4:  # attention scores with a causal mask: -inf above the diagonal
         xf = oracle.cast_to_f32(x, dtype)
@@ -103,7 +103,8 @@ def test_gpu_softmax_matches_oracle(cb, dtype, shape):
     same = bits(got) == (want.view(np.uint32) if dtype == "f32" else want)
     # exp comes from two math libraries: allow the rare last-bit disagreement, nothing systematic
     if dtype == "f32":
-        assert np.abs(g - w).max() <= 2.0 ** -22 and same.mean() > 0.97
+        assert np.abs(g - w).max() <= 2.0 ** -22
+        assert (~same).sum() <= max(2, 0.03 * same.size), f"{(~same).sum()} of {same.size} elements differ"
     else:
         assert same.mean() > 0.999, f"{(~same).sum()} of {same.size} elements differ"
 
@@ -180,7 +181,7 @@ ROPE_SHAPES = [(2, 5, 10, 16), (1, 3, 7, 6), (2, 8, 33, 128), (1, 32, 64, 64), (
 @pytest.mark.parametrize("shape", ROPE_SHAPES)
 @pytest.mark.parametrize("variant", ["rope_i", "rope", "rope_thd"])
 def test_gpu_rope_matches_oracle(cb, variant, shape, dtype):
-    rng = np.random.default_rng(hash((variant, shape, dtype)) & 0xFFFF)
+    rng = np.random.default_rng(stable_seed(variant, shape, dtype))
     b, h, t, d = shape
     xs = (b, t, h, d) if variant == "rope_thd" else shape
     x = randn(rng, xs, dtype)
