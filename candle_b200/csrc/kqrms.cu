@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(256, 4) kq_rowreg_kernel(const QRmsArgs a) {
         for (int k = 0; k < VPT; ++k) stg_stream(g + k * tpr, h[k]);
       }
       // 2^-60 <= m <= 2^60: the reciprocal is a normal number and the margin argument applies
-      const bool fast_div = (DT == kDtBF16) && (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
+      const bool fast_div = (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
       const float r = fast_div ? __frcp_rn(m) : 0.0f;
       uint4* yr = a.y + row * a.V + tx;
 #pragma unroll

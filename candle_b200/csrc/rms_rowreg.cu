@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(BT, 768 / BT) rms_rowreg_kernel(const RmsRowRe
         for (int k = 0; k < VPT; ++k) stg_stream(so + k * tpr, h[k]);
       }
       // 2^-60 <= m <= 2^60: the reciprocal is a normal number and the margin argument applies
-      const bool fast_div = (DT == kDtBF16) && (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
+      const bool fast_div = (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
       const float r = fast_div ? __frcp_rn(m) : 0.0f;
       uint4* yr = a.y + row * a.V + tx;
 #pragma unroll
@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
           stg_stream(g + 2 * p + 1, h[2 * j + 1]);
         }
       }
-      const bool fast_div = (DT == kDtBF16) && (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
+      const bool fast_div = (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
       const float r = fast_div ? __frcp_rn(m) : 0.0f;
       uint4* yr = a.y + row * a.V;
       if (OWNER == kOwnerToRowOwner) {
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
       // the multiplications; anything else calls the guarded form out of line.
       // (rows of a dense table carry no scales to bound their elements by: bf16 keeps the guard)
       const bool plain =
-          (DT != kDtBF16) || (QT != kQTypeDense16 && fast_div && row_dmin >= 9.0949470e-13f);
+          fast_div && ((DT != kDtBF16) || (QT != kQTypeDense16 && row_dmin >= 9.0949470e-13f));
       if (QT == kQTypeDense16 && !plain) {
 #pragma unroll
         for (int j = 0; j < HB; ++j) {

@@ -575,12 +575,35 @@ __device__ __forceinline__ void accumulate_vec_w(const uint4& h, float weight, f
   lw = fmaf(vs, weight, lw);
 }
 
-// y = T(T(h / m) * alpha) for one vector; r = 1/m when fast_div.
+// x / m correctly rounded to f32 in three instructions, for finite x and 2^-60 <= m <= 2^60 with
+// r = RN(1 / m) (Markstein: q = RN(x r) is within an ulp, q m - x is exact in an FMA, one correction
+// step lands on the rounded quotient; checked against the division for every pair of f16 values).
+// The sign of a zero result is not defined by this sequence: callers take it from x.
+__device__ __forceinline__ float quotient_by_reciprocal(float x, float m, float r) {
+  const float q = __fmul_rn(x, r);
+  const float t = __fmaf_rn(q, m, -x);
+  return __fmaf_rn(-t, r, q);
+}
+
+// T(h / m) for the two f16 values of `w` (f32 quotient, then one rounding to f16, as crate `half`
+// divides), sign bits taken from `w`: every quotient has the sign of its numerator, zeros included.
+template <int DT>
+__device__ __forceinline__ uint32_t quotient2_f16(uint32_t w, float m, float r) {
+  const float2 hf = unpack2<DT>(w);
+  const uint32_t q = pack2<DT>(quotient_by_reciprocal(hf.x, m, r), quotient_by_reciprocal(hf.y, m, r));
+  return (q & 0x7FFF7FFFu) | (w & 0x80008000u);
+}
+
+// y = T(T(h / m) * alpha) for one vector; r = 1/m when fast_div (2^-60 <= m <= 2^60: bf16 multiplies by
+// r, f16 uses the three-instruction quotient; a row with an infinity or a NaN has no such m).
 // GUARD = false is for callers that know no element of the row is tiny and non-zero.
 template <int DT, bool GUARD = true>
 __device__ __forceinline__ uint4 rms_output_vec(const uint4& h, const uint4& alpha, float m, float r, bool fast_div) {
   const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
   const uint32_t aw[4] = {alpha.x, alpha.y, alpha.z, alpha.w};
+  if (DT != kDtBF16 && fast_div)
+    return make_uint4(mul2_rn<DT>(quotient2_f16<DT>(hw[0], m, r), aw[0]), mul2_rn<DT>(quotient2_f16<DT>(hw[1], m, r), aw[1]),
+                      mul2_rn<DT>(quotient2_f16<DT>(hw[2], m, r), aw[2]), mul2_rn<DT>(quotient2_f16<DT>(hw[3], m, r), aw[3]));
   float q[8];
   if (fast_div) {
     float amin = 3.0e38f;
@@ -616,8 +639,8 @@ __device__ __forceinline__ uint4 rms_output_vec(const uint4& h, const uint4& alp
 }
 
 // The common case of rms_output_vec only, for callers that have established it holds for the whole
-// row: bf16 with 2^-60 <= m <= 2^60 and no tiny non-zero element (quotient = product with r = 1/m),
-// or f16 (always the division).  Kept apart so that hot loops carry nothing else.
+// row: 2^-60 <= m <= 2^60 and, for bf16, no tiny non-zero element (quotient = product with r = 1/m;
+// f16: the three-instruction quotient).  Kept apart so that hot loops carry nothing else.
 template <int DT>
 __device__ __forceinline__ uint4 rms_output_plain(const uint4& h, const uint4& alpha, float m, float r) {
   const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
@@ -625,9 +648,13 @@ __device__ __forceinline__ uint4 rms_output_plain(const uint4& h, const uint4& a
   uint32_t o[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 hf = unpack2<DT>(hw[i]);
-    const uint32_t q = (DT == kDtBF16) ? pack2<DT>(__fmul_rn(hf.x, r), __fmul_rn(hf.y, r))
-                                       : pack2<DT>(__fdiv_rn(hf.x, m), __fdiv_rn(hf.y, m));
+    uint32_t q;
+    if (DT == kDtBF16) {
+      const float2 hf = unpack2<DT>(hw[i]);
+      q = pack2<DT>(__fmul_rn(hf.x, r), __fmul_rn(hf.y, r));
+    } else {
+      q = quotient2_f16<DT>(hw[i], m, r);
+    }
     o[i] = mul2_rn<DT>(q, aw[i]);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
@@ -645,7 +672,10 @@ __device__ __forceinline__ uint4 rms_output_floats(const float (&hf)[8], const u
                                                    bool fast_div) {
   const uint32_t aw[4] = {alpha.x, alpha.y, alpha.z, alpha.w};
   float q[8];
-  if (fast_div) {
+  if (DT != kDtBF16 && fast_div) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = copysignf(quotient_by_reciprocal(hf[i], m, r), hf[i]);
+  } else if (fast_div) {
     float amin = 3.0e38f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {

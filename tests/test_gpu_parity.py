@@ -310,6 +310,40 @@ def test_norm_special_values_and_aliasing(cb):
         assert_norm_equal(xt, want, dtype)
 
 
+@pytest.mark.parametrize("hidden", [8192, 4096, 1024])
+def test_f16_rms_norm_quotients_over_the_whole_f16_range(cb, hidden):
+    # f16 rows divide by the row's m through a reciprocal and one correction step instead of the division
+    # instruction: rows whose scale sweeps m over 2^-12 ... 2^12, every row salted with +0, -0, the largest
+    # and smallest subnormals, the smallest normal and (where the sum of squares allows) large values; one
+    # row with an infinity and one with a NaN (no usable m: those take the division); residual on and off.
+    rng = np.random.default_rng(77)
+    rows = 96
+    scale = np.exp2(rng.uniform(-12, 12, size=(rows, 1))).astype(np.float32)
+    x = (rng.standard_normal((rows, hidden)).astype(np.float32) * scale)
+    salt = np.asarray([0.0, -0.0, 5.9604645e-08, -5.9604645e-08, 6.0975552e-05, -6.0975552e-05, 6.1035156e-05,
+                       -6.1035156e-05], np.float32)
+    for r in range(rows):
+        pos = rng.choice(hidden, size=salt.size, replace=False)
+        x[r, pos] = salt
+    x[5, 17], x[9, 3] = np.inf, np.nan
+    x[11, :] = 0.0
+    x[11, 40] = -0.0
+    xo = oracle.cast_from_f32(np.clip(x, -65504, 65504, out=x, where=np.isfinite(x)), "f16")
+    a = randn(rng, (hidden,), "f16", 1.0, 0.3)
+    res = randn(rng, (rows, hidden), "f16", 0.0, 0.01)
+    xt, at, rt = from_oracle(xo, "f16"), from_oracle(a, "f16"), from_oracle(res, "f16")
+
+    def same(got, want):  # bit for bit, except that a NaN may carry any payload
+        g = to_oracle(got)
+        g_nan, w_nan = (g & 0x7FFF) > 0x7C00, (want & 0x7FFF) > 0x7C00
+        return np.array_equal(g_nan, w_nan) and np.array_equal(g[~w_nan], want[~w_nan])
+
+    for eps in (1e-5, 0.0):
+        assert same(cb.rms_norm(xt, at, eps), oracle.rms_norm(xo, a, eps, "f16"))
+        h = oracle.add(xo, res, "f16")
+        assert same(cb.rms_norm(xt, at, eps, residual=rt), oracle.rms_norm(h, a, eps, "f16"))
+
+
 # ------------------------------------------------------------------------------------------------
 # gathers
 # ------------------------------------------------------------------------------------------------
