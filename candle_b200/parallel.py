@@ -45,6 +45,8 @@ def vocab_shard(vocab: int, rank: int, world: int) -> tuple[int, int]:
 def as_words(t: torch.Tensor) -> torch.Tensor:
     """A contiguous tensor's storage as a flat integer tensor (32-bit words when the byte count
     allows, bytes otherwise): what the shards' partial rows are summed as."""
+    if not t.is_contiguous():
+        raise CandleError("the rows to be summed over the ranks must be contiguous")
     flat = t.reshape(-1)
     nbytes = flat.numel() * flat.element_size()
     return flat.view(torch.int32) if nbytes % 4 == 0 else flat.view(torch.uint8)

@@ -161,3 +161,20 @@ def test_sharded_embedding_host_logic(world):
     ret = mgr.dict()
     mp.spawn(_host_logic_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def test_as_words_views_the_same_storage():
+    # what the ranks' partial rows are summed as: 32-bit words over the same bytes (bytes for an odd
+    # number of 16-bit values); a non-contiguous tensor is refused instead of being copied silently
+    from candle_b200 import CandleError
+    from candle_b200.parallel import as_words
+
+    t = torch.arange(12, dtype=torch.float32).to(torch.bfloat16).reshape(3, 4)
+    w = as_words(t)
+    assert w.dtype == torch.int32 and w.numel() == 6 and w.data_ptr() == t.data_ptr()
+    w += w  # doubling the words in place is visible through the original tensor's storage
+    assert t.view(torch.int16).reshape(-1)[1].item() == 2 * torch.tensor(1.0).to(torch.bfloat16).view(torch.int16).item()
+    odd = torch.zeros(3, dtype=torch.float16)
+    assert as_words(odd).dtype == torch.uint8 and as_words(odd).numel() == 6
+    with pytest.raises(CandleError):
+        as_words(t.t())
