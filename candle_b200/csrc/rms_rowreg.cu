@@ -374,8 +374,7 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int p = half_block(j);
-          stg_stream(g + 2 * p, h[2 * j]);
-          stg_stream(g + 2 * p + 1, h[2 * j + 1]);
+          stg_stream_pair(g + 2 * p, h[2 * j], h[2 * j + 1], a.wide);
         }
       }
       const bool fast_div = (m >= 8.6736174e-19f) && (m <= 1.1529215e18f);
@@ -393,16 +392,11 @@ __global__ void __launch_bounds__(128, 4) qrms_rowslot_kernel(const QRmsArgs a, 
       // 1/m (m <= 2^60) can fall under 2^-100, and the guard can go.
       // one finished 32-byte piece to the local buffer and to every further destination
       auto put = [&](int p, const uint4& lo, const uint4& hi) {
-        stg_stream(yr + 2 * p, lo);
-        stg_stream(yr + 2 * p + 1, hi);
+        stg_stream_pair(yr + 2 * p, lo, hi, a.wide);
         if (OWNER == kOwnerToAll) {
 #pragma unroll
           for (int d = 0; d < 7; ++d) {
-            if (d < a.n_more) {
-              uint4* dst = a.y_more[d] + row * a.V + 2 * p;
-              stg_stream(dst, lo);
-              stg_stream(dst + 1, hi);
-            }
+            if (d < a.n_more) stg_stream_pair(a.y_more[d] + row * a.V + 2 * p, lo, hi, a.wide);
           }
         }
       };
@@ -581,6 +575,10 @@ template <int QT, int DT, int HB>
 static cudaError_t launch_q_t(const QRmsArgs& a_in, int tpr, cudaStream_t stream) {
   QRmsArgs a = a_in;
   a.wt = wait_tuning();
+  // every output buffer on a 32-byte boundary (rows are multiples of 64 bytes): 256-bit stores
+  auto aligned32 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; };
+  a.wide = aligned32(a.y) && aligned32(a.gathered);
+  for (int d = 0; d < a.n_more && d < 7; ++d) a.wide = a.wide && aligned32(a.y_more[d]);
   const int rpc = 128 / tpr;  // row slots per 128-thread CTA
   const int ctas = 4;         // CTAs per SM: the register budget (alpha stays resident) and the barriers admit four
   const int stage_bytes = (a.row_bytes + 15) & ~15;

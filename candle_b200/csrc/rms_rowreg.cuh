@@ -69,6 +69,7 @@ struct QRmsArgs {
   // holds rows [row_bounds[r], row_bounds[r + 1]) as a [rows_r, V] tensor of its own.
   int owned_only;
   int n_more;
+  int wide;  // filled by the launcher: every destination is 32-byte aligned
   uint4* y_more[7];
   int64_t row_bounds[9];
   WaitTuning wt;  // filled by the launcher
