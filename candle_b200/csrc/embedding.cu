@@ -166,13 +166,14 @@ cudaError_t launch_gather_rows(const GatherArgs& a_in, cudaStream_t stream) {
 constexpr int kQGatherStages = 2;
 constexpr int kQGatherThreads = 256;
 
+// `wide`: the f32 destination is 32-byte aligned, so a lane's eight values go out in one 256-bit store
 template <int DT>
-__device__ __forceinline__ void store_decoded(void* out_row, int v, const float (&f)[8]) {
+__device__ __forceinline__ void store_decoded(void* out_row, int v, const float (&f)[8], bool wide) {
   if constexpr (DT == kDtF32) {
     uint4* o = static_cast<uint4*>(out_row) + 2 * v;
-    stg_stream(o, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
-    stg_stream(o + 1,
-               make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
+    stg_stream_pair(o, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])),
+                    make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])),
+                    wide);
   } else {
     stg_stream(static_cast<uint4*>(out_row) + v, make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]),
                                                             pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7])));
@@ -187,6 +188,8 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kQGatherStages * stage_bytes);
   const int V = a.n / 8;
   const size_t out_row_bytes = static_cast<size_t>(a.n) * Elem<DT>::kBytes;
+  // (f32 rows are multiples of 128 bytes: a 32-byte aligned base makes every lane's 32 bytes aligned)
+  const bool wide = (reinterpret_cast<uintptr_t>(a.out) & 31u) == 0;
 
   if (tx == 0) {
     for (int s = 0; s < kQGatherStages; ++s) mbar_init(&bars[s], 1);
@@ -250,7 +253,7 @@ __global__ void __launch_bounds__(kQGatherThreads) qgather_kernel(const QGatherA
       for (int v = tx; v < V; v += kQGatherThreads) {
         float f[8];
         decode8<QT, true>(buf, v, f);  // the staged row starts on a 16-byte boundary
-        store_decoded<DT>(out_row, v, f);
+        store_decoded<DT>(out_row, v, f, wide);
       }
     } else if (kind == 1) {
       const int n_vec = static_cast<int>(out_row_bytes / 16);
@@ -417,6 +420,7 @@ template <int QT, int DT>
 __global__ void __launch_bounds__(256) dequantize_flat_kernel(const unsigned char* __restrict__ blocks,
                                                               void* __restrict__ out, int64_t n_vec, int aligned16) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const bool wide = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
   for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec; v += stride) {
     constexpr int kVecs = qblock_elems(QT) / 8;  // 8-element groups per block
     const unsigned char* blk = blocks + (v / kVecs) * QBlock<QT>::kBytes;
@@ -427,7 +431,7 @@ __global__ void __launch_bounds__(256) dequantize_flat_kernel(const unsigned cha
       decode8<QT, false>(blk, static_cast<int>(v % kVecs), f);
     // element offset 8v: express as a row of one vector
     unsigned char* o = static_cast<unsigned char*>(out) + static_cast<size_t>(v) * 8 * Elem<DT>::kBytes;
-    store_decoded<DT>(o, 0, f);
+    store_decoded<DT>(o, 0, f, wide);
   }
 }
 
