@@ -10,10 +10,11 @@
  *   - the CALLER allocates every output (candle: `unsafe { dev.alloc::<T>(el) }`,
  *     candle-nn/src/ops.rs:557); the library allocates and frees nothing and writes every
  *     output element of a call that succeeds;
- *   - pointers of any alignment the element type allows are accepted, but the fast kernels want
- *     16-byte aligned tensors (cudarc's and every other allocator's buffers are), and the
- *     outputs of the quantised lookups are written fastest when they are 32-byte aligned (one
- *     256-bit store per lane); other inputs take slower kernels with the same results;
+ *   - alignment: the norms and the dense gathers accept any pointer the element type allows and
+ *     take slower kernels (same results) for tensors that are not 16-byte aligned; the quantised
+ *     entry points require 16-byte aligned outputs (refused with CB200_E_INVALID_ARGUMENT
+ *     otherwise) and write them fastest when they are 32-byte aligned, one 256-bit store per
+ *     lane; buffers from cudarc's or any other device allocator satisfy all of this;
  *   - work is enqueued on `stream` and the call returns without synchronising;
  *   - the return value is 0 or a negative CB200_E_* code; cb200_last_error() returns a
  *     thread-local message for the last failing call of the calling thread;
