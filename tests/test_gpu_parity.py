@@ -740,3 +740,48 @@ def test_cpp_host_mirror_on_the_gpu(cb, tmp_path):
     emb = np.fromfile(tmp_path / "emb.f32", np.float32).reshape(n_ids, cols)
     good = np.arange(n_ids) != 37
     assert np.array_equal(emb[good], table[ids[good]]) and not emb[37].any()
+
+
+@pytest.mark.parametrize("qtype", ["q8_0", "q4_0"])
+def test_outputs_that_are_only_16_byte_aligned(cb, qtype):
+    # The quantised kernels write a lane's 32 output bytes with one 256-bit store when the destination
+    # is 32-byte aligned and with two 16-byte stores otherwise: the same call into buffers that start
+    # 16 bytes past a 32-byte boundary must give the same bits (lookup + norm with the gathered rows,
+    # lookup to f32, dequantize to f32).
+    from candle_b200 import _cabi
+    from candle_b200.ops import _stream, new_status
+
+    rng = np.random.default_rng(88)
+    gq = getattr(cb.GgmlDType, qtype.upper())
+    vocab, hidden, n = 300, 4096, 700
+    qt = make_qtable(rng, qtype, vocab, hidden)
+    q = cb.QTensor.from_raw(torch.from_numpy(qt), gq, (vocab, hidden), device="cuda")
+    alpha = from_oracle(randn(rng, (hidden,), "bf16", 1.0, 0.1), "bf16")
+    ids_np = rng.integers(0, vocab, size=(n,)).astype(np.uint32)
+    ids = ids_tensor(ids_np)
+    st = new_status("cuda")
+    y_ref, g_ref = cb.qembedding_rms_norm(q, ids, alpha, 1e-5, return_gathered=True)
+    ybuf = torch.zeros(n * hidden + 8, dtype=torch.bfloat16, device="cuda")
+    gbuf = torch.zeros(n * hidden + 8, dtype=torch.bfloat16, device="cuda")
+    y, g = ybuf[8:], gbuf[8:]
+    assert y.data_ptr() % 32 == 16 and g.data_ptr() % 32 == 16
+    _cabi.call("cb200_qembedding_rms_norm", q.data.data_ptr(), gq.value, ids.data_ptr(), alpha.data_ptr(), y.data_ptr(),
+               g.data_ptr(), vocab, hidden, n, 1e-5, 2, 1, 0, vocab, 0, st.data_ptr(), _stream(alpha))
+    torch.cuda.synchronize()
+    assert st[0].item() == 0
+    assert torch.equal(y.view(n, hidden).view(torch.int16), y_ref.view(torch.int16))
+    assert torch.equal(g.view(n, hidden).view(torch.int16), g_ref.view(torch.int16))
+    # f32 outputs
+    e_ref = q.embedding(ids, torch.float32)
+    d_ref = q.dequantize(torch.float32)
+    ebuf = torch.zeros(n * hidden + 4, dtype=torch.float32, device="cuda")
+    dbuf = torch.zeros(vocab * hidden + 4, dtype=torch.float32, device="cuda")
+    e, d = ebuf[4:], dbuf[4:]
+    assert e.data_ptr() % 32 == 16 and d.data_ptr() % 32 == 16
+    _cabi.call("cb200_qembedding", q.data.data_ptr(), gq.value, ids.data_ptr(), e.data_ptr(), vocab, hidden, n, 0, 1, 0,
+               vocab, st.data_ptr(), _stream(alpha))
+    _cabi.call("cb200_dequantize", q.data.data_ptr(), gq.value, d.data_ptr(), vocab * hidden, 0, _stream(alpha))
+    torch.cuda.synchronize()
+    assert torch.equal(e.view(n, hidden).view(torch.int32), e_ref.view(torch.int32))
+    assert torch.equal(d.view(vocab, hidden).view(torch.int32), d_ref.view(torch.int32))
+    assert np.array_equal(to_oracle(e_ref), oracle.qembedding(qt, qtype, ids_np, "f32"))
