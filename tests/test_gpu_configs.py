@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import TORCH_DT, from_oracle, ids_tensor, make_qtable, randn, to_oracle
+from helpers import from_oracle, ids_tensor, make_qtable, randn, to_oracle
 
 pytestmark = pytest.mark.gpu
 THREADS = 0  # the oracle's default: all cores
