@@ -402,7 +402,7 @@ int cb200_qembedding_rms_norm(const void* qtable, int qtype, const void* ids, co
                      !(flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC));
   const bool forced = (flags & (CB200_FLAG_FORCE_LANEROW | CB200_FLAG_FORCE_GENERIC)) != 0;
   if (!fused && !forced && aligned16(qtable) && cb200::kqrms_supported(qtype, out_dtype, hidden)) {
-    // K-quant super-blocks: the row-register kernel with a decoder in front, one launch
+    // K-quant super-blocks and Q4_1 / Q5_0 / Q5_1: the row-register kernel with a decoder in front, one launch
     cb200::QRmsArgs a{};
     a.qtable = static_cast<const unsigned char*>(qtable);
     a.ids = ids;

@@ -1,5 +1,6 @@
 // Lookup + RMS norm in one launch for tables in the K-quant super-block formats (Q2K ... Q8K,
-// candle-core/src/quantized/k_quants.rs:698-1883): what candle computes as
+// candle-core/src/quantized/k_quants.rs:698-1883) and in the 32-element formats the row-slot kernel
+// has no decoder for (Q4_1, Q5_0, Q5_1, k_quants.rs:50-84): what candle computes as
 //   dequantize(table) -> to_dtype(T) -> embedding(ids) -> rms_norm(alpha, eps)
 // (candle-transformers/src/models/quantized_llama.rs:378-379, candle-nn/src/ops.rs:447-508).
 //
@@ -219,13 +220,14 @@ cudaError_t launch_kq(int dtype, const QRmsArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-// Row lengths the kernel takes: 16-bit output, a whole number of super-blocks, V = tpr * vpt with the
+// Row lengths the kernel takes: 16-bit output, a whole number of blocks, V = tpr * vpt with the
 // split above, the staged rows and the parked row within the shared memory of a quarter of an SM.
 bool kqrms_supported(int qtype, int dtype, int cols) {
   int tpr, vpt, rpc;
-  if (!is_kquant(qtype) || (dtype != kDtBF16 && dtype != kDtF16) || cols <= 0 || cols % 256 != 0) return false;
+  const bool takes = is_kquant(qtype) || qtype == CB200_QTYPE_Q4_1 || qtype == CB200_QTYPE_Q5_0 || qtype == CB200_QTYPE_Q5_1;
+  if (!takes || (dtype != kDtBF16 && dtype != kDtF16) || cols <= 0 || cols % qblock_elems(qtype) != 0) return false;
   if (!kq_shape(cols / 8, tpr, vpt, rpc)) return false;
-  const int row_bytes = cols / 256 * qblock_bytes(qtype);
+  const int row_bytes = cols / qblock_elems(qtype) * qblock_bytes(qtype);
   if (row_bytes % 16 != 0) return false;
   return RowRegSmem::bytes(rpc, tpr, cols / 8, true) + static_cast<size_t>(rpc) * KqStage::bytes(row_bytes) <= 56 * 1024;
 }
@@ -245,6 +247,12 @@ cudaError_t launch_kqrms(int qtype, int dtype, const QRmsArgs& a, cudaStream_t s
       return launch_kq<CB200_QTYPE_Q6K>(dtype, a, stream);
     case CB200_QTYPE_Q8K:
       return launch_kq<CB200_QTYPE_Q8K>(dtype, a, stream);
+    case CB200_QTYPE_Q4_1:
+      return launch_kq<CB200_QTYPE_Q4_1>(dtype, a, stream);
+    case CB200_QTYPE_Q5_0:
+      return launch_kq<CB200_QTYPE_Q5_0>(dtype, a, stream);
+    case CB200_QTYPE_Q5_1:
+      return launch_kq<CB200_QTYPE_Q5_1>(dtype, a, stream);
     default:
       return cudaErrorInvalidValue;
   }

@@ -59,8 +59,9 @@ extern "C" {
 
 /* Block formats: ggml type ids as in candle-core/src/quantized/mod.rs:152-171.  Q4_0 and Q8_0 are
  * accepted everywhere; Q4_1, Q5_0, Q5_1 and the K-quant super-blocks of 256 elements (Q2K .. Q8K,
- * candle-core/src/quantized/k_quants.rs:96-154) by cb200_dequantize and cb200_qembedding, and by
- * cb200_qembedding_rms_norm through its two-launch route.  A row must be a whole number of blocks:
+ * candle-core/src/quantized/k_quants.rs:96-154) by cb200_dequantize, cb200_qembedding and
+ * cb200_qembedding_rms_norm (one launch for the usual row lengths, two otherwise).  Q8_1 is refused:
+ * candle has no decoder for it (k_quants.rs:693-695).  A row must be a whole number of blocks:
  * hidden % 32 == 0, hidden % 256 == 0 for the K-quants. */
 #define CB200_QTYPE_Q4_0 2
 #define CB200_QTYPE_Q4_1 3

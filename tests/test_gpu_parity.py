@@ -491,7 +491,7 @@ def test_qembedding_rms_norm_matches_oracle(cb, qtype, dtype):
 
 
 @pytest.mark.parametrize("qtype,hidden", [("q4_0", 8192), ("q8_0", 4096), ("q8_0", 2048), ("q4k", 4096), ("q6k", 2048),
-                                          ("q5k", 8192)])
+                                          ("q5k", 8192), ("q5_0", 4096), ("q4_1", 2048), ("q5_1", 8192)])
 def test_qembedding_rms_norm_many_rows_equals_lookup_then_norm(cb, qtype, hidden):
     # Rows of two and four warps, enough of them that thousands fall to the exact replay while the
     # slot's other warps are still busy with their copy of the decision: the single-launch kernel must
